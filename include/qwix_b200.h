@@ -1,0 +1,132 @@
+/*
+ * qwix_b200 -- C ABI of the B200 (sm_100a) backend for qwix's quantized-inference path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, returns an
+ * int32 status (0 = ok) and never allocates device memory: outputs and scratch are the
+ * caller's.  Calls are re-entrant; the library keeps no mutable state besides a cache of
+ * immutable driver entry points.  Paths cited below are inside the google/qwix tree.
+ *
+ * Array views.  A quantizer call sees its operand as a contiguous row-major [P, R, C]
+ * array cut into tiles of (tp, tr, tc) elements; every tile owns one scale (and one
+ * zero point), stored row-major as [P/tp, R/tr, C/tc].  This is the rank-collapsed form
+ * of qwix's (channelwise_axes, tiled_axes): a channelwise axis has tile 1, a reduced axis
+ * has tile = extent, a sub-channel axis has its tile size (qarray.py:332-349).
+ *
+ * int4.  QWX_S4 buffers are packed two codes per byte along C, low nibble = even index.
+ * QWX_S4U holds one sign-extended code per byte (the logical layout of a QArray).
+ */
+#ifndef QWIX_B200_H_
+#define QWIX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* qwx_stream_t; /* a cudaStream_t */
+
+enum qwx_status {
+  QWX_OK = 0,
+  QWX_ERR_NULL = 1,        /* required pointer is NULL                       */
+  QWX_ERR_SHAPE = 2,       /* extents / tiles inconsistent (ValueError)      */
+  QWX_ERR_ALIGN = 3,       /* pointer or pitch misaligned for the kernel     */
+  QWX_ERR_DTYPE = 4,       /* dtype combination not implemented (ValueError) */
+  QWX_ERR_UNSUPPORTED = 5, /* valid in qwix, not built here                  */
+  QWX_ERR_WORKSPACE = 6,   /* workspace missing or too small                 */
+  QWX_ERR_LAUNCH = 7,      /* CUDA reported a launch / driver error          */
+  QWX_ERR_DEVICE_WAIT = 8, /* a bounded device-side wait ran out             */
+  QWX_ERR_NO_DEVICE = 9    /* no sm_100 device / driver entry point missing  */
+};
+
+enum qwx_dtype {
+  QWX_F32 = 0, QWX_BF16 = 1, QWX_F16 = 2,
+  QWX_S8 = 3, QWX_S4 = 4, QWX_E4M3 = 5, QWX_S32 = 6, QWX_S4U = 7
+};
+
+enum qwx_calibration { QWX_ABSMAX = 0, QWX_MINMAX = 1, QWX_RMS = 2 };
+
+/* How intermediates of x / scale (+ zero_point) round before round-half-even:
+ * STRICT rounds every primitive to the array dtype (JAX eager semantics),
+ * FUSED keeps them in float32 (XLA under jit).  Identical for float32 arrays. */
+enum qwx_rounding { QWX_STRICT = 0, QWX_FUSED = 1 };
+
+/* B-operand memory order of the GEMMs.  QWX_B_KN: the weight as qwix holds it, [K, N]
+ * row-major (N contiguous).  QWX_B_NK: a pre-transposed copy, [N, K] row-major. */
+enum qwx_b_layout { QWX_B_KN = 0, QWX_B_NK = 1 };
+
+/* Epilogue rounding of the quantized GEMMs.  QWX_EPI_F32: float(acc) * sa * sb computed
+ * in float32, rounded once to the output dtype.  QWX_EPI_REFERENCE: every step rounds to
+ * the output dtype in the reference's order R(R(R(acc) * sa) * sb) (dot_general.py:255-261). */
+enum qwx_epilogue { QWX_EPI_F32 = 0, QWX_EPI_REFERENCE = 1 };
+
+int qwx_version(void);
+const char* qwx_status_string(int status);
+
+/* Bytes of scratch the quantizer calls below need for this view (zero is possible). */
+size_t qwx_quantize_workspace_bytes(int64_t P, int64_t R, int64_t C,
+                                    int64_t tp, int64_t tr, int64_t tc);
+
+/* qarray.calibrate (qarray.py:470-534): per-tile absmax, (min, max) or rms*arg.
+ * out_a = absmax (or min), out_b = max for QWX_MINMAX else NULL; both in x_dtype.
+ * has_arg selects the optional multiplier of absmax/minmax (required for rms). */
+int qwx_calibrate(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C,
+                  int64_t tp, int64_t tr, int64_t tc, int method, int has_arg,
+                  double arg, void* out_a, void* out_b, void* workspace,
+                  size_t workspace_bytes, qwx_stream_t stream);
+
+/* qarray.compute_scale_zero_point (qarray.py:537-584) for int8/int4/e4m3 codes.
+ * calib_b == NULL: symmetric, scale = calib_a / bound.  Otherwise asymmetric with
+ * (min, max) = (calib_a, calib_b); zero_point is written as int8 codes. */
+int qwx_compute_scale_zero_point(const void* calib_a, const void* calib_b, int dtype,
+                                 int64_t n, int qtype, void* scale, void* zero_point,
+                                 qwx_stream_t stream);
+
+/* qarray.quantize_with_scale_zero_point (qarray.py:594-635): true division by the scale
+ * (already in x_dtype), optional zero point (int8 codes), round-half-even + saturate
+ * (ints) or clip + RN-even (e4m3) (numerics.py:139-196). */
+int qwx_quantize_with_scale(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C,
+                            int64_t tp, int64_t tr, int64_t tc, const void* scale,
+                            const void* zero_point, int qtype, int rounding, void* q,
+                            qwx_stream_t stream);
+
+/* qarray.quantize (qarray.py:638-644): the three steps above in as few passes over x as
+ * the view allows (one pass when tiles are row segments or fit in shared memory).
+ * scale is written in x_dtype; zero_point (int8 codes) only for QWX_MINMAX. */
+int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C,
+                 int64_t tp, int64_t tr, int64_t tc, int method, int has_arg, double arg,
+                 int qtype, int rounding, void* q, void* scale, void* zero_point,
+                 void* workspace, size_t workspace_bytes, qwx_stream_t stream);
+
+/* qarray.dequantize (qarray.py:692-708): (q - zero_point) * scale in scale_dtype. */
+int qwx_dequantize(const void* q, int qtype, int64_t P, int64_t R, int64_t C,
+                   int64_t tp, int64_t tr, int64_t tc, const void* scale, int scale_dtype,
+                   const void* zero_point, void* out, qwx_stream_t stream);
+
+/* Repack the logical [K, N] codes of a weight into the other GEMM operand order:
+ * [K, N] -> [N, K] for 8-bit codes (elem_bytes = 1). */
+int qwx_transpose_codes(const void* src, int64_t rows, int64_t cols, void* dst,
+                        qwx_stream_t stream);
+
+/* dot_general._fast_dot_general (dot_general.py:135-261) for 2-D operands whose codes
+ * are int8 (acc int32, tcgen05 kind::i8) or e4m3 (acc float32, kind::f8f6f4):
+ *   out[m, n] = sum_t ( sum_{k in tile t} a[m,k] * b[k,n] ) * sa[m, t] * sb[t, n]
+ * a: [M, K] row-major.  b: [K, N] (QWX_B_KN) or [N, K] (QWX_B_NK).
+ * k_tile = 0: one scale per row of a / column of b (sa: [M], sb: [N]); otherwise K is cut
+ * in tiles of k_tile (a multiple of 128) and sa: [M, K/k_tile], sb: [K/k_tile, N]; a side
+ * with sa_tiled/sb_tiled = 0 still has a single scale along K.  sa or sb may be NULL
+ * (operand not a QArray).  out_dtype QWX_BF16 / QWX_F32 / QWX_F16, or QWX_S32 with both
+ * scales NULL for the raw int32 accumulator.
+ * error_flag: optional device int32 that receives a nonzero code if a bounded wait inside
+ * the kernel ran out. */
+int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_layout,
+                int64_t M, int64_t N, int64_t K, int64_t k_tile,
+                const void* sa, int sa_tiled, const void* sb, int sb_tiled,
+                int scale_dtype, void* out, int out_dtype, int epilogue, int32_t* error_flag,
+                qwx_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QWIX_B200_H_ */

@@ -147,10 +147,10 @@ def call_with_generic_broadcast(op: Callable, x: np.ndarray, y: np.ndarray):
 
 def _mean_like_jnp(sq: np.ndarray, axes) -> np.ndarray:
   # jnp.mean sums 16-bit floats in float32, divides, then casts back.
-  wide = np.float32 if sq.dtype.itemsize < 4 else sq.dtype
+  wide = np.dtype(np.float32) if sq.dtype.itemsize < 4 else sq.dtype
   total = np.sum(sq.astype(wide), axis=axes, keepdims=True, dtype=wide)
   count = math.prod(sq.shape[a] for a in axes)
-  return (total / wide(count)).astype(sq.dtype)
+  return (total / wide.type(count)).astype(sq.dtype)
 
 
 def calibrate(array: np.ndarray, how: HowToQuantize) -> dict[str, np.ndarray]:

@@ -1,0 +1,12 @@
+"""qwix_b200: the quantized-inference path of qwix on B200 (sm_100a) CUDA kernels.
+
+Public names follow qwix/__init__.py:20-42.
+"""
+
+from qwix_b200.core.qarray import QArray, HowToQuantize, dequantize
+from qwix_b200.core.qarray import quantize_api as quantize
+from qwix_b200.core.dot_general import dot_general
+from qwix_b200.core.einsum import einsum
+from qwix_b200.core.dot import dot
+
+__all__ = ['QArray', 'HowToQuantize', 'quantize', 'dequantize', 'dot_general', 'einsum', 'dot']

@@ -1,0 +1,93 @@
+"""ctypes binding of libqwix_b200.so.  There is no fallback: a missing library or a
+nonzero status raises."""
+
+from __future__ import annotations
+
+import ctypes
+import pathlib
+import threading
+
+import torch
+
+_LIB_PATH = pathlib.Path(__file__).resolve().parent / 'libqwix_b200.so'
+_lock = threading.Lock()
+_lib = None
+
+# enum qwx_dtype
+F32, BF16, F16, S8, S4, E4M3, S32, S4U = range(8)
+# enum qwx_calibration
+ABSMAX, MINMAX, RMS = range(3)
+# enum qwx_rounding
+STRICT, FUSED = 0, 1
+# enum qwx_b_layout
+B_KN, B_NK = 0, 1
+# enum qwx_epilogue
+EPI_F32, EPI_REFERENCE = 0, 1
+
+_VALUE_ERRORS = {2, 3, 4}  # shape / align / dtype -> ValueError like the reference
+
+FLOAT_CODES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+_i64, _int, _vp, _sz, _dbl = (ctypes.c_int64, ctypes.c_int, ctypes.c_void_p,
+                              ctypes.c_size_t, ctypes.c_double)
+
+_SIGNATURES = {
+    'qwx_version': (_int, []),
+    'qwx_status_string': (ctypes.c_char_p, [_int]),
+    'qwx_quantize_workspace_bytes': (_sz, [_i64] * 6),
+    'qwx_calibrate': (_int, [_vp, _int] + [_i64] * 6 + [_int, _int, _dbl, _vp, _vp, _vp, _sz, _vp]),
+    'qwx_compute_scale_zero_point': (_int, [_vp, _vp, _int, _i64, _int, _vp, _vp, _vp]),
+    'qwx_quantize_with_scale': (_int, [_vp, _int] + [_i64] * 6 + [_vp, _vp, _int, _int, _vp, _vp]),
+    'qwx_quantize': (_int, [_vp, _int] + [_i64] * 6 + [_int, _int, _dbl, _int, _int, _vp, _vp, _vp, _vp, _sz, _vp]),
+    'qwx_dequantize': (_int, [_vp, _int] + [_i64] * 6 + [_vp, _int, _vp, _vp, _vp]),
+    'qwx_transpose_codes': (_int, [_vp, _i64, _i64, _vp, _vp]),
+    'qwx_gemm_q8': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,
+                           _int, _vp, _int, _int, _vp, _vp]),
+}
+
+
+def exported_symbols():
+  """Names that include/qwix_b200.h declares and the library must export."""
+  return tuple(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+  global _lib
+  if _lib is None:
+    with _lock:
+      if _lib is None:
+        if not _LIB_PATH.exists():
+          raise RuntimeError(
+              f'{_LIB_PATH} is missing: build it with `python -m qwix_b200.build` '
+              '(there is no CPU or PyTorch fallback for the quantized kernels).')
+        handle = ctypes.CDLL(str(_LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+          fn = getattr(handle, name)
+          fn.restype, fn.argtypes = res, args
+        _lib = handle
+  return _lib
+
+
+def check(status: int, what: str):
+  if status == 0:
+    return
+  msg = lib().qwx_status_string(status).decode()
+  exc = ValueError if status in _VALUE_ERRORS else (
+      NotImplementedError if status == 5 else RuntimeError)
+  raise exc(f'{what}: {msg} (status {status})')
+
+
+def ptr(t: torch.Tensor | None):
+  return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_ptr(device=None):
+  return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def require_cuda(*tensors):
+  for t in tensors:
+    if t is not None and not t.is_cuda:
+      raise RuntimeError(
+          'qwix_b200 kernels run on a CUDA device only; got a tensor on '
+          f'{t.device}.  There is no CPU fallback.')

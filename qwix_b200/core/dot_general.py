@@ -1,0 +1,223 @@
+"""Quantized dot_general on CUDA tensors: drop-in for the `_dot_general_fn` hook.
+
+Same signature, path choice and error behaviour as qwix/_src/core/dot_general.py.  The
+fast path (codes x codes, dequantize on output) is one tcgen05 GEMM with the scales fused
+into its epilogue (csrc/gemm_q8.cu); the slow path dequantizes with the CUDA kernel and
+hands the floating-point contraction to a plain library GEMM, as the reference hands it
+to XLA.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Any, Mapping, Sequence
+
+import torch
+
+from qwix_b200 import _lib
+from qwix_b200.core import numerics
+from qwix_b200.core import qarray
+from qwix_b200.core.qarray import QArray
+
+# Tiles smaller than this on a contracting axis force the dequantize-first path
+# (dot_general.py:402-404).
+MIN_TILE_SIZE_TO_DEQUANT_ON_OUTPUT = 128
+
+# 'f32': float(acc) * sa * sb in float32, rounded once (default).  'reference': every step
+# rounds to the result dtype in the reference's order (dot_general.py:255-261).
+EPILOGUE = 'f32'
+
+
+def get_how_to_quantize(*, dimension_numbers, ndims: tuple[int, int], for_lhs: bool,
+                        tile_size: Mapping[int, int | float] | int | float | None,
+                        **kwargs: Any) -> qarray.HowToQuantize:
+  """dot_general.py:28-76 -- channelwise on every non-contracting axis; sub-channel tiles
+  on the last contracting axis when a tile size is given."""
+  side = 0 if for_lhs else 1
+  ndim = ndims[side]
+  contracting = dimension_numbers[0][side]
+  if isinstance(tile_size, Mapping):
+    tiled = tile_size
+  else:
+    tiled = {contracting[-1]: tile_size} if tile_size else {}
+  channelwise = sorted(set(range(ndim)) - set(contracting) - set(tiled.keys()))
+  return qarray.HowToQuantize(channelwise_axes=channelwise, tiled_axes=tiled, **kwargs)
+
+
+def _free_axes(ndim, contracting, batch):
+  return [a for a in range(ndim) if a not in contracting and a not in batch]
+
+
+def _is_low_precision(t: torch.Tensor) -> bool:
+  return not numerics.should_quantize(t.dtype)
+
+
+def use_fast_path(lhs, rhs, dimension_numbers) -> bool:
+  """The path choice of dot_general.py:442-472."""
+  for operand, ca in zip((lhs, rhs), dimension_numbers[0]):
+    if not isinstance(operand, QArray):
+      if numerics.should_quantize(operand.dtype):
+        return False
+      continue
+    qarray.validate_qarray(operand)
+    if not numerics.can_dequant_on_output(operand.qtype):
+      return False
+    for axis in ca:
+      if operand.scale.shape[axis] > 1:
+        tile = operand.qvalue.shape[axis] // operand.scale.shape[axis]
+        if tile < MIN_TILE_SIZE_TO_DEQUANT_ON_OUTPUT:
+          return False
+  return True
+
+
+def _out_code(dtype: torch.dtype) -> int:
+  table = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16,
+           torch.int32: _lib.S32}
+  if dtype not in table:
+    raise ValueError(f'unsupported result dtype {dtype} for the quantized GEMM')
+  return table[dtype]
+
+
+def _codes_and_scale(x, contracting, batch, free, side: str):
+  """Returns (codes [B, free, K] or [B, K, free] view info, scale [B, free] or None)."""
+  if isinstance(x, QArray):
+    if x.zero_point is not None:
+      raise NotImplementedError(
+          'asymmetric operands on the dequantize-on-output path are not built yet.')
+    for a in contracting:
+      if x.scale.shape[a] != 1:
+        raise NotImplementedError(
+            'sub-channel scales along a contracting axis are not built yet for the '
+            'tensor-core path.')
+    full = [x.qvalue.shape[a] for a in list(batch) + list(free)]
+    scale = x.scale.permute(list(batch) + list(free) + list(contracting))
+    scale = scale.reshape([x.scale.shape[a] for a in list(batch) + list(free)])
+    scale = scale.expand(full).reshape(
+        math.prod(full[:len(batch)]), math.prod(full[len(batch):])).contiguous()
+    return x.qvalue, scale, x.qtype
+  return x, None, numerics.qtype_name(x.dtype)
+
+
+def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
+                      **kwargs) -> torch.Tensor:
+  """dot_general.py:135-261 on the tensor cores."""
+  del kwargs
+  (lca, rca), (lba, rba) = dimension_numbers
+  lca, rca, lba, rba = map(list, (lca, rca, lba, rba))
+  if isinstance(lhs, QArray) and isinstance(rhs, QArray) and \
+      lhs.zero_point is not None and rhs.zero_point is not None:
+    raise ValueError('Only one operand can be asymmetric.')
+  if isinstance(lhs, QArray) and isinstance(rhs, QArray):
+    lt, rt = qarray.get_tiled_axes(lhs), qarray.get_tiled_axes(rhs)
+    for l, r in zip(lca, rca):
+      if lt.get(l) and rt.get(r) and lt[l] != rt[r]:
+        raise ValueError('Contracting axes must be tiled with the same tile size.'
+                         f' lhs_tiled_axes={lt} rhs_tiled_axes={rt} {dimension_numbers=}')
+  lfa = _free_axes(lhs.ndim, lca, lba)
+  rfa = _free_axes(rhs.ndim, rca, rba)
+  acc_t, res_t = qarray.get_accumulator_and_result_type(
+      lhs, rhs, preferred_element_type=preferred_element_type)
+
+  lq, ls, lname = _codes_and_scale(lhs, lca, lba, lfa, 'lhs')
+  rq, rs, rname = _codes_and_scale(rhs, rca, rba, rfa, 'rhs')
+  if lname != rname or lname not in ('int8', 'float8_e4m3fn'):
+    raise NotImplementedError(
+        f'tensor-core path needs int8 x int8 or e4m3 x e4m3 codes, got {lname} x {rname}.')
+  code = _lib.S8 if lname == 'int8' else _lib.E4M3
+  _lib.require_cuda(lq, rq)
+
+  bshape = [lq.shape[a] for a in lba]
+  mshape = [lq.shape[a] for a in lfa]
+  nshape = [rq.shape[a] for a in rfa]
+  B, M, N = math.prod(bshape), math.prod(mshape), math.prod(nshape)
+  K = math.prod(lq.shape[a] for a in lca)
+  a3 = lq.permute(lba + lfa + lca).reshape(B, M, K).contiguous()
+  # Use the weight where it lies: [.., K, N] order needs no repack (MN-major operand).
+  kn = rq.permute(rba + rca + rfa)
+  nk = rq.permute(rba + rfa + rca)
+  if nk.is_contiguous() and not kn.is_contiguous():
+    b3, layout = nk.reshape(B, N, K), _lib.B_NK
+  else:
+    b3, layout = kn.reshape(B, K, N).contiguous(), _lib.B_KN
+  if layout == _lib.B_KN and N % 16:
+    b3, layout = nk.reshape(B, N, K).contiguous(), _lib.B_NK
+
+  scale_dt = None
+  for s in (ls, rs):
+    if s is not None:
+      scale_dt = s.dtype if scale_dt is None else torch.promote_types(scale_dt, s.dtype)
+  if scale_dt is not None:
+    ls = None if ls is None else ls.to(scale_dt)
+    rs = None if rs is None else rs.to(scale_dt)
+  raw = ls is None and rs is None and code == _lib.S8
+  out_t = torch.int32 if raw else res_t
+  out = torch.empty((B, M, N), dtype=out_t, device=lq.device)
+  err = torch.zeros(1, dtype=torch.int32, device=lq.device)
+  epi = _lib.EPI_REFERENCE if EPILOGUE == 'reference' else _lib.EPI_F32
+  fn = _lib.lib().qwx_gemm_q8
+  for b in range(B):
+    _lib.check(fn(_lib.ptr(a3[b]), _lib.ptr(b3[b]), code, layout, M, N, K, 0,
+                  _lib.ptr(None if ls is None else ls[b]), 0,
+                  _lib.ptr(None if rs is None else rs[b]), 0,
+                  numerics.code_of_float(scale_dt) if scale_dt is not None else _lib.F32,
+                  _lib.ptr(out[b]), _out_code(out_t), epi, _lib.ptr(err),
+                  _lib.stream_ptr(lq.device)), 'dot_general')
+  out = out.reshape(bshape + mshape + nshape)
+  return out if out.dtype == res_t else out.to(res_t)
+
+
+def _plain_dot_general(lhs: torch.Tensor, rhs: torch.Tensor, dimension_numbers,
+                       preferred_element_type=None) -> torch.Tensor:
+  """jax.lax.dot_general on floating tensors (library GEMM): output axes are
+  batch, lhs free, rhs free."""
+  (lca, rca), (lba, rba) = dimension_numbers
+  lca, rca, lba, rba = map(list, (lca, rca, lba, rba))
+  lfa = _free_axes(lhs.ndim, lca, lba)
+  rfa = _free_axes(rhs.ndim, rca, rba)
+  compute = torch.promote_types(lhs.dtype, rhs.dtype)
+  bshape = [lhs.shape[a] for a in lba]
+  mshape = [lhs.shape[a] for a in lfa]
+  nshape = [rhs.shape[a] for a in rfa]
+  K = math.prod(lhs.shape[a] for a in lca)
+  a3 = lhs.permute(lba + lfa + lca).reshape(math.prod(bshape), math.prod(mshape), K)
+  b3 = rhs.permute(rba + rca + rfa).reshape(math.prod(bshape), K, math.prod(nshape))
+  out = torch.bmm(a3.to(compute), b3.to(compute)).reshape(bshape + mshape + nshape)
+  want = preferred_element_type or compute
+  return out if out.dtype == want else out.to(want)
+
+
+def _slow_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
+                      **kwargs) -> torch.Tensor:
+  """dot_general.py:264-275 -- dequantize the operands, then a floating-point dot."""
+  del kwargs
+  if isinstance(lhs, QArray):
+    lhs = qarray.dequantize(lhs)
+  if isinstance(rhs, QArray):
+    rhs = qarray.dequantize(rhs)
+  return _plain_dot_general(lhs, rhs, dimension_numbers, preferred_element_type)
+
+
+def loop_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
+                     **kwargs) -> torch.Tensor:
+  """dot_general.py:278-399 -- the in-kernel accumulation loop of the reference's Pallas
+  entry point.  On this backend the loop over K tiles lives inside the GEMM kernel, so the
+  entry point resolves to the same fused kernel as the fast path."""
+  for x in (lhs, rhs):
+    if isinstance(x, QArray):
+      assert x.zero_point is None
+  return _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type, **kwargs)
+
+
+def dot_general(lhs, rhs, dimension_numbers, precision=None, preferred_element_type=None,
+                **kwargs) -> torch.Tensor:
+  """dot_general.py:407-491 -- drop-in for jax.lax.dot_general with QArray operands.
+
+  `out_sharding` and `precision` are accepted and ignored (one device per process).
+  """
+  del precision
+  kwargs.pop('out_sharding', None)
+  if use_fast_path(lhs, rhs, dimension_numbers):
+    return _fast_dot_general(lhs, rhs, dimension_numbers,
+                             preferred_element_type=preferred_element_type, **kwargs)
+  return _slow_dot_general(lhs, rhs, dimension_numbers,
+                           preferred_element_type=preferred_element_type, **kwargs)

@@ -1,0 +1,20 @@
+// Version and status strings of the C ABI.
+#include "common.cuh"
+
+extern "C" int qwx_version(void) { return 100; }
+
+extern "C" const char* qwx_status_string(int status) {
+  switch (status) {
+    case QWX_OK: return "ok";
+    case QWX_ERR_NULL: return "a required pointer is NULL";
+    case QWX_ERR_SHAPE: return "inconsistent shape, tile or option";
+    case QWX_ERR_ALIGN: return "pointer or row pitch is not 16-byte aligned";
+    case QWX_ERR_DTYPE: return "unsupported dtype combination";
+    case QWX_ERR_UNSUPPORTED: return "valid request that this build does not implement";
+    case QWX_ERR_WORKSPACE: return "workspace missing or too small";
+    case QWX_ERR_LAUNCH: return "CUDA launch or driver call failed";
+    case QWX_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+    case QWX_ERR_NO_DEVICE: return "no usable sm_100 device or driver entry point";
+    default: return "unknown status";
+  }
+}

@@ -1,0 +1,390 @@
+// Quantized GEMM for 8-bit codes on tcgen05 tensor cores with the dequant fused in the
+// epilogue: the device side of dot_general._fast_dot_general (dot_general.py:135-261).
+//
+//   out[m, n] = convert( acc[m, n] * sa[m] * sb[n] ),  acc = sum_k a[m, k] * b[k, n]
+//
+// int8 x int8 -> int32 (kind::i8) and e4m3 x e4m3 -> float32 (kind::f8f6f4).
+//
+// Structure (one persistent CTA per SM, 256 threads):
+//   warp 0      TMA producer: A [128 x 128B] and B [256 x 128B] tiles, 128-byte swizzle, into a
+//               4-stage shared-memory ring guarded by full/empty mbarriers
+//   warp 1      MMA issuer: one elected thread issues 4 x tcgen05.mma (M128 N256 K32) per stage,
+//               accumulating in tensor memory; tcgen05.commit releases the stage
+//   warp 2      allocates / frees the 512 tensor-memory columns (two 128x256 accumulators)
+//   warps 4-7   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, scale, convert, store;
+//               runs on accumulator i while the MMA warp fills accumulator i^1
+// B may be [N, K] (K-major operand) or qwix's native [K, N] (MN-major operand, no repack).
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace qwx {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;       // bytes == elements for 8-bit codes: one 128-byte swizzle row
+constexpr int UMMA_K = 32;    // K per tcgen05.mma for 8-bit operands
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK;
+constexpr int kBBytes = BN * BK;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kAccCols = BN;  // 32-bit accumulator columns per tile
+constexpr int kTmemCols = 2 * kAccCols;
+constexpr int kGemmThreads = 256;
+constexpr int kEpiWarp0 = 4;
+
+struct Control {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort;
+  float sb[4][2][BN];  // per epilogue warp, per accumulator
+};
+
+constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + sizeof(Control);
+
+struct GemmParams {
+  int64_t M, N, K;
+  const void* sa;
+  const void* sb;
+  int scale_dtype;
+  void* out;
+  int out_dtype;
+  int epilogue;
+  int32_t* error_flag;
+  int tiles_m, tiles_n;
+};
+
+__device__ __forceinline__ float load_scale(const void* p, int dtype, int64_t i) {
+  if (dtype == QWX_F32) return reinterpret_cast<const float*>(p)[i];
+  if (dtype == QWX_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(reinterpret_cast<const __half*>(p)[i]);
+}
+
+__device__ __forceinline__ float round_out(float v, int out_dtype) {
+  if (out_dtype == QWX_BF16) return round_to<BF16>(v);
+  if (out_dtype == QWX_F16) return round_to<F16>(v);
+  return v;
+}
+
+template <MmaKind KIND, int BLAYOUT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  Control* ctl = reinterpret_cast<Control*>(smem_raw + (tiles - smem_u32(smem_raw)) +
+                                            (size_t)kStages * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kblocks = (int)((p.K + BK - 1) / BK);
+  volatile int* abort = &ctl->abort;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctl->acc_full[a]), 1);
+      mbar_init(smem_u32(&ctl->acc_empty[a]), 4);
+    }
+    ctl->abort = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tma_a);
+    prefetch_tensormap(&tma_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    long issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * BM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      for (int kb = 0; kb < kblocks && ok; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort);
+          if (ok) {
+            const uint32_t bar = smem_u32(&ctl->full[stage]);
+            const uint32_t sa = tiles + stage * kStageBytes;
+            const uint32_t sb = sa + kABytes;
+            mbar_expect_tx(bar, kStageBytes);
+            tma_load_2d(sa, &tma_a, kb * BK, m0, bar);
+            if (BLAYOUT == QWX_B_NK) {
+              tma_load_2d(sb, &tma_b, kb * BK, n0, bar);
+            } else {
+              tma_load_2d(sb, &tma_b, n0, kb * BK, bar);
+              tma_load_2d(sb + BK * 128, &tma_b, n0 + 128, kb * BK, bar);
+            }
+            ++issued;
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (lane == 0 && *abort) {
+      // Let copies that are still in flight land before the CTA gives up its shared memory.
+      long pending = issued < kStages ? issued : kStages;
+      int s = stage;
+      uint32_t ph = phase;
+      for (long i = 0; i < pending; ++i) {
+        if (--s < 0) { s = kStages - 1; ph ^= 1u; }
+        for (int it = 0; it < 100000; ++it)
+          if (mbar_try_wait(smem_u32(&ctl->full[s]), ph)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc =
+        KIND == MmaKind::kI8
+            ? make_idesc(2, 1, 1, 0, BLAYOUT == QWX_B_KN ? 1 : 0, BM, BN)
+            : make_idesc(1, 0, 0, 0, BLAYOUT == QWX_B_KN ? 1 : 0, BM, BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      if (lane == 0) {
+        ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort);
+        tc_fence_after();
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      for (int kb = 0; kb < kblocks && ok; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort);
+          if (ok) {
+            tc_fence_after();
+            const uint32_t sa = tiles + stage * kStageBytes;
+            const uint32_t sb = sa + kABytes;
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              // A, K-major: 8-row groups 1024 B apart; step 32 B inside the swizzled row.
+              const uint64_t da = make_smem_desc(sa + kk * UMMA_K, 16, 1024);
+              // B, K-major: same as A.  B, MN-major ([K, N] rows of 128 N-bytes): 8 K-rows
+              // per 1024 B group, the second 128 columns BK*128 B further; step 32 K-rows.
+              const uint64_t db = BLAYOUT == QWX_B_NK
+                                      ? make_smem_desc(sb + kk * UMMA_K, 16, 1024)
+                                      : make_smem_desc(sb + kk * UMMA_K * 128, BK * 128, 1024);
+              mma_ss<KIND>(tmem_base + acc * kAccCols, da, db, idesc, (kb | kk) != 0);
+            }
+            mma_commit(smem_u32(&ctl->empty[stage]));
+            if (kb == kblocks - 1) mma_commit(smem_u32(&ctl->acc_full[acc]));
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  } else if (warp >= kEpiWarp0) {
+    // ---------------- epilogue ----------------
+    const int q = warp - kEpiWarp0;           // tensor-memory lane quarter of this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool reference = p.epilogue == QWX_EPI_REFERENCE;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * BM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      // Each warp stages this tile's column scales for itself (no cross-warp barrier, so a
+      // warp that gives up on a wait cannot strand the others).
+      for (int j = lane; j < BN; j += 32) {
+        const int64_t n = (int64_t)n0 + j;
+        ctl->sb[q][acc][j] = (p.sb && n < p.N) ? load_scale(p.sb, p.scale_dtype, n) : 1.0f;
+      }
+      __syncwarp();
+      const int64_t m = (int64_t)m0 + q * 32 + lane;
+      const float sa = (p.sa && m < p.M) ? load_scale(p.sa, p.scale_dtype, m) : 1.0f;
+
+      if (lane == 0) ok = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * kAccCols + c * 32, r);
+        tmem_ld_wait();
+        const int64_t ncol = (int64_t)n0 + c * 32;
+        if (m >= p.M || ncol >= p.N) continue;
+        const float* sbv = &ctl->sb[q][acc][c * 32];
+        if (p.out_dtype == QWX_S32) {
+          int32_t* o = reinterpret_cast<int32_t*>(p.out) + m * p.N + ncol;
+          if (ncol + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && ncol + j < p.N; ++j) o[j] = (int32_t)r[j];
+          }
+          continue;
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float a = KIND == MmaKind::kI8 ? (float)(int32_t)r[j] : __uint_as_float(r[j]);
+          if (reference) {
+            a = round_out(a, p.out_dtype);
+            a = round_out(__fmul_rn(a, sa), p.out_dtype);
+            a = round_out(__fmul_rn(a, sbv[j]), p.out_dtype);
+          } else {
+            a = __fmul_rn(__fmul_rn(a, sa), sbv[j]);
+          }
+          v[j] = a;
+        }
+        if (p.out_dtype == QWX_F32) {
+          float* o = reinterpret_cast<float*>(p.out) + m * p.N + ncol;
+          if (ncol + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && ncol + j < p.N; ++j) o[j] = v[j];
+          }
+        } else {
+          uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + m * p.N + ncol;
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (p.out_dtype == QWX_BF16) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+              __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+          }
+          if (ncol + 32 <= p.N && (p.N & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && ncol + j < p.N; ++j)
+              o[j] = (uint16_t)(w[j >> 1] >> ((j & 1) * 16));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && ctl->abort && p.error_flag) atomicExch(p.error_flag, QWX_ERR_DEVICE_WAIT);
+}
+
+template <MmaKind KIND, int BLAYOUT>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+           cudaStream_t st) {
+  auto kern = gemm_q8_kernel<KIND, BLAYOUT>;
+  static bool configured = false;  // idempotent attribute; a benign race sets it twice
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) !=
+        cudaSuccess)
+      return QWX_ERR_LAUNCH;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, kSmemBytes, st>>>(ta, tb, p);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return v;
+  }();
+  return n;
+}
+
+}  // namespace
+}  // namespace qwx
+
+using namespace qwx;
+
+extern "C" int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_layout, int64_t M,
+                           int64_t N, int64_t K, int64_t k_tile, const void* sa, int sa_tiled,
+                           const void* sb, int sb_tiled, int scale_dtype, void* out,
+                           int out_dtype, int epilogue, int32_t* error_flag,
+                           qwx_stream_t stream) {
+  if (!a || !b || !out) return QWX_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0) return QWX_ERR_SHAPE;
+  if (M > INT32_MAX - BM || N > INT32_MAX - BN || K > INT32_MAX - BK) return QWX_ERR_SHAPE;
+  if (code_dtype != QWX_S8 && code_dtype != QWX_E4M3) return QWX_ERR_DTYPE;
+  if (b_layout != QWX_B_KN && b_layout != QWX_B_NK) return QWX_ERR_SHAPE;
+  if (k_tile != 0 && k_tile != K) {
+    (void)sa_tiled; (void)sb_tiled;
+    return QWX_ERR_UNSUPPORTED;  // per-K-tile scales: not built yet
+  }
+  if (out_dtype == QWX_S32) {
+    if (code_dtype != QWX_S8 || sa || sb) return QWX_ERR_DTYPE;
+  } else if (out_dtype != QWX_BF16 && out_dtype != QWX_F32 && out_dtype != QWX_F16) {
+    return QWX_ERR_DTYPE;
+  }
+  if ((sa || sb) && scale_dtype != QWX_F32 && scale_dtype != QWX_BF16 && scale_dtype != QWX_F16)
+    return QWX_ERR_DTYPE;
+  if (epilogue != QWX_EPI_F32 && epilogue != QWX_EPI_REFERENCE) return QWX_ERR_SHAPE;
+  // TMA: 16-byte aligned bases and row pitches.
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return QWX_ERR_ALIGN;
+  if (K % 16) return QWX_ERR_ALIGN;
+  if (b_layout == QWX_B_KN && (N % 16)) return QWX_ERR_ALIGN;
+  const int elem = out_dtype == QWX_F32 || out_dtype == QWX_S32 ? 4 : 2;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return QWX_ERR_ALIGN;
+  (void)elem;
+
+  CUtensorMap ta, tb;
+  if (!get_encode_tiled()) return QWX_ERR_NO_DEVICE;
+  if (!encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)M, (uint64_t)K, BM, BK))
+    return QWX_ERR_LAUNCH;
+  const bool ok_b = b_layout == QWX_B_NK
+                        ? encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)N, (uint64_t)K, BN, BK)
+                        : encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)K, (uint64_t)N, BK, 128);
+  if (!ok_b) return QWX_ERR_LAUNCH;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.sa = sa; p.sb = sb; p.scale_dtype = scale_dtype;
+  p.out = out; p.out_dtype = out_dtype; p.epilogue = epilogue;
+  p.error_flag = error_flag;
+  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_n = (int)((N + BN - 1) / BN);
+  const int64_t num_tiles = (int64_t)p.tiles_m * p.tiles_n;
+  if (num_tiles > INT32_MAX) return QWX_ERR_SHAPE;
+  const int sms = sm_count();
+  if (sms <= 0) return QWX_ERR_NO_DEVICE;
+  const int grid = (int)(num_tiles < sms ? num_tiles : sms);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (code_dtype == QWX_S8) {
+    return b_layout == QWX_B_NK ? launch<MmaKind::kI8, QWX_B_NK>(ta, tb, p, grid, st)
+                                : launch<MmaKind::kI8, QWX_B_KN>(ta, tb, p, grid, st);
+  }
+  return b_layout == QWX_B_NK ? launch<MmaKind::kF8F6F4, QWX_B_NK>(ta, tb, p, grid, st)
+                              : launch<MmaKind::kF8F6F4, QWX_B_KN>(ta, tb, p, grid, st);
+}

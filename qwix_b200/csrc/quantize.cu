@@ -1,0 +1,719 @@
+// HBM-bound quantizer kernels: calibrate, scale/zero-point, quantize, dequantize.
+//
+// Numerics follow qwix/_src/core/qarray.py:470-708 and numerics.py:139-196 step by step:
+// every primitive is a float32 operation rounded to the array dtype (strict mode).  All
+// loads and stores are 128-bit wide and coalesced; reductions use warp shuffles plus one
+// shared-memory hop, and cross-CTA reductions use integer atomics on float bit patterns.
+#include "common.cuh"
+
+namespace qwx {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr float kTinyScale = 0x1p-63f;  // sqrt(finfo.tiny) for float32 / bfloat16
+
+struct View {
+  int64_t P, R, C, tp, tr, tc;
+  int64_t GP, GR, GC;  // tile counts per axis
+  __host__ __device__ int64_t groups() const { return GP * GR * GC; }
+};
+
+struct CalibArgs {
+  int method;      // qwx_calibration
+  int has_arg;
+  float arg;       // already narrowed to float
+};
+
+enum class Out { kS8, kS4U, kS4P, kE4M3 };
+template <Out O> struct OutTraits;
+template <> struct OutTraits<Out::kS8> { using Q = S8; };
+template <> struct OutTraits<Out::kS4U> { using Q = S4; };
+template <> struct OutTraits<Out::kS4P> { using Q = S4; };
+template <> struct OutTraits<Out::kE4M3> { using Q = E4M3; };
+
+// ---- scalar recipes -------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ float apply_arg(float v, const CalibArgs& c) {
+  if (c.has_arg) v = round_to<T>(__fmul_rn(v, round_to<T>(c.arg)));
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float guard_scale(float s) {
+  // scale < sqrt(tiny) -> 1 (qarray.py:553-554, 561-562); NaN compares false and stays.
+  constexpr float thr = std::is_same<T, F16>::value ? 0.0078125f /*2^-7*/ : kTinyScale;
+  return (s < thr) ? 1.0f : s;
+}
+
+template <typename T, typename Q>
+__device__ __forceinline__ float symmetric_scale(float absmax) {
+  return guard_scale<T>(round_to<T>(__fdiv_rn(absmax, sym_bound<Q>())));
+}
+
+template <typename T, typename Q>
+__device__ __forceinline__ void asymmetric_scale(float lo, float hi, float& s, int& zp) {
+  if constexpr (Q::kFloat) {
+    s = 1.f; zp = 0;  // floating codes have no asymmetric form (numerics.py:64-92)
+    return;
+  } else {
+  constexpr float qmin = (float)Q::kLo, qmax = (float)Q::kHi;
+  float range = round_to<T>(__fsub_rn(hi, lo));
+  s = guard_scale<T>(round_to<T>(__fdiv_rn(range, round_to<T>(qmax - qmin))));
+  float z = round_to<T>(__fsub_rn(qmin, round_to<T>(__fdiv_rn(lo, s))));
+  zp = to_code<Q>(z);
+  }
+}
+
+template <typename T, typename Q>
+__device__ __forceinline__ int quantize_one(float x, float s, float zp, bool has_zp, bool strict) {
+  float y = __fdiv_rn(x, s);
+  if (strict) y = round_to<T>(y);
+  if (has_zp) {
+    y = __fadd_rn(y, zp);
+    if (strict) y = round_to<T>(y);
+  }
+  return to_code<Q>(y);
+}
+
+template <Out O>
+__device__ __forceinline__ void store_codes8(void* q, int64_t i, const int (&c)[8]) {
+  if constexpr (O == Out::kS4P) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w |= (uint32_t)(c[j] & 0xf) << (4 * j);
+    reinterpret_cast<uint32_t*>(q)[i >> 3] = w;
+  } else {
+    uint2 w;
+    w.x = (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)(c[3] & 0xff) << 24);
+    w.y = (c[4] & 0xff) | ((c[5] & 0xff) << 8) | ((c[6] & 0xff) << 16) | ((uint32_t)(c[7] & 0xff) << 24);
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(q) + i) = w;
+  }
+}
+
+template <Out O>
+__device__ __forceinline__ void store_code1(void* q, int64_t i, int c) {
+  if constexpr (O == Out::kS4P) {
+    // Two neighbours share a byte; only used on the scalar fallback where one thread owns
+    // both nibbles of a byte (caller guarantees i is even and passes the pair separately).
+    uint8_t* b = reinterpret_cast<uint8_t*>(q) + (i >> 1);
+    if (i & 1) *b = (uint8_t)((*b & 0x0f) | ((c & 0xf) << 4));
+    else *b = (uint8_t)((*b & 0xf0) | (c & 0xf));
+  } else {
+    reinterpret_cast<int8_t*>(q)[i] = (int8_t)c;
+  }
+}
+
+// ---- one-pass kernel for tiles that are row segments (tp = tr = 1) ------------------------
+//
+// G threads own one segment of `tc` contiguous elements: load it once into registers
+// (up to kCache vectors per thread; longer segments are re-read and mostly hit L2),
+// reduce, derive the scale, quantize from registers.  G = 32: one warp per segment,
+// G = 256: one CTA per segment.
+
+constexpr int kCache = 4;
+
+template <typename T, Out O, int G>
+__global__ void __launch_bounds__(kThreads)
+quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, CalibArgs cal,
+                     int rounding, void* __restrict__ q, void* __restrict__ scale,
+                     int8_t* __restrict__ zero_point) {
+  using Q = typename OutTraits<O>::Q;
+  constexpr int kSegs = kThreads / G;
+  __shared__ float red[2][kThreads / 32];
+  const int lane_in_group = threadIdx.x % G;
+  const int64_t seg = (int64_t)blockIdx.x * kSegs + threadIdx.x / G;
+  const bool live = seg < segments;
+  const int64_t base = seg * tc;
+  const int64_t nvec = tc >> 3;
+  const bool strict = rounding == QWX_STRICT;
+
+  uint4 cache[kCache];
+  uint32_t amax_bits = 0;
+  float lo = 0.f, hi = 0.f, sumsq = 0.f;
+
+  auto accumulate = [&](const float (&v)[8]) {
+    if (cal.method == QWX_ABSMAX) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax_bits = max(amax_bits, __float_as_uint(v[j]) & 0x7fffffffu);
+    } else if (cal.method == QWX_MINMAX) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { lo = fminf(lo, v[j]); hi = fmaxf(hi, v[j]); }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sumsq += round_to<T>(__fmul_rn(v[j], v[j]));
+    }
+  };
+
+  if (live) {
+#pragma unroll
+    for (int it = 0; it < kCache; ++it) {
+      int64_t vi = lane_in_group + (int64_t)it * G;
+      if (vi < nvec) {
+        float v[8];
+        if constexpr (T::kBytes == 2) {
+          cache[it] = *reinterpret_cast<const uint4*>(
+              reinterpret_cast<const uint16_t*>(x) + base + vi * 8);
+          if constexpr (std::is_same<T, BF16>::value) unpack_bf16x8(cache[it], v);
+          else load8<T>(x, base + vi * 8, v);
+        } else {
+          load8<T>(x, base + vi * 8, v);
+        }
+        accumulate(v);
+      }
+    }
+    for (int64_t vi = lane_in_group + (int64_t)kCache * G; vi < nvec; vi += G) {
+      float v[8];
+      load8<T>(x, base + vi * 8, v);
+      accumulate(v);
+    }
+  }
+
+  // Reduce across the G threads of the segment.
+  float r0, r1;
+  if (cal.method == QWX_ABSMAX) { r0 = __uint_as_float(amax_bits); r1 = 0.f; }
+  else if (cal.method == QWX_MINMAX) { r0 = fabsf(lo); r1 = hi; }
+  else { r0 = sumsq; r1 = 0.f; }
+  if (cal.method == QWX_RMS) {
+    r0 = warp_sum(r0);
+  } else {
+    // max over non-negative floats == max over their bit patterns (NaN sorts last).
+    uint32_t b0 = __float_as_uint(r0), b1 = __float_as_uint(r1);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      b0 = max(b0, __shfl_xor_sync(0xffffffffu, b0, o));
+      b1 = max(b1, __shfl_xor_sync(0xffffffffu, b1, o));
+    }
+    r0 = __uint_as_float(b0); r1 = __uint_as_float(b1);
+  }
+  if constexpr (G > 32) {
+    const int w = threadIdx.x / 32;
+    if ((threadIdx.x & 31) == 0) { red[0][w] = r0; red[1][w] = r1; }
+    __syncthreads();
+    float a0 = red[0][0], a1 = red[1][0];
+#pragma unroll
+    for (int i = 1; i < kThreads / 32; ++i) {
+      if (cal.method == QWX_RMS) a0 += red[0][i];
+      else {
+        a0 = __uint_as_float(max(__float_as_uint(a0), __float_as_uint(red[0][i])));
+        a1 = __uint_as_float(max(__float_as_uint(a1), __float_as_uint(red[1][i])));
+      }
+    }
+    r0 = a0; r1 = a1;
+  }
+  if (!live) return;
+
+  float s, zpf = 0.f;
+  bool has_zp = false;
+  if (cal.method == QWX_MINMAX) {
+    float mn = apply_arg<T>(-r0, cal), mx = apply_arg<T>(r1, cal);
+    int zp;
+    asymmetric_scale<T, Q>(mn, mx, s, zp);
+    zpf = (float)zp; has_zp = true;
+    if (lane_in_group == 0 && zero_point) zero_point[seg] = (int8_t)zp;
+  } else {
+    float a = r0;
+    if (cal.method == QWX_RMS) {
+      float mean = round_to<T>(__fdiv_rn(r0, (float)tc));
+      a = round_to<T>(__fsqrt_rn(mean));
+      a = round_to<T>(__fmul_rn(a, round_to<T>(cal.arg)));
+    } else {
+      a = apply_arg<T>(a, cal);
+    }
+    s = symmetric_scale<T, Q>(a);
+  }
+  if (lane_in_group == 0) store1<T>(scale, seg, s);
+
+  auto emit = [&](const float (&v)[8], int64_t vi) {
+    int c[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) c[j] = quantize_one<T, Q>(v[j], s, zpf, has_zp, strict);
+    store_codes8<O>(q, base + vi * 8, c);
+  };
+#pragma unroll
+  for (int it = 0; it < kCache; ++it) {
+    int64_t vi = lane_in_group + (int64_t)it * G;
+    if (vi < nvec) {
+      float v[8];
+      if constexpr (std::is_same<T, BF16>::value) unpack_bf16x8(cache[it], v);
+      else load8<T>(x, base + vi * 8, v);
+      emit(v, vi);
+    }
+  }
+  for (int64_t vi = lane_in_group + (int64_t)kCache * G; vi < nvec; vi += G) {
+    float v[8];
+    load8<T>(x, base + vi * 8, v);
+    emit(v, vi);
+  }
+}
+
+// ---- general tiled view: statistics by atomics, then an elementwise pass --------------------
+//
+// A CTA covers kChunkRows rows x 256 columns inside one row tile.  Each lane owns eight
+// adjacent columns and walks down the rows, so global loads are 128-bit and coalesced.
+// Column groups inside the CTA reduce through shared-memory atomics, then one global atomic
+// per (CTA, column group).  Statistics are kept as int32 bit patterns of non-negative
+// floats: slot 0 = absmax, -min or sum of squares, slot 1 = max.
+
+constexpr int kChunkRows = 128;
+constexpr int kChunkCols = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+calibrate_tiles_kernel(const void* __restrict__ x, View vw, int method, int vec_ok,
+                       int* __restrict__ stats) {
+  __shared__ int sh[2][kChunkCols + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t chunks_per_tile = (vw.tr + kChunkRows - 1) / kChunkRows;
+  const int64_t row_tile = blockIdx.y / chunks_per_tile;
+  const int64_t chunk = blockIdx.y % chunks_per_tile;
+  const int64_t r_begin = row_tile * vw.tr + chunk * kChunkRows;
+  const int64_t r_end = min(r_begin + kChunkRows, (row_tile + 1) * vw.tr);
+  const int64_t p = blockIdx.z;
+  const int64_t c0 = (int64_t)blockIdx.x * kChunkCols;
+  const int64_t col = c0 + lane * 8;
+
+  for (int i = threadIdx.x; i < 2 * (kChunkCols + 1); i += kThreads) (&sh[0][0])[i] = 0;
+  __syncthreads();
+
+  uint32_t a[8];
+  float lo[8], hi[8], sq[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { a[j] = 0; lo[j] = 0.f; hi[j] = 0.f; sq[j] = 0.f; }
+
+  if (col < vw.C) {
+    for (int64_t r = r_begin + warp; r < r_end; r += kThreads / 32) {
+      const int64_t off = (p * vw.R + r) * vw.C + col;
+      float v[8];
+      if (vec_ok) {
+        load8<T>(x, off, v);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (col + j < vw.C) ? load1<T>(x, off + j) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (method == QWX_ABSMAX) a[j] = max(a[j], __float_as_uint(v[j]) & 0x7fffffffu);
+        else if (method == QWX_MINMAX) { lo[j] = fminf(lo[j], v[j]); hi[j] = fmaxf(hi[j], v[j]); }
+        else sq[j] += round_to<T>(__fmul_rn(v[j], v[j]));
+      }
+    }
+    const int64_t first_group = c0 / vw.tc;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (col + j >= vw.C) break;
+      const int slot = (int)((col + j) / vw.tc - first_group);
+      if (method == QWX_ABSMAX) atomicMax(&sh[0][slot], (int)a[j]);
+      else if (method == QWX_MINMAX) {
+        atomicMax(&sh[0][slot], __float_as_int(fabsf(lo[j])));
+        atomicMax(&sh[1][slot], __float_as_int(hi[j]));
+      } else atomicAdd(reinterpret_cast<float*>(&sh[0][slot]), sq[j]);
+    }
+  }
+  __syncthreads();
+  const int64_t first_group = c0 / vw.tc;
+  const int64_t last_col = min(c0 + kChunkCols, vw.C) - 1;
+  const int nslots = (int)(last_col / vw.tc - first_group) + 1;
+  for (int s = threadIdx.x; s < nslots; s += kThreads) {
+    const int64_t g = ((p / vw.tp) * vw.GR + row_tile) * vw.GC + first_group + s;
+    if (method == QWX_RMS) atomicAdd(reinterpret_cast<float*>(&stats[2 * g]), __int_as_float(sh[0][s]));
+    else {
+      atomicMax(&stats[2 * g], sh[0][s]);
+      if (method == QWX_MINMAX) atomicMax(&stats[2 * g + 1], sh[1][s]);
+    }
+  }
+}
+
+// stats -> calibration values in the array dtype (what qarray.calibrate returns).
+template <typename T>
+__global__ void finish_calibration_kernel(const int* __restrict__ stats, int64_t groups,
+                                          int64_t tile_elems, CalibArgs cal,
+                                          void* __restrict__ out_a, void* __restrict__ out_b) {
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= groups) return;
+  float r0 = __int_as_float(stats[2 * g]), r1 = __int_as_float(stats[2 * g + 1]);
+  if (cal.method == QWX_MINMAX) {
+    store1<T>(out_a, g, apply_arg<T>(-r0, cal));
+    store1<T>(out_b, g, apply_arg<T>(r1, cal));
+  } else if (cal.method == QWX_RMS) {
+    float mean = round_to<T>(__fdiv_rn(r0, (float)tile_elems));
+    float a = round_to<T>(__fsqrt_rn(mean));
+    store1<T>(out_a, g, round_to<T>(__fmul_rn(a, round_to<T>(cal.arg))));
+  } else {
+    store1<T>(out_a, g, apply_arg<T>(r0, cal));
+  }
+}
+
+template <typename T, typename Q>
+__global__ void scale_zero_point_kernel(const void* __restrict__ ca, const void* __restrict__ cb,
+                                        int64_t n, void* __restrict__ scale,
+                                        int8_t* __restrict__ zero_point) {
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= n) return;
+  if (cb == nullptr) {
+    store1<T>(scale, g, symmetric_scale<T, Q>(load1<T>(ca, g)));
+  } else {
+    float s; int zp;
+    asymmetric_scale<T, Q>(load1<T>(ca, g), load1<T>(cb, g), s, zp);
+    store1<T>(scale, g, s);
+    zero_point[g] = (int8_t)zp;
+  }
+}
+
+// Elementwise quantize with generic broadcast of scale / zero point over the tiles.
+template <typename T, Out O>
+__global__ void __launch_bounds__(kThreads)
+apply_scale_kernel(const void* __restrict__ x, View vw, const void* __restrict__ scale,
+                   const int8_t* __restrict__ zero_point, int rounding, int vec_ok,
+                   void* __restrict__ q) {
+  using Q = typename OutTraits<O>::Q;
+  const int64_t vec_per_row = (vw.C + 7) >> 3;
+  const int64_t total = vw.P * vw.R * vec_per_row;
+  const bool strict = rounding == QWX_STRICT;
+  const bool has_zp = zero_point != nullptr;
+  for (int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x; t < total;
+       t += (int64_t)gridDim.x * kThreads) {
+    const int64_t row = t / vec_per_row;          // p * R + r
+    const int64_t col = (t - row * vec_per_row) << 3;
+    const int64_t p = row / vw.R, r = row - p * vw.R;
+    const int64_t gbase = ((p / vw.tp) * vw.GR + r / vw.tr) * vw.GC;
+    const int64_t off = row * vw.C + col;
+    float v[8];
+    int c[8];
+    if (vec_ok) {
+      load8<T>(x, off, v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (col + j < vw.C) ? load1<T>(x, off + j) : 0.f;
+    }
+    const int64_t g0 = gbase + col / vw.tc;
+    const int64_t g7 = gbase + min(col + 7, vw.C - 1) / vw.tc;
+    if (g0 == g7) {
+      const float s = load1<T>(scale, g0);
+      const float z = has_zp ? (float)zero_point[g0] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = quantize_one<T, Q>(v[j], s, z, has_zp, strict);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int64_t g = gbase + min(col + j, vw.C - 1) / vw.tc;
+        const float s = load1<T>(scale, g);
+        const float z = has_zp ? (float)zero_point[g] : 0.f;
+        c[j] = quantize_one<T, Q>(v[j], s, z, has_zp, strict);
+      }
+    }
+    if (vec_ok) {
+      store_codes8<O>(q, off, c);
+    } else {
+      if constexpr (O == Out::kS4P) {
+        // C is even for packed int4 (checked on the host): pairs never straddle rows.
+        for (int j = 0; j < 8 && col + j < vw.C; j += 2)
+          reinterpret_cast<uint8_t*>(q)[(off + j) >> 1] = (uint8_t)((c[j] & 0xf) | ((c[j + 1] & 0xf) << 4));
+      } else {
+        for (int j = 0; j < 8 && col + j < vw.C; ++j) store_code1<O>(q, off + j, c[j]);
+      }
+    }
+  }
+}
+
+// (q - zero_point) * scale in the scale dtype S, generic broadcast (qarray.py:692-708).
+template <typename S, Out O>
+__global__ void __launch_bounds__(kThreads)
+dequantize_kernel(const void* __restrict__ q, View vw, const void* __restrict__ scale,
+                  const int8_t* __restrict__ zero_point, int vec_ok, void* __restrict__ out) {
+  const int64_t vec_per_row = (vw.C + 7) >> 3;
+  const int64_t total = vw.P * vw.R * vec_per_row;
+  const bool has_zp = zero_point != nullptr;
+  for (int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x; t < total;
+       t += (int64_t)gridDim.x * kThreads) {
+    const int64_t row = t / vec_per_row;
+    const int64_t col = (t - row * vec_per_row) << 3;
+    const int64_t p = row / vw.R, r = row - p * vw.R;
+    const int64_t gbase = ((p / vw.tp) * vw.GR + r / vw.tr) * vw.GC;
+    const int64_t off = row * vw.C + col;
+    float code[8], v[8];
+    const int nvalid = (int)min((int64_t)8, vw.C - col);
+    if constexpr (O == Out::kS4P) {
+      uint32_t w = 0;
+      if (vec_ok) w = reinterpret_cast<const uint32_t*>(q)[off >> 3];
+      else for (int j = 0; j < nvalid; j += 2)
+        w |= (uint32_t)reinterpret_cast<const uint8_t*>(q)[(off + j) >> 1] << (4 * j);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) code[j] = (float)(((int)(w << (28 - 4 * j))) >> 28);
+    } else {
+      uint8_t b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (vec_ok) *reinterpret_cast<uint2*>(b) =
+          *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(q) + off);
+      else for (int j = 0; j < nvalid; ++j) b[j] = reinterpret_cast<const uint8_t*>(q)[off + j];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        code[j] = (O == Out::kE4M3) ? e4m3_to_float(b[j]) : (float)(int8_t)b[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int64_t g = gbase + min(col + j, vw.C - 1) / vw.tc;
+      float cv = round_to<S>(code[j]);
+      if (has_zp) cv = round_to<S>(__fsub_rn(cv, (float)zero_point[g]));
+      v[j] = round_to<S>(__fmul_rn(cv, load1<S>(scale, g)));
+    }
+    if (vec_ok) store8<S>(out, off, v);
+    else for (int j = 0; j < nvalid; ++j) store1<S>(out, off + j, v[j]);
+  }
+}
+
+// [rows, cols] bytes -> [cols, rows] bytes through a padded shared tile.
+__global__ void __launch_bounds__(kThreads)
+transpose_bytes_kernel(const uint8_t* __restrict__ src, int64_t rows, int64_t cols,
+                       uint8_t* __restrict__ dst) {
+  __shared__ uint8_t tile[64][64 + 4];
+  const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
+  for (int i = threadIdx.x; i < 64 * 64; i += kThreads) {
+    const int r = i / 64, c = i % 64;
+    if (r0 + r < rows && c0 + c < cols) tile[r][c] = src[(r0 + r) * cols + c0 + c];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 64 * 64; i += kThreads) {
+    const int c = i / 64, r = i % 64;
+    if (r0 + r < rows && c0 + c < cols) dst[(c0 + c) * rows + r0 + r] = tile[r][c];
+  }
+}
+
+// ---- host-side dispatch ----------------------------------------------------------------------
+
+int make_view(int64_t P, int64_t R, int64_t C, int64_t tp, int64_t tr, int64_t tc, View* v) {
+  if (P <= 0 || R <= 0 || C <= 0 || tp <= 0 || tr <= 0 || tc <= 0) return QWX_ERR_SHAPE;
+  if (P % tp || R % tr || C % tc) return QWX_ERR_SHAPE;
+  *v = View{P, R, C, tp, tr, tc, P / tp, R / tr, C / tc};
+  return QWX_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int grid_for(int64_t items) {
+  int64_t blocks = (items + kThreads - 1) / kThreads;
+  const int64_t cap = 148 * 16;  // a few waves of resident CTAs per SM
+  return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+template <typename Fn>
+int dispatch_float(int dtype, Fn&& fn) {
+  switch (dtype) {
+    case QWX_F32: return fn(F32{});
+    case QWX_BF16: return fn(BF16{});
+    case QWX_F16: return fn(F16{});
+    default: return (int)QWX_ERR_DTYPE;
+  }
+}
+
+template <typename Fn>
+int dispatch_out(int qtype, Fn&& fn) {
+  switch (qtype) {
+    case QWX_S8: return fn(std::integral_constant<Out, Out::kS8>{});
+    case QWX_S4U: return fn(std::integral_constant<Out, Out::kS4U>{});
+    case QWX_S4: return fn(std::integral_constant<Out, Out::kS4P>{});
+    case QWX_E4M3: return fn(std::integral_constant<Out, Out::kE4M3>{});
+    default: return (int)QWX_ERR_DTYPE;
+  }
+}
+
+int check_method(int method, int has_arg, int qtype) {
+  if (method != QWX_ABSMAX && method != QWX_MINMAX && method != QWX_RMS) return QWX_ERR_UNSUPPORTED;
+  if (method == QWX_RMS && !has_arg) return QWX_ERR_SHAPE;
+  if (method == QWX_MINMAX && qtype == QWX_E4M3) return QWX_ERR_DTYPE;  // numerics.py:64-92
+  return QWX_OK;
+}
+
+int run_calibrate_tiles(const void* x, int x_dtype, const View& vw, const CalibArgs& cal,
+                        void* out_a, void* out_b, void* ws, size_t ws_bytes, cudaStream_t st) {
+  const size_t need = (size_t)vw.groups() * 2 * sizeof(int);
+  if (ws == nullptr || ws_bytes < need) return QWX_ERR_WORKSPACE;
+  if (cudaMemsetAsync(ws, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
+  const int64_t chunks = (vw.tr + kChunkRows - 1) / kChunkRows;
+  const int64_t gy = vw.GR * chunks;
+  if (gy > 65535 || vw.P > 65535) return QWX_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)((vw.C + kChunkCols - 1) / kChunkCols), (unsigned)gy, (unsigned)vw.P);
+  const int vec_ok = (vw.C % 8 == 0) && aligned16(x);
+  return dispatch_float(x_dtype, [&](auto t) {
+    using T = decltype(t);
+    calibrate_tiles_kernel<T><<<grid, kThreads, 0, st>>>(x, vw, cal.method, vec_ok, (int*)ws);
+    QWX_CHECK_LAUNCH();
+    finish_calibration_kernel<T><<<(unsigned)((vw.groups() + 255) / 256), 256, 0, st>>>(
+        (const int*)ws, vw.groups(), vw.tp * vw.tr * vw.tc, cal, out_a, out_b);
+    QWX_CHECK_LAUNCH();
+    return (int)QWX_OK;
+  });
+}
+
+int run_apply(const void* x, int x_dtype, const View& vw, const void* scale, const void* zp,
+              int qtype, int rounding, void* q, cudaStream_t st) {
+  if (qtype == QWX_S4 && (vw.C & 1)) return QWX_ERR_SHAPE;
+  const int vec_ok = (vw.C % 8 == 0) && aligned16(x) && aligned16(q);
+  const int64_t vecs = vw.P * vw.R * ((vw.C + 7) / 8);
+  return dispatch_float(x_dtype, [&](auto t) {
+    using T = decltype(t);
+    return dispatch_out(qtype, [&](auto o) {
+      apply_scale_kernel<T, decltype(o)::value><<<grid_for(vecs), kThreads, 0, st>>>(
+          x, vw, scale, (const int8_t*)zp, rounding, vec_ok, q);
+      QWX_CHECK_LAUNCH();
+      return (int)QWX_OK;
+    });
+  });
+}
+
+}  // namespace
+}  // namespace qwx
+
+using namespace qwx;
+
+extern "C" {
+
+size_t qwx_quantize_workspace_bytes(int64_t P, int64_t R, int64_t C, int64_t tp, int64_t tr,
+                                    int64_t tc) {
+  View vw;
+  if (make_view(P, R, C, tp, tr, tc, &vw) != QWX_OK) return 0;
+  // statistics (two int32 per tile) + calibration values for the fused entry point.
+  return (size_t)vw.groups() * (2 * sizeof(int) + 2 * sizeof(float)) + 256;
+}
+
+int qwx_calibrate(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, int64_t tp,
+                  int64_t tr, int64_t tc, int method, int has_arg, double arg, void* out_a,
+                  void* out_b, void* workspace, size_t workspace_bytes, qwx_stream_t stream) {
+  if (!x || !out_a) return QWX_ERR_NULL;
+  View vw;
+  int rc = make_view(P, R, C, tp, tr, tc, &vw);
+  if (rc) return rc;
+  rc = check_method(method, has_arg, QWX_S8);
+  if (rc) return rc;
+  if (method == QWX_MINMAX && !out_b) return QWX_ERR_NULL;
+  CalibArgs cal{method, has_arg, (float)arg};
+  return run_calibrate_tiles(x, x_dtype, vw, cal, out_a, out_b, workspace, workspace_bytes,
+                             (cudaStream_t)stream);
+}
+
+int qwx_compute_scale_zero_point(const void* calib_a, const void* calib_b, int dtype, int64_t n,
+                                 int qtype, void* scale, void* zero_point, qwx_stream_t stream) {
+  if (!calib_a || !scale) return QWX_ERR_NULL;
+  if (calib_b && !zero_point) return QWX_ERR_NULL;
+  if (calib_b && qtype == QWX_E4M3) return QWX_ERR_DTYPE;
+  if (n <= 0) return QWX_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  return dispatch_float(dtype, [&](auto t) {
+    using T = decltype(t);
+    switch (qtype) {
+      case QWX_S8:
+        scale_zero_point_kernel<T, S8><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
+        break;
+      case QWX_S4: case QWX_S4U:
+        scale_zero_point_kernel<T, S4><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
+        break;
+      case QWX_E4M3:
+        scale_zero_point_kernel<T, E4M3><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
+        break;
+      default: return (int)QWX_ERR_DTYPE;
+    }
+    QWX_CHECK_LAUNCH();
+    return (int)QWX_OK;
+  });
+}
+
+int qwx_quantize_with_scale(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C,
+                            int64_t tp, int64_t tr, int64_t tc, const void* scale,
+                            const void* zero_point, int qtype, int rounding, void* q,
+                            qwx_stream_t stream) {
+  if (!x || !scale || !q) return QWX_ERR_NULL;
+  if (zero_point && qtype == QWX_E4M3) return QWX_ERR_DTYPE;
+  View vw;
+  int rc = make_view(P, R, C, tp, tr, tc, &vw);
+  if (rc) return rc;
+  return run_apply(x, x_dtype, vw, scale, zero_point, qtype, rounding, q, (cudaStream_t)stream);
+}
+
+int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, int64_t tp,
+                 int64_t tr, int64_t tc, int method, int has_arg, double arg, int qtype,
+                 int rounding, void* q, void* scale, void* zero_point, void* workspace,
+                 size_t workspace_bytes, qwx_stream_t stream) {
+  if (!x || !q || !scale) return QWX_ERR_NULL;
+  View vw;
+  int rc = make_view(P, R, C, tp, tr, tc, &vw);
+  if (rc) return rc;
+  rc = check_method(method, has_arg, qtype);
+  if (rc) return rc;
+  if (method == QWX_MINMAX && !zero_point) return QWX_ERR_NULL;
+  if (qtype == QWX_S4 && (C & 1)) return QWX_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  CalibArgs cal{method, has_arg, (float)arg};
+
+  // One pass when every tile is a contiguous row segment of whole 16-byte vectors.
+  if (tp == 1 && tr == 1 && tc % 8 == 0 && aligned16(x) && aligned16(q)) {
+    const int64_t segments = P * R * (C / tc);
+    return dispatch_float(x_dtype, [&](auto t) {
+      using T = decltype(t);
+      return dispatch_out(qtype, [&](auto o) {
+        constexpr Out O = decltype(o)::value;
+        if (tc <= 32 * 8 * kCache) {
+          const int64_t blocks = (segments + 7) / 8;
+          quantize_rows_kernel<T, O, 32><<<(unsigned)blocks, kThreads, 0, st>>>(
+              x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);
+        } else {
+          quantize_rows_kernel<T, O, 256><<<(unsigned)segments, kThreads, 0, st>>>(
+              x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);
+        }
+        QWX_CHECK_LAUNCH();
+        return (int)QWX_OK;
+      });
+    });
+  }
+
+  // General view: statistics -> calibration -> scale -> elementwise pass.
+  const size_t stats_bytes = (size_t)vw.groups() * 2 * sizeof(int);
+  const size_t need = stats_bytes + (size_t)vw.groups() * 2 * sizeof(float);
+  if (!workspace || workspace_bytes < need) return QWX_ERR_WORKSPACE;
+  char* ws = (char*)workspace;
+  void* calib_a = ws + stats_bytes;
+  void* calib_b = ws + stats_bytes + (size_t)vw.groups() * sizeof(float);
+  rc = run_calibrate_tiles(x, x_dtype, vw, cal, calib_a, calib_b, ws, stats_bytes, st);
+  if (rc) return rc;
+  rc = qwx_compute_scale_zero_point(calib_a, method == QWX_MINMAX ? calib_b : nullptr, x_dtype,
+                                    vw.groups(), qtype, scale, zero_point, stream);
+  if (rc) return rc;
+  return run_apply(x, x_dtype, vw, scale, method == QWX_MINMAX ? zero_point : nullptr, qtype,
+                   rounding, q, st);
+}
+
+int qwx_dequantize(const void* q, int qtype, int64_t P, int64_t R, int64_t C, int64_t tp,
+                   int64_t tr, int64_t tc, const void* scale, int scale_dtype,
+                   const void* zero_point, void* out, qwx_stream_t stream) {
+  if (!q || !scale || !out) return QWX_ERR_NULL;
+  View vw;
+  int rc = make_view(P, R, C, tp, tr, tc, &vw);
+  if (rc) return rc;
+  if (qtype == QWX_S4 && (C & 1)) return QWX_ERR_SHAPE;
+  const int vec_ok = (C % 8 == 0) && aligned16(out) &&
+                     ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+  const int64_t vecs = P * R * ((C + 7) / 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  return dispatch_float(scale_dtype, [&](auto s) {
+    using S = decltype(s);
+    return dispatch_out(qtype, [&](auto o) {
+      dequantize_kernel<S, decltype(o)::value><<<grid_for(vecs), kThreads, 0, st>>>(
+          q, vw, scale, (const int8_t*)zero_point, vec_ok, out);
+      QWX_CHECK_LAUNCH();
+      return (int)QWX_OK;
+    });
+  });
+}
+
+int qwx_transpose_codes(const void* src, int64_t rows, int64_t cols, void* dst,
+                        qwx_stream_t stream) {
+  if (!src || !dst) return QWX_ERR_NULL;
+  if (rows <= 0 || cols <= 0) return QWX_ERR_SHAPE;
+  dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
+  if (grid.y > 65535) return QWX_ERR_UNSUPPORTED;
+  transpose_bytes_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)src, rows, cols, (uint8_t*)dst);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,94 @@
+"""GPU parity: tcgen05 quantized GEMM (through the C ABI) vs the CPU oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import dot_general as odg
+from oracle import qarray as oq
+from qwix_b200 import _lib
+from qwix_b200.core import dot_general as bdg
+from qwix_b200.core import qarray as bq
+from tests import helpers as h
+
+pytestmark = pytest.mark.gpu
+
+DN = (((1,), (0,)), ((), ()))
+
+
+def _raw_gemm(a: torch.Tensor, b: torch.Tensor, layout: int, code=_lib.S8, out_dtype=torch.int32):
+  M, K = a.shape
+  N = b.shape[1] if layout == _lib.B_KN else b.shape[0]
+  out = torch.empty((M, N), dtype=out_dtype, device='cuda')
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  oc = {torch.int32: _lib.S32, torch.float32: _lib.F32}[out_dtype]
+  _lib.check(_lib.lib().qwx_gemm_q8(_lib.ptr(a), _lib.ptr(b), code, layout, M, N, K, 0, None, 0,
+                                    None, 0, _lib.F32, _lib.ptr(out), oc, 0, _lib.ptr(err),
+                                    _lib.stream_ptr()), 'gemm')
+  torch.cuda.synchronize()
+  assert int(err.item()) == 0
+  return out
+
+
+SHAPES = [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (384, 768, 4096),
+          (100, 200 + 8, 256 + 16), (1, 16, 128), (130, 272, 144), (512, 1024, 8192)]
+
+
+@pytest.mark.parametrize('layout', [_lib.B_NK, _lib.B_KN], ids=['b_nk', 'b_kn'])
+@pytest.mark.parametrize('mnk', SHAPES, ids=[f'{m}x{n}x{k}' for m, n, k in SHAPES])
+def test_int8_accumulator_bit_exact(mnk, layout):
+  M, N, K = mnk
+  rng = np.random.default_rng(M + N + K)
+  a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+  b = rng.integers(-128, 128, (K, N), dtype=np.int8)
+  want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.int64)
+  bt = h.to_torch(b if layout == _lib.B_KN else np.ascontiguousarray(b.T))
+  got = _raw_gemm(h.to_torch(a), bt, layout).cpu().numpy().astype(np.int64)
+  bad = np.argwhere(got != want)
+  assert bad.size == 0, f'{len(bad)} mismatches, first {bad[:5].tolist()}'
+
+
+@pytest.mark.parametrize('layout', [_lib.B_NK, _lib.B_KN], ids=['b_nk', 'b_kn'])
+def test_fp8_accumulator(layout):
+  M, N, K = 256, 512, 1024
+  rng = np.random.default_rng(0)
+  import ml_dtypes
+  a = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+  b = rng.standard_normal((K, N)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+  want = a.astype(np.float32) @ b.astype(np.float32)
+  bt = h.to_torch(b if layout == _lib.B_KN else np.ascontiguousarray(b.T))
+  got = _raw_gemm(h.to_torch(a), bt, layout, code=_lib.E4M3, out_dtype=torch.float32).cpu().numpy()
+  assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
+
+
+@pytest.mark.parametrize('dtype', ['float32', 'bfloat16'])
+@pytest.mark.parametrize('qtype', ['int8', 'float8_e4m3fn'])
+def test_w8a8_dot_general_matches_oracle(qtype, dtype):
+  M, K, N = 192, 1024, 512
+  rng = np.random.default_rng(1)
+  x = rng.standard_normal((M, K)).astype(np.float32)
+  x[:, rng.choice(K, 10, replace=False)] *= 20
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32)
+  x, w = x.astype(h.np_dtype(dtype)), w.astype(h.np_dtype(dtype))
+  kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=None, qtype=qtype)
+  xo = oq.quantize(x, odg.get_how_to_quantize(for_lhs=True, **kw))
+  wo = oq.quantize(w, odg.get_how_to_quantize(for_lhs=False, **kw))
+  want = odg.dot_general(xo, wo, DN)
+  xq = bq.quantize(h.to_torch(x), bdg.get_how_to_quantize(for_lhs=True, **kw))
+  wq = bq.quantize(h.to_torch(w), bdg.get_how_to_quantize(for_lhs=False, **kw))
+  assert h.codes_equal(xq.qvalue, xo.qvalue) and h.codes_equal(wq.qvalue, wo.qvalue)
+  got = bdg.dot_general(xq, wq, DN)
+  assert got.dtype == h.to_torch(want[:1]).dtype
+  g = h.to_numpy(got).astype(np.float32)
+  r = want.astype(np.float32)
+  # BASELINE tolerance for dequantized outputs: max-abs 1e-2 or rel 2e-2.
+  assert np.all(np.abs(g - r) <= 1e-2 + 2e-2 * np.abs(r))
+  if qtype == 'int8':
+    # Reference-order epilogue: bit-exact with the strict oracle.
+    old = bdg.EPILOGUE
+    try:
+      bdg.EPILOGUE = 'reference'
+      exact = bdg.dot_general(xq, wq, DN)
+    finally:
+      bdg.EPILOGUE = old
+    assert np.array_equal(h.to_numpy(exact).view(np.uint8), want.view(np.uint8))
