@@ -1,0 +1,369 @@
+"""Benchmark of the w8a8 quantized dot_general hot path (BASELINE.json configs[1]).
+
+One step = what PtqProvider.dot_general does for one Dense layer at inference time:
+  quantize the bf16 activations A[4096, 8192] per token to int8 (absmax), then
+  int8 x int8 -> int32 GEMM against the pre-quantized weight W[8192, 8192] (int8, one
+  scale per output channel) with both scales applied in the epilogue, bf16 output.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Under torchrun every rank runs the same step on its own token shard (weak scaling, no
+collective on the data path).  Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+  sys.path.insert(0, ROOT)
+
+M, K, N = 4096, 8192, 8192
+OPS_PER_STEP = 2 * M * N * K
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_q8_kernel launch at this size,
+# from the ncu capture summarised in profiles/gemm_q8_w8a8_prefill.md (None until captured).
+GEMM_DRAM_TRAFFIC_BYTES = None
+NSETS = 3  # buffer sets cycled through so that no step finds its inputs in the 126 MB L2
+
+
+def _peaks():
+  path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+  if os.path.exists(path):
+    with open(path) as f:
+      p = json.load(f)
+    return {'bf16_sustained': p['bf16_tflops_sustained'], 'bf16_burst': p['bf16_tflops'],
+            'hbm_gbs': p['hbm_gbs'], 'source': 'measured'}
+  return {'bf16_sustained': 1400.0, 'bf16_burst': 1590.0, 'hbm_gbs': 6650.0,
+          'source': 'fallback'}
+
+
+class ClockSampler:
+  """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+  FIELDS = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,'
+            'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+            'clocks_event_reasons.sw_power_cap')
+
+  def __init__(self, index: int):
+    self.index, self.rows, self.proc = index, [], None
+
+  def start(self):
+    try:
+      self.proc = subprocess.Popen(
+          ['nvidia-smi', f'--id={self.index}', f'--query-gpu={self.FIELDS}',
+           '--format=csv,noheader,nounits', '-lms', '100'],
+          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+      self.thread = threading.Thread(target=self._read, daemon=True)
+      self.thread.start()
+    except OSError:
+      self.proc = None
+
+  def _read(self):
+    for line in self.proc.stdout:
+      self.rows.append([c.strip() for c in line.split(',')])
+
+  def stop(self) -> dict:
+    if self.proc is None:
+      return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=2)
+    except subprocess.TimeoutExpired:
+      self.proc.kill()
+    self.thread.join(timeout=2)
+    sm, mx, reasons = [], [], set()
+    names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
+    for r in self.rows:
+      if len(r) < 6:
+        continue
+      try:
+        sm.append(float(r[0]))
+        mx.append(float(r[1]))
+      except ValueError:
+        continue
+      for n, v in zip(names, r[2:6]):
+        if v.lower().startswith('active'):
+          reasons.add(n)
+    return {'sm_mhz': statistics.median(sm) if sm else None,
+            'sm_max_mhz': max(mx) if mx else None, 'reasons': sorted(reasons),
+            'samples': len(sm)}
+
+
+def _inputs(seed_base: int, device):
+  """BASELINE configs[1]: A ~ N(0,1) with 1% of the K columns scaled x20, W ~ N(0, 0.02)."""
+  sets = []
+  for s in range(NSETS):
+    g = torch.Generator(device='cpu').manual_seed(seed_base + s)
+    a = torch.randn(M, K, generator=g, dtype=torch.float32)
+    cols = torch.randperm(K, generator=g)[:K // 100]
+    a[:, cols] *= 20.0
+    w = torch.randn(K, N, generator=g, dtype=torch.float32) * 0.02
+    sets.append((a.to(torch.bfloat16), w.to(torch.bfloat16)))
+  return sets
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference path, timed on the host cores.
+# ---------------------------------------------------------------------------------------------
+
+def cpu_step_factory(rows: int):
+  """Returns (fn, ops): one w8a8 step on `rows` of the workload's tokens, full K and N."""
+  import ml_dtypes
+  from oracle import dot_general as odg
+  from oracle import qarray as oq
+  rng = np.random.default_rng(0)
+  a = rng.standard_normal((rows, K)).astype(np.float32)
+  a[:, rng.choice(K, K // 100, replace=False)] *= 20.0
+  a = a.astype(ml_dtypes.bfloat16)
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32).astype(ml_dtypes.bfloat16)
+  dn = (((1,), (0,)), ((), ()))
+  kw = dict(dimension_numbers=dn, ndims=(2, 2), tile_size=None, qtype='int8')
+  wq = oq.quantize(w, odg.get_how_to_quantize(for_lhs=False, **kw))  # offline, untimed
+  how_a = odg.get_how_to_quantize(for_lhs=True, **kw)
+
+  def step():
+    return odg.dot_general(oq.quantize(a, how_a), wq, dn)
+
+  return step, 2 * rows * N * K
+
+
+def run_cpu(steps: int, warmup: int, rows: int):
+  threads = os.cpu_count() or 1
+  torch.set_num_threads(threads)
+  step, ops = cpu_step_factory(rows)
+  for _ in range(warmup):
+    step()
+  t0 = time.perf_counter()
+  for _ in range(steps):
+    step()
+  dt = (time.perf_counter() - t0) / steps
+  return ops / dt / 1e12, dt, threads
+
+
+def reference_arm(args, rank: int):
+  if rank != 0:
+    return
+  rows = 256
+  tops, dt, threads = run_cpu(max(1, args.steps), max(1, args.warmup), rows)
+  line = {
+      'impl': 'reference', 'metric': 'quantized GEMM TOPS', 'value': tops, 'unit': 'TOPS',
+      'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
+      'ms_per_step': dt * 1e3, 'higher_is_better': True, 'scaling': 'weak',
+      'vs_baseline': None, 'dtype': 'int8', 'data': 'synthetic',
+      'config': {'workload': 'w8a8 dot_general prefill, BASELINE configs[1]', 'M': M, 'N': N,
+                 'K': K, 'sample': f'{rows} of {M} token rows per step, full K and N'},
+      'cpu_baseline': {'value': tops, 'unit': 'TOPS', 'cores': threads, 'kind': 'port',
+                       'sample': f'{rows} of {M} token rows per step (NumPy/ml_dtypes oracle; '
+                                 'the reference needs jax, which is not installed)'},
+      'e2e': {'value': tops, 'unit': 'TOPS', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+      'gpu_launches': 0,
+  }
+  print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument('--gpus', type=int, default=1)
+  ap.add_argument('--steps', type=int, default=200)
+  ap.add_argument('--warmup', type=int, default=20)
+  ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+  ap.add_argument('--no-cpu-baseline', action='store_true')
+  ap.add_argument('--m', type=int, default=None,
+                  help='token rows per step (profiling aid; the benchmark uses 4096)')
+  args = ap.parse_args()
+  args.warmup = max(args.warmup, 3)
+  if args.m is not None:
+    global M, OPS_PER_STEP
+    M = args.m
+    OPS_PER_STEP = 2 * M * N * K
+
+  rank = int(os.environ.get('RANK', '0'))
+  world = int(os.environ.get('WORLD_SIZE', '1'))
+  local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+
+  if args.impl == 'reference':
+    reference_arm(args, rank)
+    return
+
+  if not torch.cuda.is_available():
+    raise SystemExit('bench.py needs a CUDA device: the quantized path has no CPU fallback.')
+  torch.cuda.set_device(local_rank)
+  device = torch.device('cuda', local_rank)
+  dist = None
+  if world > 1:
+    import torch.distributed as dist
+    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+    dist.init_process_group('nccl', device_id=device)
+
+  from qwix_b200 import _lib
+  from qwix_b200.core import dot_general as bdg
+  from qwix_b200.core import qarray as bq
+  import qwix_b200 as qwix
+
+  dn = (((1,), (0,)), ((), ()))
+  kw = dict(dimension_numbers=dn, ndims=(2, 2), tile_size=None, qtype='int8')
+  how_a = bdg.get_how_to_quantize(for_lhs=True, **kw)
+  how_w = bdg.get_how_to_quantize(for_lhs=False, **kw)
+
+  host_sets = _inputs(1000 * rank, device)
+  dev = []
+  for a_h, w_h in host_sets:
+    a = a_h.to(device)
+    wq = bq.quantize(w_h.to(device), how_w)  # offline weight quantization (quantize_params)
+    dev.append({
+        'a': a, 'wq': wq,
+        'aq': torch.empty((M, K), dtype=torch.int8, device=device),
+        'sa': torch.empty((M, 1), dtype=torch.bfloat16, device=device),
+        'out': torch.empty((M, N), dtype=torch.bfloat16, device=device),
+    })
+  err = torch.zeros(1, dtype=torch.int32, device=device)
+  L = _lib.lib()
+  stream = _lib.stream_ptr(device)
+
+  def quantize_act(d):
+    _lib.check(L.qwx_quantize(_lib.ptr(d['a']), _lib.BF16, 1, M, K, 1, 1, K, _lib.ABSMAX, 0, 0.0,
+                              _lib.S8, _lib.STRICT, _lib.ptr(d['aq']), _lib.ptr(d['sa']), None,
+                              None, 0, stream), 'quantize')
+
+  def gemm(d):
+    _lib.check(L.qwx_gemm_q8(_lib.ptr(d['aq']), _lib.ptr(d['wq'].qvalue), _lib.S8, _lib.B_KN,
+                             M, N, K, 0, _lib.ptr(d['sa']), 0, _lib.ptr(d['wq'].scale), 0,
+                             _lib.BF16, _lib.ptr(d['out']), _lib.BF16, _lib.EPI_F32,
+                             _lib.ptr(err), stream), 'gemm')
+
+  def step(i):
+    d = dev[i % NSETS]
+    quantize_act(d)
+    gemm(d)
+
+  def barrier():
+    if dist is not None:
+      dist.barrier()
+    torch.cuda.synchronize()
+
+  # ---- device-resident throughput (`value`) + per-kernel durations for the roofline ----
+  for i in range(args.warmup):
+    step(i)
+  barrier()
+  sampler = ClockSampler(local_rank)
+  sampler.start()
+  ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
+  barrier()
+  ev[0].record()
+  for i in range(args.steps):
+    d = dev[i % NSETS]
+    quantize_act(d)
+    ev[3 * i + 1].record()
+    gemm(d)
+    ev[3 * i + 2].record()
+    ev[3 * i + 3].record()
+  barrier()
+  clocks = sampler.stop()
+  total_ms = ev[0].elapsed_time(ev[3 * args.steps])
+  quant_ms = sum(ev[3 * i].elapsed_time(ev[3 * i + 1]) for i in range(args.steps)) / args.steps
+  gemm_ms = sum(ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(args.steps)) / args.steps
+  if int(err.item()) != 0:
+    raise SystemExit(f'device-side wait ran out inside the GEMM (code {int(err.item())})')
+
+  t = torch.tensor([total_ms], dtype=torch.float64, device=device)
+  if dist is not None:
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+  total_ms = float(t.item())
+  ms_per_step = total_ms / args.steps
+  value = world * OPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
+
+  # ---- end to end through the public plugin API, host buffers in, host buffers out ----
+  provider_rule = qwix.QuantizationRule(module_path='.*', weight_qtype='int8', act_qtype='int8')
+  provider = qwix.PtqProvider([provider_rule])
+  pinned_in = [a_h.pin_memory() for a_h, _ in host_sets]
+  pinned_out = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(NSETS)]
+  boxed = [qwix.WithAux(d['wq'], how_w) for d in dev]
+
+  def e2e_step(i):
+    s = i % NSETS
+    x = pinned_in[s].to(device, non_blocking=True)
+    y = provider.dot_general(x, boxed[s], dn)
+    pinned_out[s].copy_(y, non_blocking=True)
+
+  e2e_steps = max(3, min(args.steps, 30))
+  for i in range(3):
+    e2e_step(i)
+  barrier()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for i in range(e2e_steps):
+    e2e_step(i)
+  e1.record()
+  barrier()
+  t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+  if dist is not None:
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+  e2e_ms = float(t.item()) / e2e_steps
+  e2e_value = world * OPS_PER_STEP / (e2e_ms * 1e-3) / 1e12
+
+  if rank != 0:
+    if dist is not None:
+      dist.destroy_process_group()
+    return
+
+  peaks = _peaks()
+  # int8 tcgen05 issues at twice the bf16 rate; the int8 ceiling is taken as 2 x the
+  # driver-measured sustained bf16 GEMM figure (the kernel is timed inside a long loop).
+  peak_tops = 2.0 * peaks['bf16_sustained']
+  achieved = OPS_PER_STEP / (gemm_ms * 1e-3) / 1e12
+  line = {
+      'metric': 'quantized GEMM TOPS', 'value': value, 'unit': 'TOPS', 'n_gpus': world,
+      'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step,
+      'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'int8',
+      'data': 'synthetic',
+      'config': {
+          'workload': 'w8a8 dot_general prefill, BASELINE configs[1]: per-token int8 absmax '
+                      'quantize of A + int8 GEMM with fused per-token/per-channel dequant',
+          'M': M, 'N': N, 'K': K, 'per_gpu': 'every rank runs the full [M,K]x[K,N] step on '
+          'its own tokens',
+          'l2': f'{NSETS} input/weight/output sets ({NSETS * 224} MB) cycled; one set (224 MB) '
+                'exceeds the 126 MB L2',
+      },
+      'roofline': {
+          'bound': 'tensor', 'achieved': achieved, 'peak': peak_tops, 'unit': 'TOP/s',
+          'frac': achieved / peak_tops, 'traffic': GEMM_DRAM_TRAFFIC_BYTES,
+          'kernel': 'gemm_q8_kernel<i8>', 'kernel_ms': gemm_ms,
+          'peak_source': f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
+          'quantize_kernel_ms': quant_ms,
+          'quantize_gbs': (M * K * 3 + M * 2) / (quant_ms * 1e-3) / 1e9,
+          'hbm_peak_gbs': peaks['hbm_gbs'],
+      },
+      'e2e': {'value': e2e_value, 'unit': 'TOPS', 'h2d_bytes_per_step': M * K * 2,
+              'd2h_bytes_per_step': M * N * 2, 'ms_per_step': e2e_ms, 'steps': e2e_steps},
+      'gpu_launches': 2 * args.steps,
+      'clocks': clocks,
+  }
+  if world == 1 and not args.no_cpu_baseline:
+    rows = 256
+    tops, dt, threads = run_cpu(3, 1, rows)
+    line['cpu_baseline'] = {
+        'value': tops, 'unit': 'TOPS', 'cores': threads, 'kind': 'port',
+        'sample': f'{rows} of {M} token rows per step, full K and N, 3 timed steps '
+                  f'({dt * 1e3:.0f} ms each)'}
+  print(json.dumps(line), flush=True)
+  if dist is not None:
+    dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+  main()

@@ -133,6 +133,10 @@ template <typename Q> __device__ __forceinline__ int to_code(float y) {
     if (y != y) return 0x7f;
     y = fminf(fmaxf(y, -448.0f), 448.0f);
     return (int)__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
+  } else if constexpr (Q::kLo == -128) {
+    int q;  // one instruction: round-half-even, saturate to [-128, 127], NaN -> 0
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(y));
+    return q;
   } else {
     int q = __float2int_rn(y);  // saturates at int32 range, NaN -> 0
     return min(max(q, Q::kLo), Q::kHi);

@@ -65,9 +65,29 @@ __device__ __forceinline__ void asymmetric_scale(float lo, float hi, float& s, i
   }
 }
 
+// x / s as the reference computes it (true division).  For bfloat16 operands in strict mode
+// the bf16 rounding of the quotient is obtained from x * rcp(s) instead: x and s carry 8-bit
+// significands, so the exact quotient is never closer than 2^-17 (relative) to a bf16
+// rounding boundary and never on one, while x * rcp_rn(s) is within 2^-22 of it -- both round
+// to the same bf16 value.  Scales outside [2^-100, 2^100] take the division.
+template <typename T>
+struct Divider {
+  float s, r;
+  bool fast;
+  __device__ __forceinline__ Divider(float scale, bool strict) : s(scale) {
+    const float a = fabsf(scale);
+    fast = std::is_same<T, BF16>::value && strict && a > 0x1p-100f && a < 0x1p100f;
+    r = fast ? __frcp_rn(scale) : 0.f;
+  }
+  __device__ __forceinline__ float operator()(float x) const {
+    return fast ? __fmul_rn(x, r) : __fdiv_rn(x, s);
+  }
+};
+
 template <typename T, typename Q>
-__device__ __forceinline__ int quantize_one(float x, float s, float zp, bool has_zp, bool strict) {
-  float y = __fdiv_rn(x, s);
+__device__ __forceinline__ int quantize_one(float x, const Divider<T>& div, float zp, bool has_zp,
+                                            bool strict) {
+  float y = div(x);
   if (strict) y = round_to<T>(y);
   if (has_zp) {
     y = __fadd_rn(y, zp);
@@ -224,10 +244,11 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
   }
   if (lane_in_group == 0) store1<T>(scale, seg, s);
 
+  const Divider<T> div(s, strict);
   auto emit = [&](const float (&v)[8], int64_t vi) {
     int c[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) c[j] = quantize_one<T, Q>(v[j], s, zpf, has_zp, strict);
+    for (int j = 0; j < 8; ++j) c[j] = quantize_one<T, Q>(v[j], div, zpf, has_zp, strict);
     store_codes8<O>(q, base + vi * 8, c);
   };
 #pragma unroll
@@ -389,17 +410,17 @@ apply_scale_kernel(const void* __restrict__ x, View vw, const void* __restrict__
     const int64_t g0 = gbase + col / vw.tc;
     const int64_t g7 = gbase + min(col + 7, vw.C - 1) / vw.tc;
     if (g0 == g7) {
-      const float s = load1<T>(scale, g0);
+      const Divider<T> div(load1<T>(scale, g0), strict);
       const float z = has_zp ? (float)zero_point[g0] : 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) c[j] = quantize_one<T, Q>(v[j], s, z, has_zp, strict);
+      for (int j = 0; j < 8; ++j) c[j] = quantize_one<T, Q>(v[j], div, z, has_zp, strict);
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int64_t g = gbase + min(col + j, vw.C - 1) / vw.tc;
-        const float s = load1<T>(scale, g);
+        const Divider<T> div(load1<T>(scale, g), false);  // one use: plain division
         const float z = has_zp ? (float)zero_point[g] : 0.f;
-        c[j] = quantize_one<T, Q>(v[j], s, z, has_zp, strict);
+        c[j] = quantize_one<T, Q>(v[j], div, z, has_zp, strict);
       }
     }
     if (vec_ok) {
