@@ -126,6 +126,24 @@ int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_layout,
                 int scale_dtype, void* out, int out_dtype, int epilogue, int32_t* error_flag,
                 qwx_stream_t stream);
 
+/* Weight-only int4 GEMM, the fused form of dot_general._slow_dot_general
+ * (dot_general.py:264-275, chosen at :444-452 when the activation is not quantized):
+ *   out[m, n] = sum_k a[m, k] * bf16( q[k, n] * scale[k / k_tile, n] )
+ * a: bf16 [M, K], M <= 128.  The weight is given in the kernel's streaming layout, made once
+ * by qwx_pack_w4 from the logical codes q[K, N] (QWX_S4U, one code per byte): units of
+ * 128 channels x 128 K, 8 KB each, ordered [N / 128][K / 128].  scale: [K / k_tile, N] in f32
+ * or bf16 (f32 scales are rounded to bf16 before the product), k_tile a multiple of 128.
+ * K and N must be multiples of 128.  out: bf16 or f32 [M, N].
+ * workspace: qwx_gemm_a16w4_workspace_bytes(M, N) bytes that must be zero when the kernel
+ * starts; the kernel leaves them zero.  workspace_is_zero = 0 makes the call clear it first. */
+size_t qwx_w4_packed_bytes(int64_t K, int64_t N);
+int qwx_pack_w4(const void* q, int64_t K, int64_t N, void* packed, qwx_stream_t stream);
+size_t qwx_gemm_a16w4_workspace_bytes(int64_t M, int64_t N);
+int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int scale_dtype,
+                   int64_t M, int64_t N, int64_t K, int64_t k_tile, void* out, int out_dtype,
+                   void* workspace, size_t workspace_bytes, int workspace_is_zero,
+                   int32_t* error_flag, qwx_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -41,6 +41,11 @@ _SIGNATURES = {
     'qwx_quantize': (_int, [_vp, _int] + [_i64] * 6 + [_int, _int, _dbl, _int, _int, _vp, _vp, _vp, _vp, _sz, _vp]),
     'qwx_dequantize': (_int, [_vp, _int] + [_i64] * 6 + [_vp, _int, _vp, _vp, _vp]),
     'qwx_transpose_codes': (_int, [_vp, _i64, _i64, _vp, _vp]),
+    'qwx_w4_packed_bytes': (_sz, [_i64, _i64]),
+    'qwx_pack_w4': (_int, [_vp, _i64, _i64, _vp, _vp]),
+    'qwx_gemm_a16w4_workspace_bytes': (_sz, [_i64, _i64]),
+    'qwx_gemm_a16w4': (_int, [_vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _sz, _int,
+                              _vp, _vp]),
     'qwx_gemm_q8': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,
                            _int, _vp, _int, _int, _vp, _vp]),
 }

@@ -27,6 +27,10 @@ MIN_TILE_SIZE_TO_DEQUANT_ON_OUTPUT = 128
 # rounds to the result dtype in the reference's order (dot_general.py:255-261).
 EPILOGUE = 'f32'
 
+# Weight-only int4 contractions stream the packed weight through one fused kernel instead of
+# materialising the dequantized weight (same W~ = bf16(q * s) operand, float32 accumulation).
+FUSE_WEIGHT_ONLY = True
+
 
 def get_how_to_quantize(*, dimension_numbers, ndims: tuple[int, int], for_lhs: bool,
                         tile_size: Mapping[int, int | float] | int | float | None,
@@ -190,6 +194,11 @@ def _slow_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
                       **kwargs) -> torch.Tensor:
   """dot_general.py:264-275 -- dequantize the operands, then a floating-point dot."""
   del kwargs
+  from qwix_b200.core import weight_only
+  if FUSE_WEIGHT_ONLY and weight_only.eligible(lhs, rhs, dimension_numbers):
+    want = preferred_element_type or torch.promote_types(lhs.dtype, rhs.scale.dtype)
+    if want in (torch.bfloat16, torch.float32):
+      return weight_only.matmul(lhs, rhs, want)
   if isinstance(lhs, QArray):
     lhs = qarray.dequantize(lhs)
   if isinstance(rhs, QArray):

@@ -136,7 +136,7 @@ template <typename Q> __device__ __forceinline__ int to_code(float y) {
   } else if constexpr (Q::kLo == -128) {
     int q;  // one instruction: round-half-even, saturate to [-128, 127], NaN -> 0
     asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(y));
-    return q;
+    return (int)(signed char)q;
   } else {
     int q = __float2int_rn(y);  // saturates at int32 range, NaN -> 0
     return min(max(q, Q::kLo), Q::kHi);

@@ -152,6 +152,14 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
   uint32_t amax_bits = 0;
   float lo = 0.f, hi = 0.f, sumsq = 0.f;
 
+  // bfloat16 absmax on packed pairs: |x| and max are exact in bf16, NaN propagates.
+  __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.f, 0.f);
+  auto accumulate_packed = [&](const uint4& u) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      amax2 = __hmax2_nan(amax2, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[j])));
+  };
   auto accumulate = [&](const float (&v)[8]) {
     if (cal.method == QWX_ABSMAX) {
 #pragma unroll
@@ -174,8 +182,12 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
         if constexpr (T::kBytes == 2) {
           cache[it] = *reinterpret_cast<const uint4*>(
               reinterpret_cast<const uint16_t*>(x) + base + vi * 8);
-          if constexpr (std::is_same<T, BF16>::value) unpack_bf16x8(cache[it], v);
-          else load8<T>(x, base + vi * 8, v);
+          if constexpr (std::is_same<T, BF16>::value) {
+            if (cal.method == QWX_ABSMAX) { accumulate_packed(cache[it]); continue; }
+            unpack_bf16x8(cache[it], v);
+          } else {
+            load8<T>(x, base + vi * 8, v);
+          }
         } else {
           load8<T>(x, base + vi * 8, v);
         }
@@ -191,7 +203,11 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
 
   // Reduce across the G threads of the segment.
   float r0, r1;
-  if (cal.method == QWX_ABSMAX) { r0 = __uint_as_float(amax_bits); r1 = 0.f; }
+  if (cal.method == QWX_ABSMAX) {
+    const float2 packed = __bfloat1622float2(amax2);
+    amax_bits = max(amax_bits, max(__float_as_uint(packed.x), __float_as_uint(packed.y)));
+    r0 = __uint_as_float(amax_bits); r1 = 0.f;
+  }
   else if (cal.method == QWX_MINMAX) { r0 = fabsf(lo); r1 = hi; }
   else { r0 = sumsq; r1 = 0.f; }
   if (cal.method == QWX_RMS) {
@@ -245,6 +261,26 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
   if (lane_in_group == 0) store1<T>(scale, seg, s);
 
   const Divider<T> div(s, strict);
+  // bf16 -> int8, strict rounding, symmetric: x * rcp(s) -> round to bf16 -> round-half-even
+  // with saturation, two values per conversion/pack instruction where the ISA allows.
+  auto emit_packed = [&](const uint4& u, int64_t vi) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    int c[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float y0 = __fmul_rn(__uint_as_float(w[j] << 16), div.r);
+      const float y1 = __fmul_rn(__uint_as_float(w[j] & 0xffff0000u), div.r);
+      const __nv_bfloat162 b = __floats2bfloat162_rn(y0, y1);
+      const uint32_t bw = *reinterpret_cast<const uint32_t*>(&b);
+      c[2 * j] = to_code<S8>(__uint_as_float(bw << 16));
+      c[2 * j + 1] = to_code<S8>(__uint_as_float(bw & 0xffff0000u));
+    }
+    uint2 o;
+    o.x = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
+    o.y = __byte_perm(__byte_perm(c[4], c[5], 0x0040), __byte_perm(c[6], c[7], 0x0040), 0x5410);
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(q) + base + vi * 8) = o;
+  };
+  const bool packed_path = std::is_same<T, BF16>::value && O == Out::kS8 && div.fast && !has_zp;
   auto emit = [&](const float (&v)[8], int64_t vi) {
     int c[8];
 #pragma unroll
@@ -256,8 +292,12 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
     int64_t vi = lane_in_group + (int64_t)it * G;
     if (vi < nvec) {
       float v[8];
-      if constexpr (std::is_same<T, BF16>::value) unpack_bf16x8(cache[it], v);
-      else load8<T>(x, base + vi * 8, v);
+      if constexpr (std::is_same<T, BF16>::value) {
+        if (packed_path) { emit_packed(cache[it], vi); continue; }
+        unpack_bf16x8(cache[it], v);
+      } else {
+        load8<T>(x, base + vi * 8, v);
+      }
       emit(v, vi);
     }
   }
@@ -265,6 +305,105 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
     float v[8];
     load8<T>(x, base + vi * 8, v);
     emit(v, vi);
+  }
+}
+
+// ---- the per-token hot path: bf16 rows -> int8, absmax, strict rounding ---------------------
+//
+// Persistent CTAs walk the rows with a stride of gridDim.x.  The 128-bit loads of the next row
+// are issued before the current row is reduced and quantized, so HBM always has a row per CTA
+// in flight while the SM computes.  The arithmetic is arranged to stay off the conversion
+// pipe: |x| and max on packed bf16 pairs; x * rcp(s) in float32 (exact after bf16 rounding,
+// see Divider); round-half-even through the 1.5 * 2^23 float addition whose low mantissa byte
+// is the two's-complement code.  |x / s| <= 128 here, so one min() saturates.  Rows whose
+// absmax is not finite (inf / NaN inputs) or whose scale leaves the fast range take the
+// general per-element recipe.
+
+constexpr int kRowVec = 4;  // 16-byte vectors per thread: rows up to 256 * 4 * 8 = 8192 elements
+
+__global__ void __launch_bounds__(kThreads, 3)
+quantize_rows_bf16_s8_kernel(const uint4* __restrict__ x, int64_t segments, int nvec,
+                             uint2* __restrict__ q, __nv_bfloat16* __restrict__ scale) {
+  __shared__ uint32_t red[2][kThreads / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint4 cur[kRowVec], nxt[kRowVec];
+
+  auto load_row = [&](int64_t row, uint4 (&dst)[kRowVec]) {
+#pragma unroll
+    for (int it = 0; it < kRowVec; ++it) {
+      const int vi = tid + it * kThreads;
+      if (vi < nvec) dst[it] = x[row * nvec + vi];
+    }
+  };
+
+  int64_t row = blockIdx.x;
+  if (row < segments) load_row(row, cur);
+  for (int iter = 0; row < segments; ++iter) {
+    const int64_t next = row + gridDim.x;
+    if (next < segments) load_row(next, nxt);
+
+    // absmax of the row
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+    for (int it = 0; it < kRowVec; ++it) {
+      if (tid + it * kThreads < nvec) {
+        const uint32_t w[4] = {cur[it].x, cur[it].y, cur[it].z, cur[it].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          m2 = __hmax2_nan(m2, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[j])));
+      }
+    }
+    const float2 mf = __bfloat1622float2(m2);
+    uint32_t bits = max(__float_as_uint(mf.x), __float_as_uint(mf.y));  // NaN sorts last
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+    uint32_t* slot = red[iter & 1];
+    if (lane == 0) slot[warp] = bits;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) bits = max(bits, slot[i]);
+    const float absmax = __uint_as_float(bits);
+
+    const float s = symmetric_scale<BF16, S8>(absmax);
+    if (tid == 0) scale[row] = __float2bfloat16_rn(s);
+    const Divider<BF16> div(s, true);
+    const bool fast = div.fast && bits < 0x7f800000u;  // finite absmax, scale in the fast range
+
+#pragma unroll
+    for (int it = 0; it < kRowVec; ++it) {
+      const int vi = tid + it * kThreads;
+      if (vi >= nvec) continue;
+      const uint32_t w[4] = {cur[it].x, cur[it].y, cur[it].z, cur[it].w};
+      uint32_t code[8];
+      if (fast) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float y0 = __fmul_rn(__uint_as_float(w[j] << 16), div.r);
+          const float y1 = __fmul_rn(__uint_as_float(w[j] & 0xffff0000u), div.r);
+          const __nv_bfloat162 b = __floats2bfloat162_rn(y0, y1);
+          const uint32_t bw = *reinterpret_cast<const uint32_t*>(&b);
+          const float z0 = fminf(__uint_as_float(bw << 16), 127.f);
+          const float z1 = fminf(__uint_as_float(bw & 0xffff0000u), 127.f);
+          code[2 * j] = __float_as_uint(__fadd_rn(z0, 12582912.f));
+          code[2 * j + 1] = __float_as_uint(__fadd_rn(z1, 12582912.f));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          code[2 * j] = (uint32_t)quantize_one<BF16, S8>(__uint_as_float(w[j] << 16), div, 0.f,
+                                                        false, true);
+          code[2 * j + 1] = (uint32_t)quantize_one<BF16, S8>(
+              __uint_as_float(w[j] & 0xffff0000u), div, 0.f, false, true);
+        }
+      }
+      uint2 o;
+      o.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+      o.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
+      q[row * nvec + vi] = o;
+    }
+#pragma unroll
+    for (int it = 0; it < kRowVec; ++it) cur[it] = nxt[it];
+    row = next;
   }
 }
 
@@ -668,6 +807,15 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
   // One pass when every tile is a contiguous row segment of whole 16-byte vectors.
   if (tp == 1 && tr == 1 && tc % 8 == 0 && aligned16(x) && aligned16(q)) {
     const int64_t segments = P * R * (C / tc);
+    if (x_dtype == QWX_BF16 && qtype == QWX_S8 && method == QWX_ABSMAX && !has_arg &&
+        rounding == QWX_STRICT && tc > 32 * 8 * kCache && tc <= kThreads * kRowVec * 8) {
+      const int64_t cap = 148 * 4;
+      const unsigned grid = (unsigned)(segments < cap ? segments : cap);
+      quantize_rows_bf16_s8_kernel<<<grid, kThreads, 0, st>>>(
+          (const uint4*)x, segments, (int)(tc / 8), (uint2*)q, (__nv_bfloat16*)scale);
+      QWX_CHECK_LAUNCH();
+      return (int)QWX_OK;
+    }
     return dispatch_float(x_dtype, [&](auto t) {
       using T = decltype(t);
       return dispatch_out(qtype, [&](auto o) {

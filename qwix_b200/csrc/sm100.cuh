@@ -13,12 +13,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
 // ---- mbarrier ---------------------------------------------------------------------------
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -49,19 +43,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
-// Waits for the phase with the given parity to complete.  Gives up after kWaitBudgetNs
-// (or as soon as another role of the CTA has raised *abort), raises *abort and returns
-// false, so that a lost arrival ends the kernel with an error code instead of a hang.
-constexpr uint64_t kWaitBudgetNs = 2000ull * 1000ull * 1000ull;
+// Waits for the phase with the given parity to complete.  Gives up after kWaitBudgetCycles SM
+// clocks (about two seconds at boost clocks; longer, but still finite, at idle clocks) or as
+// soon as another role of the CTA has raised *abort; it then raises *abort and returns false,
+// so that a lost arrival ends the kernel with an error code instead of a hang.  The clock is
+// first read after 256 failed polls: the common short wait never pays for it.
+constexpr long long kWaitBudgetCycles = 4000000000ll;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  for (int it = 0; it < 256; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+#pragma unroll 1
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0) {
+    if ((it & 255u) == 0) {
       if (*abort) return false;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (clock64() - t0 > kWaitBudgetCycles) {
         *abort = 1;
         return false;
       }

@@ -1,0 +1,86 @@
+"""GPU parity: fused int4 weight-only GEMM (through the C ABI) vs the CPU oracle's
+dequantize-then-dot path."""
+
+import ml_dtypes
+import numpy as np
+import pytest
+import torch
+
+from oracle import dot_general as odg
+from oracle import qarray as oq
+from qwix_b200.core import dot_general as bdg
+from qwix_b200.core import qarray as bq
+from qwix_b200.core import weight_only
+from tests import helpers as h
+
+pytestmark = pytest.mark.gpu
+DN = (((1,), (0,)), ((), ()))
+
+CASES = [
+    # M, K, N, tile, scale dtype
+    (1, 512, 256, 128, 'float32'),
+    (16, 512, 256, 128, 'float32'),
+    (16, 1024, 384, 256, 'bfloat16'),
+    (7, 4096, 1024, 128, 'float32'),      # more units than SMs: whole and split tiles mixed
+    (128, 1024, 512, 128, 'float32'),
+    (48, 512, 256, 512, 'bfloat16'),      # one scale per channel
+    (200, 512, 256, 128, 'float32'),      # more than 128 tokens: two launches
+    (16, 8192, 2048, 128, 'float32'),
+    (16, 8192, 4096, 128, 'float32'),     # ~14 units per CTA: rings and operand slots wrap
+    (128, 2048, 2048, 128, 'bfloat16'),   # 128 tokens, several units per CTA
+    (3, 1024, 8192, 256, 'float32'),      # short tiles: a CTA crosses several tile segments
+    (33, 512, 4096, 128, 'float32'),      # 64-token padding, segments shorter than the slot count
+]
+
+
+@pytest.mark.parametrize('case', CASES, ids=lambda c: 'x'.join(map(str, c)))
+def test_a16w4_matches_oracle(case):
+  M, K, N, tile, sdt = case
+  rng = np.random.default_rng(M + K + N)
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32).astype(ml_dtypes.bfloat16)
+  a = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.bfloat16)
+  sd = np.float32 if sdt == 'float32' else ml_dtypes.bfloat16
+  wo = oq.quantize_api(w, 'int4', channelwise_axes=[1], tiled_axes={0: tile}, scale_dtype=sd)
+  want = odg.dot_general(a, wo, DN, preferred_element_type=ml_dtypes.bfloat16)
+  assert not odg.use_fast_path(a, wo, DN)  # the reference takes the dequantize-first path
+
+  wq = bq.quantize_api(h.to_torch(w), 'int4', channelwise_axes=[1], tiled_axes={0: tile},
+                       scale_dtype=torch.float32 if sdt == 'float32' else torch.bfloat16)
+  assert h.codes_equal(wq.qvalue, wo.qvalue)
+  assert np.array_equal(h.to_numpy(wq.scale).view(np.uint8), wo.scale.view(np.uint8))
+  at = h.to_torch(a)
+  assert weight_only.eligible(at, wq, DN)
+  got = bdg.dot_general(at, wq, DN, preferred_element_type=torch.bfloat16)
+  again = bdg.dot_general(at, wq, DN, preferred_element_type=torch.bfloat16)
+  torch.cuda.synchronize()
+  g = h.to_numpy(got).astype(np.float32)
+  r = want.astype(np.float32)
+  assert g.shape == r.shape
+  bad = np.abs(g - r) > 1e-2 + 2e-2 * np.abs(r)
+  assert not bad.any(), f'{bad.sum()} of {bad.size} out of tolerance, max {np.abs(g - r).max()}'
+  # the scratch buffer is left zero: a second call agrees (split tiles are summed with float
+  # atomics, so the last bit may depend on arrival order)
+  assert torch.allclose(got.float(), again.float(), rtol=2 ** -7, atol=1e-3)
+  # and the unfused path (dequantize kernel + library GEMM) agrees as well
+  old = bdg.FUSE_WEIGHT_ONLY
+  try:
+    bdg.FUSE_WEIGHT_ONLY = False
+    slow = bdg.dot_general(at, wq, DN, preferred_element_type=torch.bfloat16)
+  finally:
+    bdg.FUSE_WEIGHT_ONLY = old
+  s = h.to_numpy(slow).astype(np.float32)
+  assert np.all(np.abs(s - r) <= 1e-2 + 2e-2 * np.abs(r))
+
+
+def test_a16w4_float32_output_is_tight():
+  M, K, N = 16, 2048, 512
+  rng = np.random.default_rng(5)
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32).astype(ml_dtypes.bfloat16)
+  a = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.bfloat16)
+  wo = oq.quantize_api(w, 'int4', channelwise_axes=[1], tiled_axes={0: 128})
+  # W~ = bf16(q * s) exactly as the kernel forms it, float64 accumulation as the yardstick
+  wt = oq.dequantize(wo).astype(np.float64)
+  want = a.astype(np.float64) @ wt
+  wq = bq.quantize_api(h.to_torch(w), 'int4', channelwise_axes=[1], tiled_axes={0: 128})
+  got = bdg.dot_general(h.to_torch(a), wq, DN, preferred_element_type=torch.float32)
+  assert np.abs(got.cpu().numpy() - want).max() <= 2e-4 * np.abs(want).max()
