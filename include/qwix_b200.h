@@ -99,6 +99,32 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C,
                  int qtype, int rounding, void* q, void* scale, void* zero_point,
                  void* workspace, size_t workspace_bytes, qwx_stream_t stream);
 
+/* qwx_quantize for callers that have no way to provide scratch memory.  It has no
+ * counterpart in the reference (XLA plans scratch for its own fusions); it exists for users of
+ * this library such as a custom-call handler inside a framework that fixed all of its buffers
+ * before the step started, or a serving process that must not call cudaMalloc once it is
+ * warm (the call synchronises the device and may fail when memory is tight).
+ *
+ * Same arguments and results as qwx_quantize, without the workspace pair: the scratch is a
+ * 1 MiB array in device global memory that is part of the library (every GPU that loads the
+ * library holds it until the process ends; qwx_quantize_builtin_scratch_bytes() reports its
+ * size).  Limit: the view may have at most 65,520 tiles (16 bytes of statistics per tile plus
+ * 256); larger views return QWX_ERR_WORKSPACE and nothing is launched.  Views whose tiles are
+ * row segments need no scratch and are never refused.
+ *
+ * The first call on each device looks up the array's device address (one
+ * cudaGetSymbolAddress, made with that device current, result cached); make that first call
+ * before starting any stream capture.  The call itself never allocates: no cudaMalloc,
+ * cudaFree or allocating library routine.  All calls on a device share the one array and it
+ * keeps whatever the previous call left, so each call clears the part it accumulates into;
+ * two calls whose kernels overlap on the GPU (different streams, no ordering between them)
+ * race on it and must be serialised by the caller. */
+size_t qwx_quantize_builtin_scratch_bytes(void);
+int qwx_quantize_noalloc(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C,
+                         int64_t tp, int64_t tr, int64_t tc, int method, int has_arg, double arg,
+                         int qtype, int rounding, void* q, void* scale, void* zero_point,
+                         qwx_stream_t stream);
+
 /* qarray.dequantize (qarray.py:692-708): (q - zero_point) * scale in scale_dtype. */
 int qwx_dequantize(const void* q, int qtype, int64_t P, int64_t R, int64_t C,
                    int64_t tp, int64_t tr, int64_t tc, const void* scale, int scale_dtype,

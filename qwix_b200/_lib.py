@@ -39,6 +39,8 @@ _SIGNATURES = {
     'qwx_compute_scale_zero_point': (_int, [_vp, _vp, _int, _i64, _int, _vp, _vp, _vp]),
     'qwx_quantize_with_scale': (_int, [_vp, _int] + [_i64] * 6 + [_vp, _vp, _int, _int, _vp, _vp]),
     'qwx_quantize': (_int, [_vp, _int] + [_i64] * 6 + [_int, _int, _dbl, _int, _int, _vp, _vp, _vp, _vp, _sz, _vp]),
+    'qwx_quantize_builtin_scratch_bytes': (_sz, []),
+    'qwx_quantize_noalloc': (_int, [_vp, _int] + [_i64] * 6 + [_int, _int, _dbl, _int, _int, _vp, _vp, _vp, _vp]),
     'qwx_dequantize': (_int, [_vp, _int] + [_i64] * 6 + [_vp, _int, _vp, _vp, _vp]),
     'qwx_transpose_codes': (_int, [_vp, _i64, _i64, _vp, _vp]),
     'qwx_w4_packed_bytes': (_sz, [_i64, _i64]),

@@ -6,6 +6,8 @@
 // shared-memory hop, and cross-CTA reductions use integer atomics on float bit patterns.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace qwx {
 namespace {
 
@@ -848,6 +850,64 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
   if (rc) return rc;
   return run_apply(x, x_dtype, vw, scale, method == QWX_MINMAX ? zero_point : nullptr, qtype,
                    rounding, q, st);
+}
+
+// ---- quantize without any allocation by anyone --------------------------------------------
+//
+// Some callers cannot obtain device scratch at the moment they need to quantize: a custom-call
+// handler that runs inside a framework whose buffers were all planned before the step began
+// has nobody to ask for a workspace, and a serving loop that has finished warm-up must not
+// call cudaMalloc, because that call synchronises the whole device and can fail under memory
+// pressure.  For them the statistics scratch of the tiled quantizer lives in the library
+// image: a fixed array in device global memory that every GPU loading the library keeps
+// until the process exits.
+
+constexpr size_t kBuiltinScratchBytes = 1u << 20;  // 1 MiB: views of up to 65,520 tiles
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+namespace {
+
+// Device address of g_builtin_scratch on the current device.  In host code the array's name
+// is only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once
+// per device while that device is current, and remembered.
+int builtin_scratch_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* address[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return QWX_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (address[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_builtin_scratch) != cudaSuccess || p == nullptr)
+      return QWX_ERR_LAUNCH;
+    address[dev] = p;
+  }
+  *out = address[dev];
+  return QWX_OK;
+}
+
+}  // namespace
+
+size_t qwx_quantize_builtin_scratch_bytes(void) { return kBuiltinScratchBytes; }
+
+int qwx_quantize_noalloc(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, int64_t tp,
+                         int64_t tr, int64_t tc, int method, int has_arg, double arg, int qtype,
+                         int rounding, void* q, void* scale, void* zero_point,
+                         qwx_stream_t stream) {
+  View vw;
+  int rc = make_view(P, R, C, tp, tr, tc, &vw);
+  if (rc) return rc;
+  // Refuse, before touching anything, a view whose statistics do not fit the built-in array.
+  if (qwx_quantize_workspace_bytes(P, R, C, tp, tr, tc) > kBuiltinScratchBytes)
+    return QWX_ERR_WORKSPACE;
+  void* scratch = nullptr;
+  rc = builtin_scratch_address(&scratch);
+  if (rc) return rc;
+  // qwx_quantize clears the statistics it accumulates into (an asynchronous memset on
+  // `stream`) and neither it nor the kernels behind it allocate.
+  return qwx_quantize(x, x_dtype, P, R, C, tp, tr, tc, method, has_arg, arg, qtype, rounding, q,
+                      scale, zero_point, scratch, kBuiltinScratchBytes, stream);
 }
 
 int qwx_dequantize(const void* q, int qtype, int64_t P, int64_t R, int64_t C, int64_t tp,
