@@ -170,6 +170,37 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
                    void* workspace, size_t workspace_bytes, int workspace_is_zero,
                    int32_t* error_flag, qwx_stream_t stream);
 
+/* Blockwise Hadamard rotation, the arithmetic of qwix/contrib/hadamard_rot.py:35-117 with the
+ * Sylvester matrix H of size `block` (= 128) and optional +/-1 sign vectors (int8, one entry
+ * per index of the rotated axis; `signs_in` is applied before H, `signs_out` after it, as in
+ * contrib/kernels/fused_hadamard_quantized_matmul.py:150-160).  x: bf16 [R, C].
+ *   axis = 1: out = x . H per `block` columns               (_apply_hadamard_lhs, :99-106)
+ *   axis = 0: out = H . x / block per `block` rows          (_apply_hadamard_rhs, :109-117;
+ *             contrib/kernels/fused_hadamard_quantized_matmul.py:443-478) */
+int qwx_hadamard_rotate(const void* x, int x_dtype, int64_t R, int64_t C, int axis, int block,
+                        const int8_t* signs_in, const int8_t* signs_out, void* out,
+                        qwx_stream_t stream);
+
+/* Rotate (axis = 1) and quantize in one pass over x: bf16 [rows, K] -> codes [rows, K] (QWX_S8
+ * or QWX_E4M3) with one absmax scale per row (bf16 [rows]); the fused form of
+ * contrib/kernels/fused_hadamard_quantize.py:43-119 and of `quantize_a_tile`
+ * (fused_hadamard_quantized_matmul.py:50-56) for whole-row tiles.  K <= 8192. */
+int qwx_hadamard_quantize(const void* x, int x_dtype, int64_t rows, int64_t K, int block,
+                          const int8_t* signs_in, const int8_t* signs_out, int qtype,
+                          int rounding, void* q, void* scale, qwx_stream_t stream);
+
+/* The Hadamard-quantized matmul (`hadamard_quantize_multiply`,
+ * fused_hadamard_quantized_matmul.py:349-414): a bf16 [M, K] is rotated and quantized per row,
+ * then contracted with the already rotated and quantized weight wq ([K, N] or [N, K] codes of
+ * code_dtype, scales sw [N] bf16) on the tensor cores, scales applied in the epilogue.
+ * workspace: qwx_hadamard_gemm_workspace_bytes(M, K) bytes, 256-byte aligned. */
+size_t qwx_hadamard_gemm_workspace_bytes(int64_t M, int64_t K);
+int qwx_hadamard_gemm(const void* a, int64_t M, int64_t K, const int8_t* signs_in,
+                      const int8_t* signs_out, const void* wq, const void* sw, int64_t N,
+                      int code_dtype, int b_layout, int rounding, void* out, int out_dtype,
+                      int epilogue, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                      qwx_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

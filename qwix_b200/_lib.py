@@ -48,6 +48,11 @@ _SIGNATURES = {
     'qwx_gemm_a16w4_workspace_bytes': (_sz, [_i64, _i64]),
     'qwx_gemm_a16w4': (_int, [_vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _sz, _int,
                               _vp, _vp]),
+    'qwx_hadamard_rotate': (_int, [_vp, _int, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp]),
+    'qwx_hadamard_quantize': (_int, [_vp, _int, _i64, _i64, _int, _vp, _vp, _int, _int, _vp, _vp, _vp]),
+    'qwx_hadamard_gemm_workspace_bytes': (_sz, [_i64, _i64]),
+    'qwx_hadamard_gemm': (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _vp, _int,
+                                 _int, _vp, _sz, _vp, _vp]),
     'qwx_gemm_q8': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,
                            _int, _vp, _int, _int, _vp, _vp]),
 }

@@ -1,0 +1,289 @@
+// Blockwise Walsh-Hadamard rotation fused with quantization: the device side of
+// qwix/contrib/hadamard_rot.py:99-117 (x . H per block of the contraction axis for the
+// activation, H . w / d for the weight) and of the activation half of
+// qwix/contrib/kernels/fused_hadamard_quantized_matmul.py:150-170 (sign flip, rotate, sign
+// flip, absmax-quantize).  H is the Sylvester matrix with +/-1 entries, so x . H is a fast
+// Walsh-Hadamard transform in natural order: log2(d) butterfly stages, done here in float32 on
+// values held in registers (three stages inside a thread's 8 values, the rest by warp shuffles
+// between the 16 lanes that share a 128-value block).
+#include "common.cuh"
+
+namespace qwx {
+namespace {
+
+constexpr int kHThreads = 256;
+constexpr int kHVec = 4;      // 16-byte vectors per thread: rows up to 256 * 4 * 8 = 8192 values
+constexpr int kBlock = 128;   // Hadamard block (2^7)
+
+__device__ __forceinline__ void fwht8(float (&v)[8]) {
+#pragma unroll
+  for (int s = 1; s < 8; s <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if ((i & s) == 0) {
+        const float a = v[i], b = v[i | s];
+        v[i] = a + b;
+        v[i | s] = a - b;
+      }
+    }
+  }
+}
+
+// Stages over the four lane bits that index the 16 vectors of a 128-value block.
+__device__ __forceinline__ void fwht_lanes(float (&v)[8], int lane) {
+#pragma unroll
+  for (int m = 1; m < 16; m <<= 1) {
+    const bool upper = (lane & m) != 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], m);
+      v[i] = upper ? other - v[i] : v[i] + other;
+    }
+  }
+}
+
+__device__ __forceinline__ void apply_signs8(float (&v)[8], const int8_t* s, int64_t at) {
+  const int2 w = *reinterpret_cast<const int2*>(s + at);
+  const int words[2] = {w.x, w.y};
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if ((int8_t)(words[i >> 2] >> (8 * (i & 3))) < 0) v[i] = -v[i];
+}
+
+// One CTA per row (persistent, stride gridDim.x): load the row, rotate every 128-value block,
+// round to bf16 (the rotated activation of the reference is a bf16 array), row absmax, scale,
+// quantize.  Q = S8 or E4M3.
+template <typename Q>
+__global__ void __launch_bounds__(kHThreads, 2)
+hadamard_quantize_rows_kernel(const uint4* __restrict__ x, int64_t rows, int nvec,
+                              const int8_t* __restrict__ signs_in,
+                              const int8_t* __restrict__ signs_out, int rounding,
+                              uint2* __restrict__ q, __nv_bfloat16* __restrict__ scale) {
+  __shared__ uint32_t red[2][kHThreads / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool strict = rounding == QWX_STRICT;
+  uint4 rot[kHVec];  // the rotated row, as packed bf16
+
+  int iter = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++iter) {
+    uint32_t bits = 0;
+#pragma unroll
+    for (int it = 0; it < kHVec; ++it) {
+      const int vi = tid + it * kHThreads;
+      // Whole warps run or skip together: nvec is a multiple of 16 and a block never
+      // straddles a half-warp, but the shuffles need all 32 lanes, so inactive lanes
+      // rotate zeros.
+      float v[8];
+      if (vi < nvec) unpack_bf16x8(x[row * nvec + vi], v);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
+      if (signs_in && vi < nvec) apply_signs8(v, signs_in, (int64_t)vi * 8);
+      fwht8(v);
+      fwht_lanes(v, lane);
+      if (signs_out && vi < nvec) apply_signs8(v, signs_out, (int64_t)vi * 8);
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        bits = max(bits, max((w[j] << 16) & 0x7fffffffu, w[j] & 0x7fff0000u));
+      }
+      rot[it] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+    uint32_t* slot = red[iter & 1];
+    if (lane == 0) slot[warp] = bits;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kHThreads / 32; ++i) bits = max(bits, slot[i]);
+    const float absmax = __uint_as_float(bits);
+
+    // scale = absmax / bound in bf16 with the tiny-scale guard (qarray.py:557-562)
+    float s = round_to<BF16>(__fdiv_rn(absmax, sym_bound<Q>()));
+    if (s < 0x1p-63f) s = 1.0f;
+    if (tid == 0) scale[row] = __float2bfloat16_rn(s);
+
+#pragma unroll
+    for (int it = 0; it < kHVec; ++it) {
+      const int vi = tid + it * kHThreads;
+      if (vi >= nvec) continue;
+      float v[8];
+      unpack_bf16x8(rot[it], v);
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float y = __fdiv_rn(v[j], s);
+        if (strict) y = round_to<BF16>(y);
+        c[j] = to_code<Q>(y);
+      }
+      uint2 o;
+      o.x = (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)(c[3] & 0xff) << 24);
+      o.y = (c[4] & 0xff) | ((c[5] & 0xff) << 8) | ((c[6] & 0xff) << 16) | ((uint32_t)(c[7] & 0xff) << 24);
+      q[row * nvec + vi] = o;
+    }
+  }
+}
+
+// Rotation only, blocks along the contiguous axis: out = x . H per 128 columns (bf16).
+__global__ void __launch_bounds__(kHThreads)
+hadamard_rotate_cols_kernel(const uint4* __restrict__ x, int64_t total_vec,
+                            const int8_t* __restrict__ signs_in,
+                            const int8_t* __restrict__ signs_out, int vec_per_row,
+                            uint4* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t start = (int64_t)blockIdx.x * kHThreads + threadIdx.x;
+  // total_vec is a multiple of 16 and blocks are 16 consecutive vectors: keep warps whole.
+  for (int64_t base = (int64_t)blockIdx.x * kHThreads; base < total_vec;
+       base += (int64_t)gridDim.x * kHThreads) {
+    const int64_t vi = base + threadIdx.x;
+    float v[8];
+    if (vi < total_vec) unpack_bf16x8(x[vi], v);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    const int64_t col = (vi % vec_per_row) * 8;
+    if (signs_in && vi < total_vec) apply_signs8(v, signs_in, col);
+    fwht8(v);
+    fwht_lanes(v, lane);
+    if (signs_out && vi < total_vec) apply_signs8(v, signs_out, col);
+    if (vi < total_vec) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      out[vi] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  (void)start;
+}
+
+// Rotation only, blocks along the row axis of a [K, N] weight: out = H . w_block / 128.  One
+// thread owns one column of one block (128 values in registers); neighbouring threads own
+// neighbouring columns, so every load and store is coalesced.
+__global__ void __launch_bounds__(128)
+hadamard_rotate_rows_kernel(const __nv_bfloat16* __restrict__ w, int64_t K, int64_t N,
+                            const int8_t* __restrict__ signs_in,
+                            const int8_t* __restrict__ signs_out, __nv_bfloat16* __restrict__ out) {
+  const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t k0 = (int64_t)blockIdx.y * kBlock;
+  if (n >= N) return;
+  float v[kBlock];
+#pragma unroll
+  for (int i = 0; i < kBlock; ++i) {
+    v[i] = __bfloat162float(w[(k0 + i) * N + n]);
+    if (signs_in && signs_in[k0 + i] < 0) v[i] = -v[i];
+  }
+#pragma unroll
+  for (int s = 1; s < kBlock; s <<= 1) {
+#pragma unroll
+    for (int i = 0; i < kBlock; ++i) {
+      if ((i & s) == 0) {
+        const float a = v[i], b = v[i | s];
+        v[i] = a + b;
+        v[i | s] = a - b;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kBlock; ++i) {
+    // the reference rounds the product to bf16, then divides by the block size (exact)
+    float r = round_to<BF16>(v[i]);
+    if (signs_out && signs_out[k0 + i] < 0) r = -r;
+    out[(k0 + i) * N + n] = __float2bfloat16_rn(r * (1.0f / kBlock));
+  }
+}
+
+}  // namespace
+}  // namespace qwx
+
+using namespace qwx;
+
+extern "C" {
+
+int qwx_hadamard_quantize(const void* x, int x_dtype, int64_t rows, int64_t K, int block,
+                          const int8_t* signs_in, const int8_t* signs_out, int qtype,
+                          int rounding, void* q, void* scale, qwx_stream_t stream) {
+  if (!x || !q || !scale) return QWX_ERR_NULL;
+  if (x_dtype != QWX_BF16) return QWX_ERR_DTYPE;
+  if (block != kBlock) return QWX_ERR_UNSUPPORTED;
+  if (rows <= 0 || K <= 0 || K % kBlock) return QWX_ERR_SHAPE;
+  if (K > (int64_t)kHThreads * kHVec * 8) return QWX_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7)) return QWX_ERR_ALIGN;
+  if ((signs_in && (reinterpret_cast<uintptr_t>(signs_in) & 7)) ||
+      (signs_out && (reinterpret_cast<uintptr_t>(signs_out) & 7)))
+    return QWX_ERR_ALIGN;
+  const int64_t cap = 148 * 4;
+  const unsigned grid = (unsigned)(rows < cap ? rows : cap);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (qtype == QWX_E4M3)
+    hadamard_quantize_rows_kernel<E4M3><<<grid, kHThreads, 0, st>>>(
+        (const uint4*)x, rows, (int)(K / 8), signs_in, signs_out, rounding, (uint2*)q,
+        (__nv_bfloat16*)scale);
+  else if (qtype == QWX_S8)
+    hadamard_quantize_rows_kernel<S8><<<grid, kHThreads, 0, st>>>(
+        (const uint4*)x, rows, (int)(K / 8), signs_in, signs_out, rounding, (uint2*)q,
+        (__nv_bfloat16*)scale);
+  else
+    return QWX_ERR_DTYPE;
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+int qwx_hadamard_rotate(const void* x, int x_dtype, int64_t R, int64_t C, int axis, int block,
+                        const int8_t* signs_in, const int8_t* signs_out, void* out,
+                        qwx_stream_t stream) {
+  if (!x || !out) return QWX_ERR_NULL;
+  if (x_dtype != QWX_BF16) return QWX_ERR_DTYPE;
+  if (block != kBlock) return QWX_ERR_UNSUPPORTED;
+  if (R <= 0 || C <= 0) return QWX_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (axis == 1) {
+    if (C % kBlock) return QWX_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return QWX_ERR_ALIGN;
+    const int64_t total = R * (C / 8);
+    int64_t blocks = (total + kHThreads - 1) / kHThreads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    hadamard_rotate_cols_kernel<<<(unsigned)blocks, kHThreads, 0, st>>>(
+        (const uint4*)x, total, signs_in, signs_out, (int)(C / 8), (uint4*)out);
+  } else if (axis == 0) {
+    if (R % kBlock) return QWX_ERR_SHAPE;
+    if (R / kBlock > 65535) return QWX_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)((C + 127) / 128), (unsigned)(R / kBlock));
+    hadamard_rotate_rows_kernel<<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, R, C, signs_in,
+                                                      signs_out, (__nv_bfloat16*)out);
+  } else {
+    return QWX_ERR_SHAPE;
+  }
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+size_t qwx_hadamard_gemm_workspace_bytes(int64_t M, int64_t K) {
+  if (M <= 0 || K <= 0) return 0;
+  return (size_t)(M * K) + (size_t)((M * 2 + 255) / 256 * 256);
+}
+
+int qwx_hadamard_gemm(const void* a, int64_t M, int64_t K, const int8_t* signs_in,
+                      const int8_t* signs_out, const void* wq, const void* sw, int64_t N,
+                      int code_dtype, int b_layout, int rounding, void* out, int out_dtype,
+                      int epilogue, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                      qwx_stream_t stream) {
+  if (!workspace) return QWX_ERR_NULL;
+  if (workspace_bytes < qwx_hadamard_gemm_workspace_bytes(M, K)) return QWX_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return QWX_ERR_ALIGN;
+  void* sa = workspace;                                     // [M] bf16 row scales
+  void* aq = (char*)workspace + (M * 2 + 255) / 256 * 256;  // [M, K] codes
+  int rc = qwx_hadamard_quantize(a, QWX_BF16, M, K, kBlock, signs_in, signs_out, code_dtype,
+                                 rounding, aq, sa, stream);
+  if (rc) return rc;
+  return qwx_gemm_q8(aq, wq, code_dtype, b_layout, M, N, K, 0, sa, 0, sw, 0, QWX_BF16, out,
+                     out_dtype, epilogue, error_flag, stream);
+}
+
+}  // extern "C"

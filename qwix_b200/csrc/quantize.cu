@@ -312,37 +312,58 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
 
 // ---- the per-token hot path: bf16 rows -> int8, absmax, strict rounding ---------------------
 //
-// Persistent CTAs walk the rows with a stride of gridDim.x.  The 128-bit loads of the next row
-// are issued before the current row is reduced and quantized, so HBM always has a row per CTA
-// in flight while the SM computes.  The arithmetic is arranged to stay off the conversion
-// pipe: |x| and max on packed bf16 pairs; x * rcp(s) in float32 (exact after bf16 rounding,
-// see Divider); round-half-even through the 1.5 * 2^23 float addition whose low mantissa byte
-// is the two's-complement code.  |x / s| <= 128 here, so one min() saturates.  Rows whose
-// absmax is not finite (inf / NaN inputs) or whose scale leaves the fast range take the
-// general per-element recipe.
+// Persistent CTAs walk the rows with a stride of gridDim.x and keep three rows in flight
+// through a shared-memory ring while one is reduced and quantized.  The arithmetic is arranged to work on packed bf16
+// pairs: |x| and max on packed bf16, the division as three packed bf16 FMAs that give the
+// correctly rounded bf16 quotient, one conversion per value and a saturating pack.  Rows whose
+// absmax is not finite (inf / NaN inputs) or whose scale leaves the fast range take the general
+// per-element recipe.
 
 constexpr int kRowVec = 4;  // 16-byte vectors per thread: rows up to 256 * 4 * 8 = 8192 elements
+constexpr int kRowDepth = 4;  // rows per CTA in the shared-memory ring: one in use, three in flight
 
 __global__ void __launch_bounds__(kThreads, 3)
 quantize_rows_bf16_s8_kernel(const uint4* __restrict__ x, int64_t segments, int nvec,
                              uint2* __restrict__ q, __nv_bfloat16* __restrict__ scale) {
+  extern __shared__ uint4 ring[];   // [kRowDepth][nvec]; thread t only touches vectors t + 256 i
   __shared__ uint32_t red[2][kThreads / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  uint4 cur[kRowVec], nxt[kRowVec];
+  uint4 cur[kRowVec];
 
-  auto load_row = [&](int64_t row, uint4 (&dst)[kRowVec]) {
+  // Rows reach shared memory through 16-byte cp.async copies that every thread issues for its
+  // own vectors, three rows ahead: the bytes in flight per SM no longer depend on registers.
+  int64_t fetch_row = blockIdx.x;
+  int fetch_stage = 0;
+  auto fetch = [&]() {
+    if (fetch_row < segments) {
+#pragma unroll
+      for (int it = 0; it < kRowVec; ++it) {
+        const int vi = tid + it * kThreads;
+        if (vi < nvec) {
+          const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ring + fetch_stage * nvec + vi);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                       "l"(x + fetch_row * nvec + vi) : "memory");
+        }
+      }
+      fetch_row += gridDim.x;
+    }
+    if (++fetch_stage == kRowDepth) fetch_stage = 0;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  for (int d = 0; d < kRowDepth - 1; ++d) fetch();
+
+  int stage = 0;
+  int64_t row = blockIdx.x;
+  for (int iter = 0; row < segments; ++iter) {
+    const int64_t next = row + gridDim.x;
+    asm volatile("cp.async.wait_group %0;" ::"n"(kRowDepth - 2) : "memory");
 #pragma unroll
     for (int it = 0; it < kRowVec; ++it) {
       const int vi = tid + it * kThreads;
-      if (vi < nvec) dst[it] = x[row * nvec + vi];
+      if (vi < nvec) cur[it] = ring[stage * nvec + vi];
     }
-  };
-
-  int64_t row = blockIdx.x;
-  if (row < segments) load_row(row, cur);
-  for (int iter = 0; row < segments; ++iter) {
-    const int64_t next = row + gridDim.x;
-    if (next < segments) load_row(next, nxt);
+    if (++stage == kRowDepth) stage = 0;
+    fetch();   // refills the stage consumed one iteration ago
 
     // absmax of the row
     __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
@@ -370,26 +391,45 @@ quantize_rows_bf16_s8_kernel(const uint4* __restrict__ x, int64_t segments, int 
     if (tid == 0) scale[row] = __float2bfloat16_rn(s);
     const Divider<BF16> div(s, true);
     const bool fast = div.fast && bits < 0x7f800000u;  // finite absmax, scale in the fast range
+    const __nv_bfloat16 sb = __float2bfloat16_rn(s);
+    const __nv_bfloat16 rb = __float2bfloat16_rn(__frcp_rn(s));  // RN_bf16(1 / s), no double rounding
+    const __nv_bfloat162 r2 = __halves2bfloat162(rb, rb);
+    const __nv_bfloat162 ns2 = __hneg2(__halves2bfloat162(sb, sb));
 
 #pragma unroll
     for (int it = 0; it < kRowVec; ++it) {
       const int vi = tid + it * kThreads;
       if (vi >= nvec) continue;
       const uint32_t w[4] = {cur[it].x, cur[it].y, cur[it].z, cur[it].w};
-      uint32_t code[8];
+      uint2 o;
       if (fast) {
+        // Correctly rounded bf16 quotients from three packed bf16 FMAs (Markstein's division):
+        // q0 = x * r, rem = x - q0 * s (one rounding), z = q0 + rem * r, with r = RN(1 / s).
+        // Checked exhaustively for all 128 x 128 pairs of bf16 significands.  Then
+        // round-half-even to int32 and a saturating pack of four codes per word.
+        uint32_t packed[2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float y0 = __fmul_rn(__uint_as_float(w[j] << 16), div.r);
-          const float y1 = __fmul_rn(__uint_as_float(w[j] & 0xffff0000u), div.r);
-          const __nv_bfloat162 b = __floats2bfloat162_rn(y0, y1);
-          const uint32_t bw = *reinterpret_cast<const uint32_t*>(&b);
-          const float z0 = fminf(__uint_as_float(bw << 16), 127.f);
-          const float z1 = fminf(__uint_as_float(bw & 0xffff0000u), 127.f);
-          code[2 * j] = __float_as_uint(__fadd_rn(z0, 12582912.f));
-          code[2 * j + 1] = __float_as_uint(__fadd_rn(z1, 12582912.f));
+        for (int half = 0; half < 2; ++half) {
+          int c[4];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(&w[2 * half + j]);
+            const __nv_bfloat162 q0 = __hmul2(xv, r2);
+            const __nv_bfloat162 rem = __hfma2(q0, ns2, xv);
+            const __nv_bfloat162 z = __hfma2(rem, r2, q0);
+            const uint32_t zw = *reinterpret_cast<const uint32_t*>(&z);
+            asm("{ .reg .b16 lo, hi;\n\t mov.b32 {lo, hi}, %2;\n\t"
+                " cvt.rni.s32.bf16 %0, lo;\n\t cvt.rni.s32.bf16 %1, hi; }"
+                : "=r"(c[2 * j]), "=r"(c[2 * j + 1]) : "r"(zw));
+          }
+          uint32_t hi16;
+          asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi16) : "r"(c[3]), "r"(c[2]), "r"(0u));
+          asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed[half]) : "r"(c[1]), "r"(c[0]), "r"(hi16));
         }
+        o.x = packed[0];
+        o.y = packed[1];
       } else {
+        uint32_t code[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           code[2 * j] = (uint32_t)quantize_one<BF16, S8>(__uint_as_float(w[j] << 16), div, 0.f,
@@ -397,16 +437,14 @@ quantize_rows_bf16_s8_kernel(const uint4* __restrict__ x, int64_t segments, int 
           code[2 * j + 1] = (uint32_t)quantize_one<BF16, S8>(
               __uint_as_float(w[j] & 0xffff0000u), div, 0.f, false, true);
         }
+        o.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+        o.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
       }
-      uint2 o;
-      o.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
-      o.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
       q[row * nvec + vi] = o;
     }
-#pragma unroll
-    for (int it = 0; it < kRowVec; ++it) cur[it] = nxt[it];
     row = next;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 // ---- general tiled view: statistics by atomics, then an elementwise pass --------------------
@@ -813,7 +851,16 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
         rounding == QWX_STRICT && tc > 32 * 8 * kCache && tc <= kThreads * kRowVec * 8) {
       const int64_t cap = 148 * 4;
       const unsigned grid = (unsigned)(segments < cap ? segments : cap);
-      quantize_rows_bf16_s8_kernel<<<grid, kThreads, 0, st>>>(
+      const size_t ring_bytes = (size_t)kRowDepth * (tc / 8) * 16;
+      static bool configured = false;  // idempotent attribute; a benign race sets it twice
+      if (!configured) {
+        if (cudaFuncSetAttribute(quantize_rows_bf16_s8_kernel,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kRowDepth * kThreads * kRowVec * 16) != cudaSuccess)
+          return (int)QWX_ERR_LAUNCH;
+        configured = true;
+      }
+      quantize_rows_bf16_s8_kernel<<<grid, kThreads, ring_bytes, st>>>(
           (const uint4*)x, segments, (int)(tc / 8), (uint2*)q, (__nv_bfloat16*)scale);
       QWX_CHECK_LAUNCH();
       return (int)QWX_OK;
