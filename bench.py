@@ -100,6 +100,25 @@ class ClockSampler:
             'samples': len(sm)}
 
 
+def token_shard(rank: int, world: int, tokens_per_rank: int):
+  """Global token ids owned by `rank`: ranks own disjoint, equal, contiguous shards."""
+  del world
+  return list(range(rank * tokens_per_rank, (rank + 1) * tokens_per_rank))
+
+
+def max_over_ranks(ms: float, dist, device) -> float:
+  """The job's time for a timed region is the slowest rank's time."""
+  t = torch.tensor([ms], dtype=torch.float64, device=device)
+  if dist is not None:
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+  return float(t.item())
+
+
+def whole_job_tops(ms_per_step: float, world: int) -> float:
+  """Every rank runs one full step on its own tokens: the job does `world` steps' work."""
+  return world * OPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
+
+
 def _inputs(seed_base: int, device):
   """BASELINE configs[1]: A ~ N(0,1) with 1% of the K columns scaled x20, W ~ N(0, 0.02)."""
   sets = []
@@ -280,12 +299,9 @@ def main():
   if int(err.item()) != 0:
     raise SystemExit(f'device-side wait ran out inside the GEMM (code {int(err.item())})')
 
-  t = torch.tensor([total_ms], dtype=torch.float64, device=device)
-  if dist is not None:
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-  total_ms = float(t.item())
+  total_ms = max_over_ranks(total_ms, dist, device)
   ms_per_step = total_ms / args.steps
-  value = world * OPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
+  value = whole_job_tops(ms_per_step, world)
 
   # ---- end to end through the public plugin API, host buffers in, host buffers out ----
   provider_rule = qwix.QuantizationRule(module_path='.*', weight_qtype='int8', act_qtype='int8')
@@ -310,11 +326,8 @@ def main():
     e2e_step(i)
   e1.record()
   barrier()
-  t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-  if dist is not None:
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-  e2e_ms = float(t.item()) / e2e_steps
-  e2e_value = world * OPS_PER_STEP / (e2e_ms * 1e-3) / 1e12
+  e2e_ms = max_over_ranks(e0.elapsed_time(e1), dist, device) / e2e_steps
+  e2e_value = whole_job_tops(e2e_ms, world)
 
   if rank != 0:
     if dist is not None:

@@ -1,0 +1,373 @@
+"""Llama-shaped decoder whose projections run through the quantized path, tensor-parallel.
+
+This is the workload of BASELINE configs[4]: every Dense of the decoder is issued through
+qwix_b200.ops, so under `quantize_model(model, PtqProvider(w8a8 rule))` each projection is a
+per-token int8 activation quantization plus one int8 tcgen05 GEMM with the scales fused in its
+epilogue.  Everything that is not a contraction with a weight (RMSNorm, RoPE, the attention
+core, sampling) is ordinary tensor code; the attention core is the library's fused
+scaled-dot-product kernel, which -- like a fused attention primitive under the reference's
+interception -- is not a quantized op.
+
+Tensor parallelism (one process per GPU): q/k/v and gate/up are column-parallel (heads and
+FFN columns split across ranks), o_proj and down_proj are row-parallel and followed by one
+all-reduce (NCCL over NVLink through torch.distributed).  Weights are quantized per output
+channel from the full matrix and then sliced, so a rank's codes and scales are exactly the
+slices of the single-GPU model's (what sharding propagation gives the reference under GSPMD,
+utils/flax_util.py:320-426).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+import torch.nn.functional as F
+
+import qwix_b200 as qwix
+from qwix_b200 import nn
+from qwix_b200 import ops
+from qwix_b200.core import qarray
+from qwix_b200.providers import ptq
+
+
+@dataclasses.dataclass(frozen=True)
+class DecoderConfig:
+  layers: int = 32
+  d_model: int = 4096
+  q_heads: int = 32
+  kv_heads: int = 8
+  head_dim: int = 128
+  ffn: int = 14336
+  vocab: int = 128256
+  rope_theta: float = 500000.0
+  norm_eps: float = 1e-5
+  dtype: torch.dtype = torch.bfloat16
+
+  @staticmethod
+  def llama3_8b() -> 'DecoderConfig':
+    return DecoderConfig()
+
+  @staticmethod
+  def tiny() -> 'DecoderConfig':
+    """Two layers, same structure: the cut-down used for oracle parity."""
+    return DecoderConfig(layers=2, d_model=512, q_heads=8, kv_heads=2, head_dim=64, ffn=1024,
+                         vocab=1024)
+
+
+class _Comm:
+  """The tensor-parallel group: rank, size and the two collectives the path needs."""
+
+  def __init__(self, group=None):
+    import torch.distributed as dist
+    self.dist = dist if (dist.is_available() and dist.is_initialized()) else None
+    self.group = group
+    self.size = self.dist.get_world_size(group) if self.dist else 1
+    self.rank = self.dist.get_rank(group) if self.dist else 0
+
+  def all_reduce_sum(self, x: torch.Tensor) -> torch.Tensor:
+    if self.size > 1:
+      self.dist.all_reduce(x, op=self.dist.ReduceOp.SUM, group=self.group)
+    return x
+
+  def all_reduce_max(self, x: torch.Tensor) -> torch.Tensor:
+    if self.size > 1:
+      self.dist.all_reduce(x, op=self.dist.ReduceOp.MAX, group=self.group)
+    return x
+
+  def all_gather_last(self, x: torch.Tensor) -> torch.Tensor:
+    if self.size == 1:
+      return x
+    parts = [torch.empty_like(x) for _ in range(self.size)]
+    self.dist.all_gather(parts, x.contiguous(), group=self.group)
+    return torch.cat(parts, dim=-1)
+
+
+def _normal(shape, seed: int, device, dtype, std=0.02) -> torch.Tensor:
+  g = torch.Generator(device=device).manual_seed(seed)
+  return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).to(dtype)
+
+
+class RMSNorm(torch.nn.Module):
+
+  def __init__(self, d: int, eps: float, dtype, device):
+    super().__init__()
+    self.scale = torch.nn.Parameter(torch.ones(d, dtype=dtype, device=device), requires_grad=False)
+    self.eps = eps
+
+  def forward(self, x):
+    v = x.float()
+    v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
+    return (v * self.scale.float()).to(x.dtype)
+
+
+class RowParallelDense(nn.Dense):
+  """Dense whose input features are sharded: y = all_reduce(x_shard @ kernel_shard).
+
+  exact_act_scale: quantize the activation with the absmax of the whole (unsharded) row, which
+  takes one extra max all-reduce of a [tokens] vector -- the collective that dynamic
+  calibration over a sharded contraction axis needs in the reference
+  (docs/source/basics.md:83-86).  Otherwise every shard scales its own slice, which is
+  sub-channel quantization with tile K / ranks."""
+
+  def __init__(self, *a, comm: _Comm, exact_act_scale: bool, **k):
+    super().__init__(*a, **k)
+    self.comm = comm
+    self.exact_act_scale = exact_act_scale
+
+  def forward(self, x):
+    dn = (((x.ndim - 1,), (0,)), ((), ()))
+    rule = qwix.get_current_rule('dot_general')
+    kernel = self.kernel
+    if (self.exact_act_scale and self.comm.size > 1 and rule is not None
+        and rule.act_qtype is not None and isinstance(kernel, ptq.WithAux)):
+      how = qarray.HowToQuantize(qtype=rule.act_qtype, channelwise_axes=list(range(x.ndim - 1)),
+                                 calibration_method=rule.act_calibration_method or 'absmax')
+      cal = qarray.calibrate(x, how)
+      cal = {k: self.comm.all_reduce_max(v) for k, v in cal.items()}
+      scale, zp = qarray.compute_scale_zero_point(cal, how.qtype)
+      xq = qarray.quantize_with_scale_zero_point(x, how.qtype, scale, zp)
+      from qwix_b200.core import dot_general as dg
+      y = dg.dot_general(xq, kernel.array, dn)
+    else:
+      y = ops.dot_general(x, kernel, dn)
+    return self.comm.all_reduce_sum(y)
+
+
+class Attention(torch.nn.Module):
+
+  def __init__(self, cfg: DecoderConfig, comm: _Comm, layer: int, device, exact: bool):
+    super().__init__()
+    t = comm.size
+    assert cfg.q_heads % t == 0 and cfg.kv_heads % t == 0
+    self.cfg, self.comm = cfg, comm
+    self.hq, self.hkv = cfg.q_heads // t, cfg.kv_heads // t
+    d, hd = cfg.d_model, cfg.head_dim
+    # One fused column-parallel projection [d, (hq + 2 hkv) * hd] per rank.
+    self.qkv = nn.Dense(d, (self.hq + 2 * self.hkv) * hd, use_bias=False, dtype=cfg.dtype,
+                        device=device)
+    self.o = RowParallelDense(self.hq * hd, d, use_bias=False, dtype=cfg.dtype, device=device,
+                              comm=comm, exact_act_scale=exact)
+    self.layer = layer
+
+  def forward(self, x, cos, sin, cache_k, cache_v, pos):
+    B, T, _ = x.shape
+    hd = self.cfg.head_dim
+    qkv = self.qkv(x)
+    q, k, v = qkv.split([self.hq * hd, self.hkv * hd, self.hkv * hd], dim=-1)
+    q = q.view(B, T, self.hq, hd).transpose(1, 2)
+    k = k.view(B, T, self.hkv, hd).transpose(1, 2)
+    v = v.view(B, T, self.hkv, hd).transpose(1, 2)
+    q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+    if isinstance(pos, torch.Tensor):
+      # One new token at a position held on the device (the form a CUDA graph can replay):
+      # write it into the cache by index and mask the keys that lie beyond it.
+      cache_k.index_copy_(2, pos, k)
+      cache_v.index_copy_(2, pos, v)
+      mask = (torch.arange(cache_k.shape[2], device=x.device) <= pos).view(1, 1, 1, -1)
+      out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
+      out = out.transpose(1, 2).reshape(B, T, self.hq * hd)
+      return self.o(out)
+    cache_k[:, :, pos:pos + T] = k
+    cache_v[:, :, pos:pos + T] = v
+    if pos == 0:
+      out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+    else:
+      out = F.scaled_dot_product_attention(q, cache_k[:, :, :pos + T], cache_v[:, :, :pos + T],
+                                           is_causal=False, enable_gqa=True)
+    out = out.transpose(1, 2).reshape(B, T, self.hq * hd)
+    return self.o(out)
+
+
+def _rope(x, cos, sin):
+  half = x.shape[-1] // 2
+  x1, x2 = x[..., :half].float(), x[..., half:].float()
+  return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+
+class FeedForward(torch.nn.Module):
+
+  def __init__(self, cfg: DecoderConfig, comm: _Comm, device, exact: bool):
+    super().__init__()
+    assert cfg.ffn % comm.size == 0
+    self.local = cfg.ffn // comm.size
+    self.gate_up = nn.Dense(cfg.d_model, 2 * self.local, use_bias=False, dtype=cfg.dtype,
+                            device=device)
+    self.down = RowParallelDense(self.local, cfg.d_model, use_bias=False, dtype=cfg.dtype,
+                                 device=device, comm=comm, exact_act_scale=exact)
+
+  def forward(self, x):
+    gu = self.gate_up(x)
+    g, u = gu.split(self.local, dim=-1)
+    return self.down(F.silu(g) * u)
+
+
+class Block(torch.nn.Module):
+
+  def __init__(self, cfg, comm, layer, device, exact):
+    super().__init__()
+    self.attn_norm = RMSNorm(cfg.d_model, cfg.norm_eps, cfg.dtype, device)
+    self.attn = Attention(cfg, comm, layer, device, exact)
+    self.ffn_norm = RMSNorm(cfg.d_model, cfg.norm_eps, cfg.dtype, device)
+    self.ffn = FeedForward(cfg, comm, device, exact)
+
+  def forward(self, x, cos, sin, ck, cv, pos):
+    x = x + self.attn(self.attn_norm(x), cos, sin, ck, cv, pos)
+    return x + self.ffn(self.ffn_norm(x))
+
+
+class Decoder(torch.nn.Module):
+  """Random-init decoder of the given shape, sharded for this rank of the TP group.
+
+  Weights come from per-tensor seeds and are generated as the full matrix then sliced, so all
+  TP degrees hold slices of the same model."""
+
+  def __init__(self, cfg: DecoderConfig, device='cuda', group=None, exact_act_scale: bool = False,
+               seed: int = 0):
+    super().__init__()
+    self.cfg = cfg
+    self.comm = _Comm(group)
+    self.device = torch.device(device)
+    t, r = self.comm.size, self.comm.rank
+    assert cfg.vocab % t == 0
+    self.embed = torch.nn.Parameter(_normal((cfg.vocab, cfg.d_model), seed + 1, self.device,
+                                            cfg.dtype), requires_grad=False)
+    self.layers = torch.nn.ModuleList(
+        [Block(cfg, self.comm, i, self.device, exact_act_scale) for i in range(cfg.layers)])
+    self.final_norm = RMSNorm(cfg.d_model, cfg.norm_eps, cfg.dtype, self.device)
+    self.lm_head = nn.Dense(cfg.d_model, cfg.vocab // t, use_bias=False, dtype=cfg.dtype,
+                            device=self.device)
+    self._init_weights(seed, t, r)
+    self.cache = None
+
+  # -- weights ---------------------------------------------------------------------------
+
+  def _full(self, shape, seed):
+    return _normal(shape, seed, self.device, self.cfg.dtype)
+
+  def _init_weights(self, seed, t, r):
+    cfg, hd = self.cfg, self.cfg.head_dim
+    hq, hkv, fl = cfg.q_heads // t, cfg.kv_heads // t, cfg.ffn // t
+    for i, blk in enumerate(self.layers):
+      s = seed + 100 * (i + 1)
+      wq = self._full((cfg.d_model, cfg.q_heads * hd), s + 1)[:, r * hq * hd:(r + 1) * hq * hd]
+      wk = self._full((cfg.d_model, cfg.kv_heads * hd), s + 2)[:, r * hkv * hd:(r + 1) * hkv * hd]
+      wv = self._full((cfg.d_model, cfg.kv_heads * hd), s + 3)[:, r * hkv * hd:(r + 1) * hkv * hd]
+      blk.attn.qkv.kernel.data = torch.cat([wq, wk, wv], dim=1).contiguous()
+      blk.attn.o.kernel.data = self._full((cfg.q_heads * hd, cfg.d_model), s + 4)[
+          r * hq * hd:(r + 1) * hq * hd].contiguous()
+      wg = self._full((cfg.d_model, cfg.ffn), s + 5)[:, r * fl:(r + 1) * fl]
+      wu = self._full((cfg.d_model, cfg.ffn), s + 6)[:, r * fl:(r + 1) * fl]
+      blk.ffn.gate_up.kernel.data = torch.cat([wg, wu], dim=1).contiguous()
+      blk.ffn.down.kernel.data = self._full((cfg.ffn, cfg.d_model), s + 7)[
+          r * fl:(r + 1) * fl].contiguous()
+    vl = cfg.vocab // t
+    self.lm_head.kernel.data = self._full((cfg.d_model, cfg.vocab), seed + 2)[
+        :, r * vl:(r + 1) * vl].contiguous()
+
+  def quantize_weights(self, qtype='int8'):
+    """Offline PTQ of every projection (the role of quantize_params): per output channel,
+    computed on the full matrix so that row-parallel shards share the unsharded scales."""
+    t, r = self.comm.size, self.comm.rank
+    how = qarray.HowToQuantize(qtype=qtype, channelwise_axes=[1])
+
+    def box(mod, full_rows=None):
+      w = mod.kernel.data
+      if full_rows is None or t == 1:
+        qa = qarray.quantize(w, how)
+      else:
+        # row-parallel: scale from the absmax over all ranks' rows of each column
+        cal = qarray.calibrate(w, how)
+        cal = {k: self.comm.all_reduce_max(v) for k, v in cal.items()}
+        scale, _ = qarray.compute_scale_zero_point(cal, qtype)
+        qa = qarray.quantize_with_scale_zero_point(w, qtype, scale, None)
+      del mod._parameters['kernel']
+      mod.kernel = ptq.WithAux(qa, how)
+
+    for blk in self.layers:
+      box(blk.attn.qkv)
+      box(blk.attn.o, full_rows=True)
+      box(blk.ffn.gate_up)
+      box(blk.ffn.down, full_rows=True)
+    box(self.lm_head)
+    torch.cuda.empty_cache()
+
+  # -- inference -------------------------------------------------------------------------
+
+  def alloc_cache(self, batch: int, max_len: int):
+    cfg = self.cfg
+    hkv = cfg.kv_heads // self.comm.size
+    shape = (cfg.layers, 2, batch, hkv, max_len, cfg.head_dim)
+    self.cache = torch.zeros(shape, dtype=cfg.dtype, device=self.device)
+    pos = torch.arange(max_len, device=self.device, dtype=torch.float32)
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=self.device,
+                                                 dtype=torch.float32) / cfg.head_dim))
+    ang = pos[:, None] * inv[None, :]
+    self.cos, self.sin = ang.cos(), ang.sin()
+
+  def forward(self, tokens: torch.Tensor, pos=0, batch_offset: int = 0,
+              last_only: bool = True) -> torch.Tensor:
+    """tokens [B, T] at positions pos..pos+T-1 of sequences batch_offset..batch_offset+B-1.
+    `pos` is an int, or for single-token steps a one-element int64 device tensor.
+    Returns full-vocabulary logits [B, 1 or T, vocab] (float32)."""
+    B, T = tokens.shape
+    x = self.embed[tokens]
+    if isinstance(pos, torch.Tensor):
+      assert T == 1
+      cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
+    else:
+      cos, sin = self.cos[pos:pos + T], self.sin[pos:pos + T]
+    for i, blk in enumerate(self.layers):
+      ck = self.cache[i, 0, batch_offset:batch_offset + B]
+      cv = self.cache[i, 1, batch_offset:batch_offset + B]
+      x = blk(x, cos, sin, ck, cv, pos)
+    x = self.final_norm(x[:, -1:] if last_only else x)
+    logits = self.lm_head(x)
+    return self.comm.all_gather_last(logits).float()
+
+
+def w8a8_rules():
+  return [qwix.QuantizationRule(module_path='.*', weight_qtype='int8', act_qtype='int8')]
+
+
+@torch.no_grad()
+def generate(model, tokens: torch.Tensor, steps: int, prefill_batch: int = 4,
+             use_graph: bool = True):
+  """Greedy decoding: chunked prefill of [B, T] prompts, then `steps` tokens per sequence.
+  `model` is a Decoder or its quantized wrapper.  The single-token step is launch-bound
+  (hundreds of small kernels), so after one eager step it is captured in a CUDA graph and
+  replayed.  Returns the generated ids [B, steps]."""
+  dec = model.model if isinstance(model, qwix.model.QuantizedModel) else model
+  B, T = tokens.shape
+  if dec.cache is None or dec.cache.shape[2] < B or dec.cache.shape[4] < T + steps:
+    dec.alloc_cache(B, T + steps)
+  nxt = torch.empty((B,), dtype=torch.long, device=tokens.device)
+  for b0 in range(0, B, prefill_batch):
+    logits = model(tokens[b0:b0 + prefill_batch], 0, b0)
+    nxt[b0:b0 + prefill_batch] = logits[:, -1].argmax(-1)
+  out = torch.empty((B, steps), dtype=torch.long, device=tokens.device)
+  out[:, 0] = nxt
+  if steps == 1:
+    return out
+  tok = nxt.clone().view(B, 1)
+  pos = torch.full((1,), T, dtype=torch.long, device=tokens.device)
+
+  def step():
+    tok.copy_(model(tok, pos, 0)[:, -1].argmax(-1, keepdim=True))
+    pos.add_(1)
+
+  step()                       # eager: warms every kernel up before any capture
+  out[:, 1] = tok[:, 0]
+  graph = None
+  if use_graph and steps > 2:
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):   # records the step; it runs only when replayed
+      step()
+  for s in range(2, steps):
+    if graph is not None:
+      graph.replay()
+    else:
+      step()
+    out[:, s] = tok[:, 0]
+  return out

@@ -1,0 +1,72 @@
+"""NumPy restatement of qwix_b200.decoder for parity tests: same architecture, every projection
+through the oracle's quantize + dot_general (w8a8), everything else in float32 rounded to bf16
+where the model holds bf16 tensors."""
+
+import ml_dtypes
+import numpy as np
+
+from oracle import dot_general as odg
+from oracle import qarray as oq
+
+bf16 = ml_dtypes.bfloat16
+DN2 = lambda nd: (((nd - 1,), (0,)), ((), ()))
+
+
+def _dense(x, wq):
+  dn = DN2(x.ndim)
+  how = odg.get_how_to_quantize(dimension_numbers=dn, ndims=(x.ndim, 2), for_lhs=True,
+                                tile_size=None, qtype='int8')
+  return odg.dot_general(oq.quantize(x, how), wq, dn)
+
+
+def _rms(x, eps):
+  v = x.astype(np.float32)
+  v = v / np.sqrt((v * v).mean(-1, keepdims=True) + eps)
+  return v.astype(bf16)
+
+
+def _rope(x, cos, sin):
+  half = x.shape[-1] // 2
+  x1, x2 = x[..., :half].astype(np.float32), x[..., half:].astype(np.float32)
+  return np.concatenate([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).astype(bf16)
+
+
+def quantize_weight(w):
+  return oq.quantize(w, oq.HowToQuantize(qtype='int8', channelwise_axes=[1]))
+
+
+def forward(cfg, weights, tokens):
+  """weights: dict of bf16 NumPy arrays named like the torch model's full (unsharded) matrices.
+  tokens [B, T].  Returns float32 logits [B, T, vocab] of a causal prefill."""
+  B, T = tokens.shape
+  hd, hq, hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
+  x = weights['embed'][tokens]
+  pos = np.arange(T, dtype=np.float32)
+  inv = 1.0 / (cfg.rope_theta ** (np.arange(0, hd, 2, dtype=np.float32) / hd))
+  ang = pos[:, None] * inv[None, :]
+  cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+  mask = np.triu(np.full((T, T), -np.inf, np.float32), 1)
+  for i in range(cfg.layers):
+    w = weights['layers'][i]
+    h = _rms(x, cfg.norm_eps)
+    qkv = _dense(h, w['qkv'])
+    q, k, v = np.split(qkv, [hq * hd, (hq + hkv) * hd], axis=-1)
+    q = _rope(q.reshape(B, T, hq, hd).transpose(0, 2, 1, 3), cos, sin)
+    k = _rope(k.reshape(B, T, hkv, hd).transpose(0, 2, 1, 3), cos, sin)
+    v = v.reshape(B, T, hkv, hd).transpose(0, 2, 1, 3)
+    rep = hq // hkv
+    kf = np.repeat(k.astype(np.float32), rep, axis=1)
+    vf = np.repeat(v.astype(np.float32), rep, axis=1)
+    s = q.astype(np.float32) @ kf.transpose(0, 1, 3, 2) / np.sqrt(hd) + mask
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p = p / p.sum(-1, keepdims=True)
+    att = (p @ vf).astype(bf16).transpose(0, 2, 1, 3).reshape(B, T, hq * hd)
+    x = (x.astype(np.float32) + _dense(att, w['o']).astype(np.float32)).astype(bf16)
+    h = _rms(x, cfg.norm_eps)
+    gu = _dense(h, w['gate_up']).astype(np.float32)
+    g, u = np.split(gu, 2, axis=-1)
+    g, u = g.astype(bf16).astype(np.float32), u.astype(bf16).astype(np.float32)
+    act = ((g / (1.0 + np.exp(-g))).astype(bf16).astype(np.float32) * u).astype(bf16)
+    x = (x.astype(np.float32) + _dense(act, w['down']).astype(np.float32)).astype(bf16)
+  h = _rms(x, cfg.norm_eps)
+  return _dense(h, weights['lm_head']).astype(np.float32)

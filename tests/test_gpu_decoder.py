@@ -1,0 +1,124 @@
+"""GPU: the w8a8 decoder (BASELINE configs[4] architecture, cut down to two layers) against a
+NumPy oracle decoder, decode steps against prefill, and tensor-parallel against single-GPU."""
+
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import qwix_b200 as qwix
+from qwix_b200 import decoder as D
+from tests import decoder_oracle as DO
+from tests import helpers as h
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _full_weights(model: D.Decoder):
+  """Unsharded bf16 weights of a TP=1 model as NumPy, quantized for the oracle."""
+  out = {'embed': h.to_numpy(model.embed.data), 'layers': []}
+  for blk in model.layers:
+    out['layers'].append({
+        'qkv': DO.quantize_weight(h.to_numpy(blk.attn.qkv.kernel.data)),
+        'o': DO.quantize_weight(h.to_numpy(blk.attn.o.kernel.data)),
+        'gate_up': DO.quantize_weight(h.to_numpy(blk.ffn.gate_up.kernel.data)),
+        'down': DO.quantize_weight(h.to_numpy(blk.ffn.down.kernel.data)),
+    })
+  out['lm_head'] = DO.quantize_weight(h.to_numpy(model.lm_head.kernel.data))
+  return out
+
+
+def test_tiny_decoder_matches_oracle_and_decode_matches_prefill():
+  cfg = D.DecoderConfig.tiny()
+  model = D.Decoder(cfg, device='cuda')
+  weights = _full_weights(model)
+  model.quantize_weights()
+  for i, blk in enumerate(model.layers):   # offline PTQ gives the oracle's codes bit for bit
+    assert h.codes_equal(blk.attn.qkv.kernel.array.qvalue, weights['layers'][i]['qkv'].qvalue)
+    assert h.codes_equal(blk.ffn.down.kernel.array.qvalue, weights['layers'][i]['down'].qvalue)
+  ptq_model = qwix.quantize_model(model, qwix.PtqProvider(D.w8a8_rules()))
+  B, T = 2, 32
+  tokens = torch.randint(0, cfg.vocab, (B, T), generator=torch.Generator().manual_seed(0)).cuda()
+  model.alloc_cache(B, T + 8)
+  with torch.no_grad():
+    got = ptq_model(tokens, 0, 0, last_only=False).cpu().numpy()
+  want = DO.forward(cfg, weights, tokens.cpu().numpy())
+  rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+  assert rel < 3e-2, rel
+  assert (got.argmax(-1) == want.argmax(-1)).mean() > 0.9
+
+  # Decode: feeding token t at position t against the cache reproduces the prefill logits.
+  with torch.no_grad():
+    ptq_model(tokens[:, :T - 1], 0, 0)
+    step = ptq_model(tokens[:, T - 1:], T - 1, 0).cpu().numpy()
+  rel = np.linalg.norm(step[:, 0] - got[:, -1]) / np.linalg.norm(got[:, -1])
+  assert rel < 3e-2, rel
+
+  ids = D.generate(ptq_model, tokens, steps=6, prefill_batch=1, use_graph=False)
+  assert ids.shape == (B, 6) and int(ids.max()) < cfg.vocab
+  # the first generated token is the argmax of the prefill's last position
+  assert torch.equal(ids[:, 0].cpu(), torch.from_numpy(got[:, -1].argmax(-1)))
+  # replaying the captured single-token step gives the same ids as running it eagerly
+  replay = D.generate(ptq_model, tokens, steps=6, prefill_batch=1, use_graph=True)
+  assert torch.equal(ids, replay)
+
+
+TP_WORKER = '''
+import os, sys, json
+sys.path.insert(0, os.environ["REPO_ROOT"])
+import torch, torch.distributed as dist
+rank = int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(rank)
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+import qwix_b200 as qwix
+from qwix_b200 import decoder as D
+cfg = D.DecoderConfig.tiny()
+tokens = torch.randint(0, cfg.vocab, (2, 24), generator=torch.Generator().manual_seed(0)).cuda()
+def run(group, exact):
+  m = D.Decoder(cfg, device="cuda", group=group, exact_act_scale=exact)
+  m.quantize_weights()
+  m.alloc_cache(2, 32)
+  q = qwix.quantize_model(m, qwix.PtqProvider(D.w8a8_rules()))
+  with torch.no_grad():
+    return q(tokens, 0, 0, last_only=False)
+solo = dist.new_group([rank]) if False else None
+# TP=1 reference on every rank: a one-rank group
+groups = [dist.new_group([r]) for r in range(dist.get_world_size())]
+ref = run(groups[rank], False)
+res = {}
+for exact in (True, False):
+  out = run(None, exact)
+  res["exact" if exact else "local"] = float((out - ref).norm() / ref.norm())
+  res["max_" + ("exact" if exact else "local")] = float((out - ref).abs().max())
+if rank == 0:
+  print(json.dumps(res))
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def _free_port():
+  with socket.socket() as s:
+    s.bind(('127.0.0.1', 0))
+    return s.getsockname()[1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_tensor_parallel_matches_single_gpu(tmp_path):
+  script = tmp_path / 'tp_worker.py'
+  script.write_text(TP_WORKER)
+  env = dict(os.environ, REPO_ROOT=ROOT)
+  cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node=2',
+         '--master-addr', '127.0.0.1', '--master-port', str(_free_port()), str(script)]
+  out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+  assert out.returncode == 0, out.stderr[-3000:]
+  import json
+  res = json.loads([l for l in out.stdout.splitlines() if l.startswith('{')][-1])
+  # exact activation scales: only the bf16 rounding of the two partial sums differs
+  assert res['exact'] < 1e-2 and res['local'] < 2e-2, res
