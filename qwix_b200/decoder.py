@@ -128,9 +128,11 @@ class RowParallelDense(nn.Dense):
       scale, zp = qarray.compute_scale_zero_point(cal, how.qtype)
       xq = qarray.quantize_with_scale_zero_point(x, how.qtype, scale, zp)
       from qwix_b200.core import dot_general as dg
-      y = dg.dot_general(xq, kernel.array, dn)
-    else:
-      y = ops.dot_general(x, kernel, dn)
+      # float32 partial products, summed across ranks before the one rounding to the model
+      # dtype: the nearest a sharded contraction gets to the unsharded result
+      y = dg.dot_general(xq, kernel.array, dn, preferred_element_type=torch.float32)
+      return self.comm.all_reduce_sum(y).to(x.dtype)
+    y = ops.dot_general(x, kernel, dn)
     return self.comm.all_reduce_sum(y)
 
 
@@ -330,44 +332,68 @@ def w8a8_rules():
   return [qwix.QuantizationRule(module_path='.*', weight_qtype='int8', act_qtype='int8')]
 
 
+class _StepGraph:
+  """The single-token decode step with its static buffers, captured once per batch size."""
+
+  def __init__(self, model, batch: int, device):
+    self.tok = torch.zeros((batch, 1), dtype=torch.long, device=device)
+    self.pos = torch.zeros((1,), dtype=torch.long, device=device)
+    self.model = model
+    self.graph = None
+
+  def step(self):
+    self.tok.copy_(self.model(self.tok, self.pos, 0)[:, -1].argmax(-1, keepdim=True))
+    self.pos.add_(1)
+
+  def capture(self):
+    torch.cuda.synchronize()
+    self.graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(self.graph):   # records the step; it runs only when replayed
+      self.step()
+
+
 @torch.no_grad()
 def generate(model, tokens: torch.Tensor, steps: int, prefill_batch: int = 4,
-             use_graph: bool = True):
+             use_graph: bool = True, timings: dict | None = None):
   """Greedy decoding: chunked prefill of [B, T] prompts, then `steps` tokens per sequence.
   `model` is a Decoder or its quantized wrapper.  The single-token step is launch-bound
-  (hundreds of small kernels), so after one eager step it is captured in a CUDA graph and
-  replayed.  Returns the generated ids [B, steps]."""
+  (hundreds of small kernels), so it is captured in a CUDA graph (once per batch size, after
+  one eager step that warms every kernel up) and replayed.  Returns the ids [B, steps];
+  `timings`, if given, receives the device time of the two phases in ms."""
   dec = model.model if isinstance(model, qwix.model.QuantizedModel) else model
   B, T = tokens.shape
   if dec.cache is None or dec.cache.shape[2] < B or dec.cache.shape[4] < T + steps:
     dec.alloc_cache(B, T + steps)
+    dec._step_graphs = {}
+  ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+  ev[0].record()
   nxt = torch.empty((B,), dtype=torch.long, device=tokens.device)
   for b0 in range(0, B, prefill_batch):
     logits = model(tokens[b0:b0 + prefill_batch], 0, b0)
     nxt[b0:b0 + prefill_batch] = logits[:, -1].argmax(-1)
+  ev[1].record()
   out = torch.empty((B, steps), dtype=torch.long, device=tokens.device)
   out[:, 0] = nxt
-  if steps == 1:
-    return out
-  tok = nxt.clone().view(B, 1)
-  pos = torch.full((1,), T, dtype=torch.long, device=tokens.device)
-
-  def step():
-    tok.copy_(model(tok, pos, 0)[:, -1].argmax(-1, keepdim=True))
-    pos.add_(1)
-
-  step()                       # eager: warms every kernel up before any capture
-  out[:, 1] = tok[:, 0]
-  graph = None
-  if use_graph and steps > 2:
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):   # records the step; it runs only when replayed
-      step()
-  for s in range(2, steps):
-    if graph is not None:
-      graph.replay()
+  graphs = dec.__dict__.setdefault('_step_graphs', {})
+  runner = graphs.get(B)
+  if runner is None:
+    runner = graphs[B] = _StepGraph(model, B, tokens.device)
+  runner.tok.copy_(nxt.view(B, 1))
+  runner.pos.fill_(T)
+  for s in range(1, steps):
+    if not use_graph:
+      runner.step()
+    elif runner.graph is None:
+      runner.step()            # eager once, then record for all later steps and calls
+      out[:, s] = runner.tok[:, 0]
+      runner.capture()
+      continue
     else:
-      step()
-    out[:, s] = tok[:, 0]
+      runner.graph.replay()
+    out[:, s] = runner.tok[:, 0]
+  ev[2].record()
+  if timings is not None:
+    torch.cuda.synchronize()
+    timings['prefill_ms'] = ev[0].elapsed_time(ev[1])
+    timings['decode_ms'] = ev[1].elapsed_time(ev[2])
   return out
