@@ -152,6 +152,26 @@ int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_layout,
                 int scale_dtype, void* out, int out_dtype, int epilogue, int32_t* error_flag,
                 qwx_stream_t stream);
 
+/* The same product with a caller-provided workspace, for decode-shaped problems (a few rows
+ * of activations against a large weight) whose output tiles are fewer than the SMs: K is cut
+ * into ranges so that every SM streams a share of the weight, each range writes its partial
+ * sums to a slab of the workspace, and the CTA that completes a tile adds the slabs in range
+ * order, scales and stores.  Results are bit-identical to qwx_gemm_q8 for int8 codes and
+ * repeatable for e4m3 codes (float32 partial sums are added in a fixed order).
+ * qwx_gemm_q8_workspace_bytes returns 0 when the shape would not be cut (the call then
+ * behaves exactly like qwx_gemm_q8 and workspace may be NULL).  The workspace opens with
+ * one int32 counter per output tile; these must be zero on entry (workspace_is_zero = 0
+ * makes the call clear them first) and are left zero on return, so one buffer cleared once
+ * serves every call on a stream.  The reference has no counterpart: XLA picks its own split
+ * of the contraction (dot_general.py:253-258 hands it one lax.dot_general). */
+size_t qwx_gemm_q8_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int qwx_gemm_q8_ws(const void* a, const void* b, int code_dtype, int b_layout,
+                   int64_t M, int64_t N, int64_t K, int64_t k_tile,
+                   const void* sa, int sa_tiled, const void* sb, int sb_tiled,
+                   int scale_dtype, void* out, int out_dtype, int epilogue,
+                   void* workspace, size_t workspace_bytes, int workspace_is_zero,
+                   int32_t* error_flag, qwx_stream_t stream);
+
 /* Weight-only int4 GEMM, the fused form of dot_general._slow_dot_general
  * (dot_general.py:264-275, chosen at :444-452 when the activation is not quantized):
  *   out[m, n] = sum_k a[m, k] * bf16( q[k, n] * scale[k / k_tile, n] )

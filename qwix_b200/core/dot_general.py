@@ -10,6 +10,7 @@ to XLA.
 from __future__ import annotations
 
 import math
+import threading
 from typing import Any, Mapping, Sequence
 
 import torch
@@ -158,16 +159,36 @@ def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
   out = torch.empty((B, M, N), dtype=out_t, device=lq.device)
   err = torch.zeros(1, dtype=torch.int32, device=lq.device)
   epi = _lib.EPI_REFERENCE if EPILOGUE == 'reference' else _lib.EPI_F32
-  fn = _lib.lib().qwx_gemm_q8
+  L = _lib.lib()
+  ws_bytes = L.qwx_gemm_q8_workspace_bytes(M, N, K)
+  ws = _splitk_workspace(lq.device, ws_bytes) if ws_bytes else None
   for b in range(B):
-    _lib.check(fn(_lib.ptr(a3[b]), _lib.ptr(b3[b]), code, layout, M, N, K, 0,
-                  _lib.ptr(None if ls is None else ls[b]), 0,
-                  _lib.ptr(None if rs is None else rs[b]), 0,
-                  numerics.code_of_float(scale_dt) if scale_dt is not None else _lib.F32,
-                  _lib.ptr(out[b]), _out_code(out_t), epi, _lib.ptr(err),
-                  _lib.stream_ptr(lq.device)), 'dot_general')
+    _lib.check(L.qwx_gemm_q8_ws(
+        _lib.ptr(a3[b]), _lib.ptr(b3[b]), code, layout, M, N, K, 0,
+        _lib.ptr(None if ls is None else ls[b]), 0,
+        _lib.ptr(None if rs is None else rs[b]), 0,
+        numerics.code_of_float(scale_dt) if scale_dt is not None else _lib.F32,
+        _lib.ptr(out[b]), _out_code(out_t), epi, _lib.ptr(ws), ws_bytes, 1, _lib.ptr(err),
+        _lib.stream_ptr(lq.device)), 'dot_general')
   out = out.reshape(bshape + mshape + nshape)
   return out if out.dtype == res_t else out.to(res_t)
+
+
+_ws_lock = threading.Lock()
+_ws_cache: dict = {}
+
+
+def _splitk_workspace(device, nbytes: int) -> torch.Tensor:
+  """Zero-filled scratch for the split-K form of the GEMM, one per (device, stream).  The
+  kernel leaves it zero and calls on one stream run in order, so it is cleared only when it
+  is created or grown."""
+  key = (device, torch.cuda.current_stream(device).cuda_stream)
+  with _ws_lock:
+    ws = _ws_cache.get(key)
+    if ws is None or ws.numel() < nbytes:
+      ws = torch.zeros(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
+      _ws_cache[key] = ws
+  return ws
 
 
 def _plain_dot_general(lhs: torch.Tensor, rhs: torch.Tensor, dimension_numbers,

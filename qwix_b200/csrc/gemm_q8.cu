@@ -40,8 +40,10 @@ struct Control {
   uint64_t empty[kStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t epi_done, fin_done;   // split-K: hand-over between the four epilogue warps
   uint32_t tmem_base;
   int abort;
+  int finalize;
   float sb[4][2][BN];  // per epilogue warp, per accumulator
 };
 
@@ -57,6 +59,9 @@ struct GemmParams {
   int epilogue;
   int32_t* error_flag;
   int tiles_m, tiles_n;
+  int splits;          // K is cut in `splits` ranges; 1 = every CTA owns whole tiles
+  uint32_t* ws;        // splits > 1: [splits][tiles][BN][BM] partial sums (int32 or float32 bits)
+  int* counters;       // splits > 1: [tiles], zero on entry
 };
 
 __device__ __forceinline__ float load_scale(const void* p, int dtype, int64_t i) {
@@ -80,8 +85,10 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   Control* ctl = reinterpret_cast<Control*>(smem_raw + (tiles - smem_u32(smem_raw)) +
                                             (size_t)kStages * kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  // Work items: (tile, K range).  With splits == 1 an item is a whole output tile; decode-shaped
+  // problems with fewer tiles than SMs cut K so that every SM streams a share of the weight.
   const int kblocks = (int)((p.K + BK - 1) / BK);
+  const int num_tiles = p.tiles_m * p.tiles_n * p.splits;
   volatile int* abort = &ctl->abort;
 
   if (threadIdx.x == 0) {
@@ -93,7 +100,10 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
       mbar_init(smem_u32(&ctl->acc_empty[a]), 4);
     }
+    mbar_init(smem_u32(&ctl->epi_done), 128);
+    mbar_init(smem_u32(&ctl->fin_done), 1);
     ctl->abort = 0;
+    ctl->finalize = 0;
     fence_barrier_init();
     prefetch_tensormap(&tma_a);
     prefetch_tensormap(&tma_b);
@@ -114,9 +124,12 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     long issued = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * BM;
-      const int n0 = (tile / p.tiles_m) * BN;
-      for (int kb = 0; kb < kblocks && ok; ++kb) {
+      const int split = tile % p.splits, t = tile / p.splits;
+      const int m0 = (t % p.tiles_m) * BM;
+      const int n0 = (t / p.tiles_m) * BN;
+      const int kb0 = (int)((int64_t)kblocks * split / p.splits);
+      const int kb1 = (int)((int64_t)kblocks * (split + 1) / p.splits);
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
         if (lane == 0) {
           ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort);
           if (ok) {
@@ -166,7 +179,10 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         tc_fence_after();
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
-      for (int kb = 0; kb < kblocks && ok; ++kb) {
+      const int split = tile % p.splits;
+      const int kb0 = (int)((int64_t)kblocks * split / p.splits);
+      const int kb1 = (int)((int64_t)kblocks * (split + 1) / p.splits);
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
         if (lane == 0) {
           ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort);
           if (ok) {
@@ -182,10 +198,10 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               const uint64_t db = BLAYOUT == QWX_B_NK
                                       ? make_smem_desc(sb + kk * UMMA_K, 16, 1024)
                                       : make_smem_desc(sb + kk * UMMA_K * 128, BK * 128, 1024);
-              mma_ss<KIND>(tmem_base + acc * kAccCols, da, db, idesc, (kb | kk) != 0);
+              mma_ss<KIND>(tmem_base + acc * kAccCols, da, db, idesc, kb != kb0 || kk != 0);
             }
             mma_commit(smem_u32(&ctl->empty[stage]));
-            if (kb == kblocks - 1) mma_commit(smem_u32(&ctl->acc_full[acc]));
+            if (kb == kb1 - 1) mma_commit(smem_u32(&ctl->acc_full[acc]));
           }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -200,9 +216,11 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     uint32_t acc_phase = 0;
     bool ok = true;
     const bool reference = p.epilogue == QWX_EPI_REFERENCE;
+    uint32_t epi_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * BM;
-      const int n0 = (tile / p.tiles_m) * BN;
+      const int t = tile / p.splits;
+      const int m0 = (t % p.tiles_m) * BM;
+      const int n0 = (t / p.tiles_m) * BN;
       // Each warp stages this tile's column scales for itself (no cross-warp barrier, so a
       // warp that gives up on a wait cannot strand the others).
       for (int j = lane; j < BN; j += 32) {
@@ -218,14 +236,8 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
 
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * kAccCols + c * 32, r);
-        tmem_ld_wait();
-        const int64_t ncol = (int64_t)n0 + c * 32;
-        if (m >= p.M || ncol >= p.N) continue;
-        const float* sbv = &ctl->sb[q][acc][c * 32];
+      // Scale, convert and store 32 consecutive columns of row m (r: raw accumulator bits).
+      auto emit32 = [&](const uint32_t (&r)[32], int64_t m, float sa, int64_t ncol, const float* sbv) {
         if (p.out_dtype == QWX_S32) {
           int32_t* o = reinterpret_cast<int32_t*>(p.out) + m * p.N + ncol;
           if (ncol + 32 <= p.N && (p.N & 3) == 0) {
@@ -235,7 +247,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           } else {
             for (int j = 0; j < 32 && ncol + j < p.N; ++j) o[j] = (int32_t)r[j];
           }
-          continue;
+          return;
         }
         float v[32];
 #pragma unroll
@@ -281,10 +293,84 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               o[j] = (uint16_t)(w[j >> 1] >> ((j & 1) * 16));
           }
         }
+      };
+
+      // Split-K: this item's partial sums go to a private slab, laid out as the accumulator
+      // comes out of tensor memory ([column][tile row]) so that every store is coalesced.
+      uint32_t* slab = nullptr;
+      if (p.splits > 1)
+        slab = p.ws + ((size_t)(tile % p.splits) * (p.tiles_m * p.tiles_n) + t) * (size_t)(BM * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * kAccCols + c * 32, r);
+        tmem_ld_wait();
+        const int64_t ncol = (int64_t)n0 + c * 32;
+        if (m >= p.M || ncol >= p.N) continue;
+        if (p.splits == 1) {
+          emit32(r, m, sa, ncol, &ctl->sb[q][acc][c * 32]);
+        } else {
+          uint32_t* w = slab + (size_t)(c * 32) * BM + q * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) __stcg(w + j * BM, r[j]);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+
+      if (p.splits > 1) {
+        // Count this K range for the tile.  The CTA that completes the tile adds the ranges'
+        // slabs in range order (so float sums do not depend on timing) and runs the ordinary
+        // epilogue; (row group, column chunk) pairs are dealt round-robin to the four warps.
+        __threadfence();
+        mbar_arrive(smem_u32(&ctl->epi_done));
+        if (q == 0 && lane == 0) {
+          bool done = mbar_wait(smem_u32(&ctl->epi_done), epi_phase, abort);
+          if (done) {
+            const int old = atomicAdd(p.counters + t, 1);
+            __threadfence();
+            ctl->finalize = (old + 1 == p.splits) ? 1 : 0;
+            if (ctl->finalize) p.counters[t] = 0;
+          }
+          mbar_arrive(smem_u32(&ctl->fin_done));
+        }
+        if (lane == 0) ok = mbar_wait(smem_u32(&ctl->fin_done), epi_phase, abort);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        epi_phase ^= 1u;
+        if (!ok) break;
+        if (ctl->finalize) {
+          const int64_t rows_left = p.M - m0;
+          const int groups = (int)(rows_left >= BM ? BM / 32 : (rows_left + 31) / 32);
+          const size_t split_stride = (size_t)(p.tiles_m * p.tiles_n) * (size_t)(BM * BN);
+          const uint32_t* base = p.ws + (size_t)t * (size_t)(BM * BN);
+#pragma unroll 1
+          for (int u = q; u < groups * (BN / 32); u += 4) {
+            const int g = u % groups, c = u / groups;
+            const int64_t ncol = (int64_t)n0 + c * 32;
+            const int64_t mr = (int64_t)m0 + g * 32 + lane;
+            if (ncol >= p.N || mr >= p.M) continue;
+            const uint32_t* w = base + (size_t)(c * 32) * BM + g * 32 + lane;
+            uint32_t r[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __ldcg(w + j * BM);
+            for (int sp = 1; sp < p.splits; ++sp) {
+              w += split_stride;
+              uint32_t v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __ldcg(w + j * BM);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (KIND == MmaKind::kI8) r[j] += v[j];
+                else r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(v[j])));
+              }
+            }
+            const float sar = p.sa ? load_scale(p.sa, p.scale_dtype, mr) : 1.0f;
+            emit32(r, mr, sar, ncol, &ctl->sb[q][acc][c * 32]);
+          }
+        }
+        __syncwarp();
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -329,11 +415,33 @@ int sm_count() {
 
 using namespace qwx;
 
-extern "C" int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_layout, int64_t M,
-                           int64_t N, int64_t K, int64_t k_tile, const void* sa, int sa_tiled,
-                           const void* sb, int sb_tiled, int scale_dtype, void* out,
-                           int out_dtype, int epilogue, int32_t* error_flag,
-                           qwx_stream_t stream) {
+// Split-K is worth it when the tiles cannot occupy the SMs: cut K so that tiles x splits comes
+// close to the SM count, keeping at least four 128-wide K blocks per range.
+// The workspace opens with one int32 counter per tile (rounded up to 256 bytes), zero between
+// calls; the partial-sum slabs follow and need no initialisation.
+static size_t counter_bytes(int64_t tiles) { return ((size_t)tiles * 4 + 255) & ~(size_t)255; }
+
+static int choose_splits(int64_t tiles, int kblocks, int sms) {
+  if (tiles * 2 > sms) return 1;
+  int64_t s = sms / tiles;
+  if (s > kblocks / 4) s = kblocks / 4;
+  return s < 1 ? 1 : (int)s;
+}
+
+extern "C" size_t qwx_gemm_q8_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const int splits = choose_splits(tiles, (int)((K + BK - 1) / BK), sms);
+  if (splits == 1) return 0;
+  return counter_bytes(tiles) + (size_t)splits * tiles * BM * BN * 4;
+}
+
+static int gemm_q8_impl(const void* a, const void* b, int code_dtype, int b_layout, int64_t M,
+                        int64_t N, int64_t K, int64_t k_tile, const void* sa, int sa_tiled,
+                        const void* sb, int sb_tiled, int scale_dtype, void* out, int out_dtype,
+                        int epilogue, void* workspace, size_t workspace_bytes,
+                        int workspace_is_zero, int32_t* error_flag, qwx_stream_t stream) {
   if (!a || !b || !out) return QWX_ERR_NULL;
   if (M <= 0 || N <= 0 || K <= 0) return QWX_ERR_SHAPE;
   if (M > INT32_MAX - BM || N > INT32_MAX - BN || K > INT32_MAX - BK) return QWX_ERR_SHAPE;
@@ -375,16 +483,54 @@ extern "C" int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_l
   p.error_flag = error_flag;
   p.tiles_m = (int)((M + BM - 1) / BM);
   p.tiles_n = (int)((N + BN - 1) / BN);
-  const int64_t num_tiles = (int64_t)p.tiles_m * p.tiles_n;
-  if (num_tiles > INT32_MAX) return QWX_ERR_SHAPE;
+  int64_t num_tiles = (int64_t)p.tiles_m * p.tiles_n;
+  if (num_tiles > INT32_MAX / 64) return QWX_ERR_SHAPE;
   const int sms = sm_count();
   if (sms <= 0) return QWX_ERR_NO_DEVICE;
-  const int grid = (int)(num_tiles < sms ? num_tiles : sms);
   cudaStream_t st = (cudaStream_t)stream;
+  p.splits = 1;
+  p.ws = nullptr;
+  p.counters = nullptr;
+  if (workspace != nullptr) {
+    const int splits = choose_splits(num_tiles, (int)((K + BK - 1) / BK), sms);
+    if (splits > 1) {
+      const size_t need = counter_bytes(num_tiles) + (size_t)splits * num_tiles * BM * BN * 4;
+      if (workspace_bytes < need) return QWX_ERR_WORKSPACE;
+      if (reinterpret_cast<uintptr_t>(workspace) & 15) return QWX_ERR_ALIGN;
+      if (!workspace_is_zero &&
+          cudaMemsetAsync(workspace, 0, counter_bytes(num_tiles), st) != cudaSuccess)
+        return QWX_ERR_LAUNCH;
+      p.splits = splits;
+      p.counters = (int*)workspace;
+      p.ws = (uint32_t*)((char*)workspace + counter_bytes(num_tiles));
+      num_tiles *= splits;
+    }
+  }
+  const int grid = (int)(num_tiles < sms ? num_tiles : sms);
   if (code_dtype == QWX_S8) {
     return b_layout == QWX_B_NK ? launch<MmaKind::kI8, QWX_B_NK>(ta, tb, p, grid, st)
                                 : launch<MmaKind::kI8, QWX_B_KN>(ta, tb, p, grid, st);
   }
   return b_layout == QWX_B_NK ? launch<MmaKind::kF8F6F4, QWX_B_NK>(ta, tb, p, grid, st)
                               : launch<MmaKind::kF8F6F4, QWX_B_KN>(ta, tb, p, grid, st);
+}
+
+extern "C" int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_layout, int64_t M,
+                           int64_t N, int64_t K, int64_t k_tile, const void* sa, int sa_tiled,
+                           const void* sb, int sb_tiled, int scale_dtype, void* out,
+                           int out_dtype, int epilogue, int32_t* error_flag,
+                           qwx_stream_t stream) {
+  return gemm_q8_impl(a, b, code_dtype, b_layout, M, N, K, k_tile, sa, sa_tiled, sb, sb_tiled,
+                      scale_dtype, out, out_dtype, epilogue, nullptr, 0, 0, error_flag, stream);
+}
+
+extern "C" int qwx_gemm_q8_ws(const void* a, const void* b, int code_dtype, int b_layout, int64_t M,
+                              int64_t N, int64_t K, int64_t k_tile, const void* sa, int sa_tiled,
+                              const void* sb, int sb_tiled, int scale_dtype, void* out,
+                              int out_dtype, int epilogue, void* workspace,
+                              size_t workspace_bytes, int workspace_is_zero, int32_t* error_flag,
+                              qwx_stream_t stream) {
+  return gemm_q8_impl(a, b, code_dtype, b_layout, M, N, K, k_tile, sa, sa_tiled, sb, sb_tiled,
+                      scale_dtype, out, out_dtype, epilogue, workspace, workspace_bytes,
+                      workspace_is_zero, error_flag, stream);
 }

@@ -30,6 +30,89 @@ def _raw_gemm(a: torch.Tensor, b: torch.Tensor, layout: int, code=_lib.S8, out_d
   return out
 
 
+def _splitk_gemm(a, b, layout, code=_lib.S8, out_dtype=torch.int32, sa=None, sb=None, ws=None):
+  """The workspace form; returns (out, workspace) so a test can reuse the buffer."""
+  M, K = a.shape
+  N = b.shape[1] if layout == _lib.B_KN else b.shape[0]
+  L = _lib.lib()
+  need = L.qwx_gemm_q8_workspace_bytes(M, N, K)
+  if ws is None:
+    ws = torch.zeros(max(need, 16), dtype=torch.uint8, device='cuda')
+  out = torch.empty((M, N), dtype=out_dtype, device='cuda')
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  oc = {torch.int32: _lib.S32, torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}[out_dtype]
+  _lib.check(L.qwx_gemm_q8_ws(_lib.ptr(a), _lib.ptr(b), code, layout, M, N, K, 0, _lib.ptr(sa), 0,
+                              _lib.ptr(sb), 0, _lib.F32, _lib.ptr(out), oc, 0, _lib.ptr(ws), need,
+                              1, _lib.ptr(err), _lib.stream_ptr()), 'gemm_ws')
+  torch.cuda.synchronize()
+  assert int(err.item()) == 0
+  return out, ws, need
+
+
+DECODE_SHAPES = [(32, 4096, 4096), (1, 1024, 14336), (8, 6144, 4096), (33, 512 + 32, 2048 + 128),
+                 (128, 2048, 8192), (160, 256, 16384)]
+
+
+@pytest.mark.parametrize('layout', [_lib.B_NK, _lib.B_KN], ids=['b_nk', 'b_kn'])
+@pytest.mark.parametrize('mnk', DECODE_SHAPES, ids=[f'{m}x{n}x{k}' for m, n, k in DECODE_SHAPES])
+def test_split_k_int8_bit_exact_and_workspace_reusable(mnk, layout):
+  M, N, K = mnk
+  rng = np.random.default_rng(M + N + K)
+  a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+  b = rng.integers(-128, 128, (K, N), dtype=np.int8)
+  want = a.astype(np.int32) @ b.astype(np.int32)
+  bt = h.to_torch(b if layout == _lib.B_KN else np.ascontiguousarray(b.T))
+  at = h.to_torch(a)
+  got, ws, need = _splitk_gemm(at, bt, layout)
+  assert need > 0, 'shape was expected to be cut along K'
+  assert np.array_equal(got.cpu().numpy(), want)
+  # second call on the same, uncleared workspace; scaled bf16 output equals the unsplit kernel
+  sa = torch.rand(M, device='cuda') + 0.5
+  sb = torch.rand(N, device='cuda') * 1e-3
+  got2, ws, _ = _splitk_gemm(at, bt, layout, out_dtype=torch.bfloat16, sa=sa, sb=sb, ws=ws)
+  ref = torch.empty_like(got2)
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  _lib.check(_lib.lib().qwx_gemm_q8(_lib.ptr(at), _lib.ptr(bt), _lib.S8, layout, M, N, K, 0,
+                                    _lib.ptr(sa), 0, _lib.ptr(sb), 0, _lib.F32, _lib.ptr(ref),
+                                    _lib.BF16, 0, _lib.ptr(err), _lib.stream_ptr()), 'gemm')
+  torch.cuda.synchronize()
+  assert torch.equal(got2.view(torch.int16), ref.view(torch.int16))
+  tiles = -(-M // 128) * -(-N // 256)
+  assert int(ws[:tiles * 4].count_nonzero().item()) == 0   # tile counters are left zero
+
+
+def test_split_k_fp8():
+  M, N, K = 16, 1024, 4096
+  rng = np.random.default_rng(5)
+  import ml_dtypes
+  a = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+  b = rng.standard_normal((N, K)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+  want = a.astype(np.float32) @ b.astype(np.float32).T
+  got, ws, need = _splitk_gemm(h.to_torch(a), h.to_torch(b), _lib.B_NK, code=_lib.E4M3,
+                               out_dtype=torch.float32)
+  assert need > 0
+  assert np.abs(got.cpu().numpy() - want).max() <= 1e-3 * np.abs(want).max()
+  again, _, _ = _splitk_gemm(h.to_torch(a), h.to_torch(b), _lib.B_NK, code=_lib.E4M3,
+                             out_dtype=torch.float32, ws=ws)
+  assert torch.equal(got, again)   # partial sums are added in a fixed order
+
+
+def test_split_k_workspace_query_and_errors():
+  L = _lib.lib()
+  assert L.qwx_gemm_q8_workspace_bytes(4096, 8192, 8192) == 0      # enough tiles already
+  assert L.qwx_gemm_q8_workspace_bytes(32, 4096, 256) == 0         # K too short to cut
+  need = L.qwx_gemm_q8_workspace_bytes(32, 4096, 4096)
+  assert need == 256 + 8 * 16 * 128 * 256 * 4, need   # 16 tiles, K cut in 8
+  a = torch.zeros((32, 4096), dtype=torch.int8, device='cuda')
+  b = torch.zeros((4096, 4096), dtype=torch.int8, device='cuda')
+  out = torch.empty((32, 4096), dtype=torch.int32, device='cuda')
+  ws = torch.zeros(need, dtype=torch.uint8, device='cuda')
+  rc = L.qwx_gemm_q8_ws(_lib.ptr(a), _lib.ptr(b), _lib.S8, _lib.B_NK, 32, 4096, 4096, 0, None, 0,
+                        None, 0, _lib.F32, _lib.ptr(out), _lib.S32, 0, _lib.ptr(ws), need - 4, 1,
+                        None, _lib.stream_ptr())
+  assert rc == 6  # QWX_ERR_WORKSPACE
+
+
 SHAPES = [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (384, 768, 4096),
           (100, 200 + 8, 256 + 16), (1, 16, 128), (130, 272, 144), (512, 1024, 8192)]
 
