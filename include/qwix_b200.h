@@ -172,6 +172,33 @@ int qwx_gemm_q8_ws(const void* a, const void* b, int code_dtype, int b_layout,
                    void* workspace, size_t workspace_bytes, int workspace_is_zero,
                    int32_t* error_flag, qwx_stream_t stream);
 
+/* The general dequantize-on-output contraction of dot_general._fast_dot_general
+ * (dot_general.py:135-261): scales that change along K (sub-channel quantization, the tiled
+ * contracting axis of :187-203 and the tile sum of :259) and the zero-point correction of an
+ * asymmetric operand (:228-253), all inside one kernel:
+ *   out[m, n] = sum_t ( acc_t[m, n] - corr_row[m, t] * corr_col[t, n] ) * sa[m, t] * sb[t, n]
+ * with acc_t the integer (or float32, for e4m3 codes) dot over K tile t.  T = K / k_tile tiles;
+ * k_tile is a multiple of 128, or 0 / K for a single tile.  sa: [M, T] if sa_tiled else [M];
+ * sb: [T, N] if sb_tiled else [N]; either may be NULL.  corr_row [M, T] and corr_col [T, N]
+ * are int32 and given together or not at all (int8 codes only):
+ *   asymmetric a (zero point za[m, t]):  corr_row = za,           corr_col = column sums of b
+ *   asymmetric b (zero point zb[t, n]):  corr_row = row sums of a, corr_col = zb
+ * the sums taken over each K tile (qwx_code_sums).  out_dtype QWX_BF16 / QWX_F32 / QWX_F16.
+ * qwx_gemm_q8 forwards here when k_tile cuts K. */
+int qwx_gemm_q8_tiled(const void* a, const void* b, int code_dtype, int b_layout,
+                      int64_t M, int64_t N, int64_t K, int64_t k_tile,
+                      const void* sa, int sa_tiled, const void* sb, int sb_tiled,
+                      int scale_dtype, const int32_t* corr_row, const int32_t* corr_col,
+                      void* out, int out_dtype, int epilogue, int32_t* error_flag,
+                      qwx_stream_t stream);
+
+/* Sums of int8 codes over each K tile, the integer dot of the other operand with a broadcast
+ * zero point (dot_general.py:233, :246) reduced to what it is: a row or column sum.
+ * k_axis = 1: codes [rows, cols = K]; k_axis = 0: codes [rows = K, cols].  k_tile = 0 means K.
+ * out is int32 [T, other] if t_major else [other, T], other being the non-K extent. */
+int qwx_code_sums(const void* codes, int64_t rows, int64_t cols, int k_axis, int64_t k_tile,
+                  int t_major, int32_t* out, qwx_stream_t stream);
+
 /* Weight-only int4 GEMM, the fused form of dot_general._slow_dot_general
  * (dot_general.py:264-275, chosen at :444-452 when the activation is not quantized):
  *   out[m, n] = sum_k a[m, k] * bf16( q[k, n] * scale[k / k_tile, n] )

@@ -55,6 +55,9 @@ _SIGNATURES = {
                                  _int, _vp, _sz, _vp, _vp]),
     'qwx_gemm_q8': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,
                            _int, _vp, _int, _int, _vp, _vp]),
+    'qwx_gemm_q8_tiled': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,
+                                 _int, _vp, _vp, _vp, _int, _int, _vp, _vp]),
+    'qwx_code_sums': (_int, [_vp, _i64, _i64, _int, _i64, _int, _vp, _vp]),
     'qwx_gemm_q8_workspace_bytes': (_sz, [_i64, _i64, _i64]),
     'qwx_gemm_q8_ws': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,
                               _int, _vp, _int, _int, _vp, _sz, _int, _vp, _vp]),

@@ -83,24 +83,55 @@ def _out_code(dtype: torch.dtype) -> int:
   return table[dtype]
 
 
-def _codes_and_scale(x, contracting, batch, free, side: str):
-  """Returns (codes [B, free, K] or [B, K, free] view info, scale [B, free] or None)."""
+def _along_k(aux: torch.Tensor, x: QArray, contracting, batch, free):
+  """Lays a scale (or zero point) of `x` out as [B, F, T]: batch axes, free axes (expanded to
+  the operand's extents) and the contracting axes flattened into T tiles of the flattened K.
+
+  K is the contracting axes flattened in the given order.  With j the last contracting axis
+  along which the scale varies, one run of K that shares a scale is the tile of axis j times
+  the extents of the later axes, and the runs are numbered by (earlier axes, tile of j).
+  Returns (tensor [B, F, T], k_tile) with k_tile == K when T == 1.
+  """
+  dims = [x.qvalue.shape[a] for a in contracting]
+  sdims = [aux.shape[a] for a in contracting]
+  K = math.prod(dims)
+  full = [x.qvalue.shape[a] for a in list(batch) + list(free)]
+  t = aux.permute(list(batch) + list(free) + list(contracting))
+  t = t.expand(full + sdims)
+  varying = [i for i, n in enumerate(sdims) if n > 1]
+  if not varying:
+    return t.reshape(math.prod(full[:len(batch)]), math.prod(full[len(batch):]), 1), K
+  j = varying[-1]
+  for i in range(j):          # earlier axes: one run per index
+    if sdims[i] != dims[i]:
+      t = t.repeat_interleave(dims[i] // sdims[i], dim=len(full) + i)
+  t = t.reshape(full + [-1])  # later axes have extent 1
+  k_tile = (dims[j] // sdims[j]) * math.prod(dims[j + 1:])
+  return t.reshape(math.prod(full[:len(batch)]), math.prod(full[len(batch):]), K // k_tile), k_tile
+
+
+def _operand(x, contracting, batch, free):
+  """Returns (codes, qtype name, scale [B, F, T] | None, zero point [B, F, T] | None, k_tile)."""
   if isinstance(x, QArray):
+    scale, k_tile = _along_k(x.scale, x, contracting, batch, free)
+    zp = None
     if x.zero_point is not None:
-      raise NotImplementedError(
-          'asymmetric operands on the dequantize-on-output path are not built yet.')
-    for a in contracting:
-      if x.scale.shape[a] != 1:
-        raise NotImplementedError(
-            'sub-channel scales along a contracting axis are not built yet for the '
-            'tensor-core path.')
-    full = [x.qvalue.shape[a] for a in list(batch) + list(free)]
-    scale = x.scale.permute(list(batch) + list(free) + list(contracting))
-    scale = scale.reshape([x.scale.shape[a] for a in list(batch) + list(free)])
-    scale = scale.expand(full).reshape(
-        math.prod(full[:len(batch)]), math.prod(full[len(batch):])).contiguous()
-    return x.qvalue, scale, x.qtype
-  return x, None, numerics.qtype_name(x.dtype)
+      zp, zk = _along_k(x.zero_point, x, contracting, batch, free)
+      if zk != k_tile:   # zero point and scale share one shape in a valid QArray
+        raise ValueError('zero_point and scale must have the same shape.')
+    return x.qvalue, x.qtype, scale, zp, k_tile
+  K = math.prod(x.shape[a] for a in contracting)
+  return x, numerics.qtype_name(x.dtype), None, None, K
+
+
+def _refine(t: torch.Tensor | None, k_from: int, k_to: int) -> torch.Tensor | None:
+  """Repeats per-tile values [B, F, T] for a finer tiling of K."""
+  if t is None or k_from == k_to or t.shape[-1] == 1:
+    return t
+  return t.repeat_interleave(k_from // k_to, dim=-1)
+
+
+_INT_CODES = ('int8', 'int4')
 
 
 def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
@@ -123,12 +154,15 @@ def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
   acc_t, res_t = qarray.get_accumulator_and_result_type(
       lhs, rhs, preferred_element_type=preferred_element_type)
 
-  lq, ls, lname = _codes_and_scale(lhs, lca, lba, lfa, 'lhs')
-  rq, rs, rname = _codes_and_scale(rhs, rca, rba, rfa, 'rhs')
-  if lname != rname or lname not in ('int8', 'float8_e4m3fn'):
+  lq, lname, ls, lz, lk = _operand(lhs, lca, lba, lfa)
+  rq, rname, rs, rz, rk = _operand(rhs, rca, rba, rfa)
+  if lname in _INT_CODES and rname in _INT_CODES and lq.dtype == rq.dtype == torch.int8:
+    code = _lib.S8     # int4 codes are small int8 values to the tensor cores
+  elif lname == rname == 'float8_e4m3fn':
+    code = _lib.E4M3
+  else:
     raise NotImplementedError(
-        f'tensor-core path needs int8 x int8 or e4m3 x e4m3 codes, got {lname} x {rname}.')
-  code = _lib.S8 if lname == 'int8' else _lib.E4M3
+        f'tensor-core path needs int8/int4 x int8/int4 or e4m3 x e4m3 codes, got {lname} x {rname}.')
   _lib.require_cuda(lq, rq)
 
   bshape = [lq.shape[a] for a in lba]
@@ -136,6 +170,16 @@ def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
   nshape = [rq.shape[a] for a in rfa]
   B, M, N = math.prod(bshape), math.prod(mshape), math.prod(nshape)
   K = math.prod(lq.shape[a] for a in lca)
+  k_tile = min(lk, rk)
+  if max(lk, rk) % k_tile:
+    raise ValueError(f'K tiles of {lk} and {rk} do not nest.')
+  if k_tile != K and k_tile % 128:
+    raise NotImplementedError(
+        f'the tensor-core path takes scale tiles that are multiples of 128 along K, got {k_tile}.')
+  ls, lz = _refine(ls, lk, k_tile), _refine(lz, lk, k_tile)
+  rs, rz = _refine(rs, rk, k_tile), _refine(rz, rk, k_tile)
+  T = K // k_tile
+
   a3 = lq.permute(lba + lfa + lca).reshape(B, M, K).contiguous()
   # Use the weight where it lies: [.., K, N] order needs no repack (MN-major operand).
   kn = rq.permute(rba + rca + rfa)
@@ -148,28 +192,55 @@ def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
     b3, layout = nk.reshape(B, N, K).contiguous(), _lib.B_NK
 
   scale_dt = None
-  for s in (ls, rs):
-    if s is not None:
-      scale_dt = s.dtype if scale_dt is None else torch.promote_types(scale_dt, s.dtype)
-  if scale_dt is not None:
-    ls = None if ls is None else ls.to(scale_dt)
-    rs = None if rs is None else rs.to(scale_dt)
+  for sc in (ls, rs):
+    if sc is not None:
+      scale_dt = sc.dtype if scale_dt is None else torch.promote_types(scale_dt, sc.dtype)
+  # Kernel layouts: a-side values [B, M, T], b-side values [B, T, N].
+  ls = None if ls is None else ls.to(scale_dt).contiguous()
+  rs = None if rs is None else rs.to(scale_dt).transpose(1, 2).contiguous()
+  scale_code = numerics.code_of_float(scale_dt) if scale_dt is not None else _lib.F32
   raw = ls is None and rs is None and code == _lib.S8
   out_t = torch.int32 if raw else res_t
   out = torch.empty((B, M, N), dtype=out_t, device=lq.device)
   err = torch.zeros(1, dtype=torch.int32, device=lq.device)
   epi = _lib.EPI_REFERENCE if EPILOGUE == 'reference' else _lib.EPI_F32
   L = _lib.lib()
-  ws_bytes = L.qwx_gemm_q8_workspace_bytes(M, N, K)
-  ws = _splitk_workspace(lq.device, ws_bytes) if ws_bytes else None
-  for b in range(B):
-    _lib.check(L.qwx_gemm_q8_ws(
-        _lib.ptr(a3[b]), _lib.ptr(b3[b]), code, layout, M, N, K, 0,
-        _lib.ptr(None if ls is None else ls[b]), 0,
-        _lib.ptr(None if rs is None else rs[b]), 0,
-        numerics.code_of_float(scale_dt) if scale_dt is not None else _lib.F32,
-        _lib.ptr(out[b]), _out_code(out_t), epi, _lib.ptr(ws), ws_bytes, 1, _lib.ptr(err),
-        _lib.stream_ptr(lq.device)), 'dot_general')
+  stream = _lib.stream_ptr(lq.device)
+
+  if T > 1 or lz is not None or rz is not None:
+    if raw:
+      raise NotImplementedError('raw accumulators of a tiled contraction are not offered.')
+    corr_row = corr_col = None
+    if lz is not None:      # dot_general.py:228-240
+      corr_row = lz.to(torch.int32).expand(B, M, T).contiguous()
+      corr_col = torch.empty((B, T, N), dtype=torch.int32, device=lq.device)
+    elif rz is not None:    # dot_general.py:241-253
+      corr_col = rz.to(torch.int32).expand(B, N, T).transpose(1, 2).contiguous()
+      corr_row = torch.empty((B, M, T), dtype=torch.int32, device=lq.device)
+    for b in range(B):
+      if lz is not None:
+        rows, cols, k_axis = (N, K, 1) if layout == _lib.B_NK else (K, N, 0)
+        _lib.check(L.qwx_code_sums(_lib.ptr(b3[b]), rows, cols, k_axis, k_tile, 1,
+                                   _lib.ptr(corr_col[b]), stream), 'code_sums')
+      elif rz is not None:
+        _lib.check(L.qwx_code_sums(_lib.ptr(a3[b]), M, K, 1, k_tile, 0,
+                                   _lib.ptr(corr_row[b]), stream), 'code_sums')
+      _lib.check(L.qwx_gemm_q8_tiled(
+          _lib.ptr(a3[b]), _lib.ptr(b3[b]), code, layout, M, N, K, k_tile,
+          _lib.ptr(None if ls is None else ls[b]), int(ls is not None and ls.shape[-1] > 1),
+          _lib.ptr(None if rs is None else rs[b]), int(rs is not None and rs.shape[1] > 1),
+          scale_code, _lib.ptr(None if corr_row is None else corr_row[b]),
+          _lib.ptr(None if corr_col is None else corr_col[b]), _lib.ptr(out[b]),
+          _out_code(out_t), epi, _lib.ptr(err), stream), 'dot_general')
+  else:
+    ws_bytes = L.qwx_gemm_q8_workspace_bytes(M, N, K)
+    ws = _splitk_workspace(lq.device, ws_bytes) if ws_bytes else None
+    for b in range(B):
+      _lib.check(L.qwx_gemm_q8_ws(
+          _lib.ptr(a3[b]), _lib.ptr(b3[b]), code, layout, M, N, K, 0,
+          _lib.ptr(None if ls is None else ls[b]), 0, _lib.ptr(None if rs is None else rs[b]), 0,
+          scale_code, _lib.ptr(out[b]), _out_code(out_t), epi, _lib.ptr(ws), ws_bytes, 1,
+          _lib.ptr(err), stream), 'dot_general')
   out = out.reshape(bshape + mshape + nshape)
   return out if out.dtype == res_t else out.to(res_t)
 

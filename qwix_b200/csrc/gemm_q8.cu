@@ -447,10 +447,10 @@ static int gemm_q8_impl(const void* a, const void* b, int code_dtype, int b_layo
   if (M > INT32_MAX - BM || N > INT32_MAX - BN || K > INT32_MAX - BK) return QWX_ERR_SHAPE;
   if (code_dtype != QWX_S8 && code_dtype != QWX_E4M3) return QWX_ERR_DTYPE;
   if (b_layout != QWX_B_KN && b_layout != QWX_B_NK) return QWX_ERR_SHAPE;
-  if (k_tile != 0 && k_tile != K) {
-    (void)sa_tiled; (void)sb_tiled;
-    return QWX_ERR_UNSUPPORTED;  // per-K-tile scales: not built yet
-  }
+  if (k_tile != 0 && k_tile != K)  // scales change along K: the kernel with running sums
+    return qwx_gemm_q8_tiled(a, b, code_dtype, b_layout, M, N, K, k_tile, sa, sa_tiled, sb, sb_tiled,
+                             scale_dtype, nullptr, nullptr, out, out_dtype, epilogue, error_flag,
+                             stream);
   if (out_dtype == QWX_S32) {
     if (code_dtype != QWX_S8 || sa || sb) return QWX_ERR_DTYPE;
   } else if (out_dtype != QWX_BF16 && out_dtype != QWX_F32 && out_dtype != QWX_F16) {

@@ -1,5 +1,7 @@
 """GPU parity: tcgen05 quantized GEMM (through the C ABI) vs the CPU oracle."""
 
+import dataclasses
+
 import numpy as np
 import pytest
 import torch
@@ -175,3 +177,156 @@ def test_w8a8_dot_general_matches_oracle(qtype, dtype):
     finally:
       bdg.EPILOGUE = old
     assert np.array_equal(h.to_numpy(exact).view(np.uint8), want.view(np.uint8))
+
+
+# ---------------------------------------------------------------------------------------------
+# Scales that change along K (sub-channel tiles) and asymmetric operands: the general form of
+# the reference's dequantize-on-output contraction (dot_general.py:187-259).
+
+def _quantize_pair(x, w, dn, l_kw, r_kw):
+  ndims = (x.ndim, w.ndim)
+  lo = oq.quantize(x, odg.get_how_to_quantize(dimension_numbers=dn, ndims=ndims, for_lhs=True, **l_kw))
+  ro = oq.quantize(w, odg.get_how_to_quantize(dimension_numbers=dn, ndims=ndims, for_lhs=False, **r_kw))
+  lb = bq.quantize(h.to_torch(x), bdg.get_how_to_quantize(dimension_numbers=dn, ndims=ndims, for_lhs=True, **l_kw))
+  rb = bq.quantize(h.to_torch(w), bdg.get_how_to_quantize(dimension_numbers=dn, ndims=ndims, for_lhs=False, **r_kw))
+  assert h.codes_equal(lb.qvalue, lo.qvalue) and h.codes_equal(rb.qvalue, ro.qvalue)
+  return lo, ro, lb, rb
+
+
+def _close(got, want):
+  g = h.to_numpy(got).astype(np.float32)
+  r = np.asarray(want).astype(np.float32)
+  assert g.shape == r.shape
+  # tolerance stated for dequantized outputs: max-abs 1e-2 or relative 2e-2
+  bad = np.abs(g - r) > 1e-2 + 2e-2 * np.abs(r)
+  assert not bad.any(), f'{bad.sum()} of {bad.size} outside tolerance; worst {np.abs(g - r).max()}'
+
+
+TILED_CASES = [
+    # (M, K, N, lhs tile, rhs tile, qtype, dtype)
+    (192, 1024, 384, 128, 128, 'int8', 'float32'),
+    (192, 1024, 384, 256, 256, 'int8', 'bfloat16'),
+    (200, 1024, 264, None, 128, 'int8', 'float32'),      # per-row activations, sub-channel weight
+    (64, 2048, 512, 512, None, 'int8', 'bfloat16'),
+    (130, 1024, 256, 128, 128, 'float8_e4m3fn', 'float32'),
+]
+
+
+@pytest.mark.parametrize('case', TILED_CASES, ids=[str(c) for c in TILED_CASES])
+def test_tiled_scales_match_oracle(case):
+  M, K, N, lt, rt, qtype, dtype = case
+  rng = np.random.default_rng(M + K + N)
+  x = rng.standard_normal((M, K)).astype(np.float32)
+  x[:, rng.choice(K, 8, replace=False)] *= 12
+  w = (0.05 * rng.standard_normal((K, N))).astype(np.float32)
+  x, w = x.astype(h.np_dtype(dtype)), w.astype(h.np_dtype(dtype))
+  lo, ro, lb, rb = _quantize_pair(x, w, DN, dict(tile_size=lt, qtype=qtype),
+                                  dict(tile_size=rt, qtype=qtype))
+  assert bdg.use_fast_path(lb, rb, DN)
+  want = odg.dot_general(lo, ro, DN)
+  got = bdg.dot_general(lb, rb, DN)
+  assert got.dtype == h.to_torch(np.asarray(want)[:1]).dtype
+  if dtype == 'float32':
+    _close(got, want)
+  else:
+    # The reference rounds every tile's product to bfloat16 three times before the tile sum,
+    # so its own result carries a few bfloat16 ulps of the largest tile term.  The float32
+    # epilogue is held to the stated tolerance against the same contraction with float32
+    # scales; the reference-order epilogue is held to the oracle itself.
+    wide = lambda q: dataclasses.replace(q, scale=q.scale.astype(np.float32))
+    _close(got, odg.dot_general(wide(lo), wide(ro), DN))
+    old = bdg.EPILOGUE
+    try:
+      bdg.EPILOGUE = 'reference'
+      strict = h.to_numpy(bdg.dot_general(lb, rb, DN)).astype(np.float32)
+    finally:
+      bdg.EPILOGUE = old
+    w32 = np.asarray(want).astype(np.float32)
+    # the only freedom left is the order of the float32 tile sum: at most one bfloat16 ulp
+    assert np.all(np.abs(strict - w32) <= 2.0 ** -7 * np.maximum(np.abs(w32), 2.0 ** -6))
+    assert np.mean(strict == w32) > 0.98
+  # the loop form (one contraction per K tile, added in order) is the same kernel here
+  if lt == rt and dtype == 'float32':
+    _close(bdg.loop_dot_general(lb, rb, DN), odg.loop_dot_general(lo, ro, DN))
+
+
+@pytest.mark.parametrize('side', ['lhs', 'rhs'])
+@pytest.mark.parametrize('tile', [None, 128])
+def test_asymmetric_operand_matches_oracle(side, tile):
+  M, K, N = 160, 512, 272
+  rng = np.random.default_rng(7)
+  x = (rng.random((M, K)) * 3 + 1).astype(np.float32)           # far from symmetric
+  w = (0.05 * rng.standard_normal((K, N)) + 0.02).astype(np.float32)
+  sym = dict(tile_size=tile, qtype='int8')
+  asym = dict(tile_size=tile, qtype='int8', calibration_method='minmax')
+  lo, ro, lb, rb = _quantize_pair(x, w, DN, asym if side == 'lhs' else sym,
+                                  asym if side == 'rhs' else sym)
+  assert (lb.zero_point is not None) == (side == 'lhs')
+  assert (rb.zero_point is not None) == (side == 'rhs')
+  want = odg.dot_general(lo, ro, DN)
+  got = bdg.dot_general(lb, rb, DN)
+  _close(got, want)
+  # and the result approximates the float product much better than a symmetric int8 lhs would
+  ref = x @ w
+  assert np.abs(h.to_numpy(got) - ref).mean() / np.abs(ref).mean() < 2e-2
+
+
+def test_mismatched_tiles_raise():
+  x = np.random.default_rng(0).random((32, 768)).astype(np.float32)
+  w = np.random.default_rng(1).random((768, 32)).astype(np.float32)
+  _, _, lb, rb = _quantize_pair(x, w, DN, dict(tile_size=128, qtype='int8'),
+                                dict(tile_size=384, qtype='int8'))
+  with pytest.raises(ValueError, match='same tile size'):
+    bdg.dot_general(lb, rb, DN)
+
+
+def test_both_asymmetric_raises():
+  x = np.random.default_rng(0).random((32, 128)).astype(np.float32)
+  w = np.random.default_rng(1).random((128, 32)).astype(np.float32)
+  kw = dict(tile_size=None, qtype='int8', calibration_method='minmax')
+  _, _, lb, rb = _quantize_pair(x, w, DN, kw, kw)
+  with pytest.raises(ValueError, match='Only one operand can be asymmetric'):
+    bdg.dot_general(lb, rb, DN)
+
+
+def test_w4a8_sub_channel_matches_oracle():
+  """int4 weight codes with 128-wide tiles against int8 per-token activations."""
+  M, K, N = 48, 1024, 512
+  rng = np.random.default_rng(11)
+  x = rng.standard_normal((M, K)).astype(np.float32)
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32)
+  lo, ro, lb, rb = _quantize_pair(x, w, DN, dict(tile_size=None, qtype='int8'),
+                                  dict(tile_size=128, qtype='int4'))
+  _close(bdg.dot_general(lb, rb, DN), odg.dot_general(lo, ro, DN))
+
+
+def test_tiled_batched_einsum_shape():
+  """Batch axis plus two contracting axes, the last one tiled: K runs are numbered by
+  (first contracting axis, tile)."""
+  Bn, M, C1, C2, N = 2, 40, 2, 256, 64
+  rng = np.random.default_rng(3)
+  x = rng.standard_normal((Bn, M, C1, C2)).astype(np.float32)
+  w = (0.05 * rng.standard_normal((Bn, C1, C2, N))).astype(np.float32)
+  dn = (((2, 3), (1, 2)), ((0,), (0,)))
+  lo, ro, lb, rb = _quantize_pair(x, w, dn, dict(tile_size=128, qtype='int8'),
+                                  dict(tile_size=128, qtype='int8'))
+  _close(bdg.dot_general(lb, rb, dn), odg.dot_general(lo, ro, dn))
+
+
+@pytest.mark.parametrize('k_axis', [0, 1])
+@pytest.mark.parametrize('t_major', [0, 1])
+def test_code_sums(k_axis, t_major):
+  rng = np.random.default_rng(k_axis * 2 + t_major)
+  other, K, tile = 70, 512 + 128, 128
+  codes = rng.integers(-128, 128, (other, K) if k_axis == 1 else (K, other), dtype=np.int8)
+  T = K // tile
+  src = codes if k_axis == 1 else codes.T
+  want = src.astype(np.int32).reshape(other, T, tile).sum(-1)       # [other, T]
+  if t_major:
+    want = want.T
+  out = torch.empty(want.shape, dtype=torch.int32, device='cuda')
+  ct = h.to_torch(codes)
+  _lib.check(_lib.lib().qwx_code_sums(_lib.ptr(ct), codes.shape[0], codes.shape[1], k_axis, tile,
+                                      t_major, _lib.ptr(out), _lib.stream_ptr()), 'code_sums')
+  torch.cuda.synchronize()
+  assert np.array_equal(out.cpu().numpy(), want)
