@@ -42,9 +42,16 @@ def test_rotations_match_oracle(signed):
   assert np.abs(prod - ref).max() <= 2e-2 * np.abs(ref).max()
 
 
+# Rows of 1..32 blocks (a power of two) take the thread-per-block kernel, partial last
+# groups included; 3 and 40 blocks per row take the shuffle kernel.
+@pytest.mark.parametrize('shape', [(96, 4096), (3, 1024), (1000, 128), (70, 2048), (33, 256),
+                                   (50, 384), (20, 5120)],
+                         ids=lambda s: f'{s[0]}x{s[1]}')
 @pytest.mark.parametrize('qtype', ['float8_e4m3fn', 'int8'])
-def test_rotate_quantize_matches_oracle(qtype):
-  x = _student_t((96, 4096), 2)
+def test_rotate_quantize_matches_oracle(qtype, shape):
+  x = _student_t(shape, 2)
+  x[min(5, shape[0] - 1)] = 0          # an all-zero row: scale 1, codes 0
+  x[0, :7] *= 1e-30                    # values far below the row maximum
   got = bhd.hadamard_quantize(h.to_torch(x), qtype)
   rot = h.to_numpy(bhd.rotate_lhs(h.to_torch(x)))
   # Given the device's rotated array, scales and codes follow the absmax recipe bit for bit.
