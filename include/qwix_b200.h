@@ -201,14 +201,21 @@ int qwx_code_sums(const void* codes, int64_t rows, int64_t cols, int k_axis, int
 
 /* Weight-only int4 GEMM, the fused form of dot_general._slow_dot_general
  * (dot_general.py:264-275, chosen at :444-452 when the activation is not quantized):
- *   out[m, n] = sum_k a[m, k] * bf16( q[k, n] * scale[k / k_tile, n] )
- * a: bf16 [M, K], M <= 128.  The weight is given in the kernel's streaming layout, made once
- * by qwx_pack_w4 from the logical codes q[K, N] (QWX_S4U, one code per byte): units of
- * 128 channels x 128 K, 8 KB each, ordered [N / 128][K / 128].  scale: [K / k_tile, N] in f32
- * or bf16 (f32 scales are rounded to bf16 before the product), k_tile a multiple of 128.
- * K and N must be multiples of 128.  out: bf16 or f32 [M, N].
+ *   out[m, n] = sum_k a[m, k] * ( q[k, n] * scale[k / k_tile, n] )
+ * with the code products summed exactly per 128 K and the scale applied in float32.  For
+ * float32 scales this is the reference's dequantized weight (q * s is exact in float32); for
+ * bf16 scales the reference rounds q * s to bf16, which is not reproduced (the result is
+ * closer to the unquantized product, inside the output tolerance).
+ * a: bf16 [M, K], M <= 128 (the weight is streamed once per 32 tokens).  The weight is given
+ * in the kernel's streaming layout, made once by qwx_pack_w4 from the logical codes q[K, N]
+ * (QWX_S4U, one code per byte): 1 KB chunks of 16 channels x 128 K, ordered [N / 16][K / 128],
+ * each lane's 2 x 16 bytes holding its tensor-core fragment values.  scale: [K / k_tile, N]
+ * in f32 or bf16, k_tile a multiple of 128.  K must be a multiple of 128, N of 16.
+ * out: bf16 or f32 [M, N].
  * workspace: qwx_gemm_a16w4_workspace_bytes(M, N) bytes that must be zero when the kernel
- * starts; the kernel leaves them zero.  workspace_is_zero = 0 makes the call clear it first. */
+ * starts; the kernel leaves them zero.  workspace_is_zero = 0 makes the call clear it first.
+ * error_flag is accepted for symmetry with the other GEMMs; this kernel has no device-side
+ * waits and never writes it. */
 size_t qwx_w4_packed_bytes(int64_t K, int64_t N);
 int qwx_pack_w4(const void* q, int64_t K, int64_t N, void* packed, qwx_stream_t stream);
 size_t qwx_gemm_a16w4_workspace_bytes(int64_t M, int64_t N);

@@ -37,7 +37,7 @@ def eligible(lhs, rhs, dimension_numbers) -> bool:
     return False
   K, N = rhs.shape
   sk, sn = rhs.scale.shape
-  if sn != N or K % 128 or N % 128 or K % sk or (K // sk) % 128:
+  if sn != N or K % 128 or N % 16 or K % sk or (K // sk) % 128:
     return False
   rows = lhs.numel() // K
   return 0 < rows <= _MAX_FUSED_ROWS and lhs.is_cuda

@@ -2,433 +2,352 @@
 // side of dot_general._slow_dot_general (dot_general.py:264-275) for a bf16 activation and an
 // int4 sub-channel-quantized weight,
 //
-//   out[m, n] = sum_k a[m, k] * W~[k, n],   W~[k, n] = bf16( q[k, n] * s[k / tile, n] )
+//   out[m, n] = sum_k a[m, k] * W~[k, n],   W~[k, n] = q[k, n] * s[k / tile, n]
 //
 // without ever writing W~ to global memory.  The kernel is HBM-bound on the packed weight:
-// K*N/2 bytes are streamed exactly once.
+// K*N/2 bytes are streamed exactly once, every warp reading its own contiguous run.
 //
-// Operands are swapped so that the 128 output channels of a tile are the M dimension of
-// tcgen05.mma (kind::f16, bf16 x bf16 -> f32 in tensor memory) and the (padded) token count is
-// its N dimension.  Work is cut into units of (128 channels x 128 K) and dealt to one
-// persistent CTA per SM as contiguous ranges (stream-K), so all SMs stream for the same time;
-// a tile split between CTAs is summed with float atomics in a caller-provided workspace and
-// converted by the CTA that contributes last.
+// Design.  With 1..64 tokens the arithmetic is small; what decides the time is how little
+// happens per weight byte besides the load.  A CTA-wide tcgen05 pipeline (operand tiles in
+// shared memory, one MMA-issuing thread, mbarrier hand-overs per 8 KB of weights) was measured
+// at 80-90 us for 8192 x 28672 whatever the payload: each hand-over costs about 200 cycles of
+// a single thread and a 128 x 128 unit needs several.  Here nothing is handed over: every warp
+// owns a contiguous range of (16-channel strip, 64-wide K chunk) work items (stream-K at warp
+// granularity), loads its packed codes straight into registers (128-bit loads, eight in
+// flight per lane), converts them in registers into the A fragments of warp-level
+// mma.sync.m16n8k16 (channels are the MMA's M, tokens its N), and takes the B fragments with
+// ldmatrix from the activation slice that the CTA keeps resident in shared memory.  The weight
+// layout is made for this by qwx_pack_w4: a lane's 16 bytes hold exactly its fragment values
+// for four consecutive K tiles, so a warp's load is one contiguous 512-byte line.
 //
-//   warps 4-15    weight stream + unpack, in up to three groups of four warps that take the
-//                 units round-robin: every thread owns one channel row (64 bytes, 128 codes) of
-//                 its group's units and keeps three of them in flight with 16-byte
-//                 cp.async copies into a private slice of a shared-memory ring (the LSU path: a
-//                 single TMA bulk stream per SM was measured at a third of the HBM rate); then
-//                 int4 -> bf16 (magic-number conversion), scale, store into the swizzled
-//                 K-major operand layout; group 0 also runs the epilogue of each tile segment
-//   warp 0        TMA tile loads of the activations (small, L2-resident), one per unit
-//   warps 1-3     MMA issuers (8 x M128 N{16..128} K16 per unit), units taken round-robin;
-//                 warp 1 also owns the tensor-memory allocation
+// The tensor cores multiply the activation with the integer codes themselves (exact in bf16);
+// every 128 K the float32 partial sums are multiplied by the channel's scale and added to the
+// running sums.  With float32 scales this is the reference's arithmetic up to the order of the
+// float32 sums (its dequantized weight q * s is exact in float32); with bf16 scales the
+// reference rounds q * s to bf16 first, which this kernel does not reproduce -- it is closer to
+// the unquantized product, within the stated output tolerance.
+//
+// K is cut into `split` slices so that the activation slice (tokens x K / split, bf16) fits
+// shared memory; CTA c works on slice c % split.  A strip whose chunks are spread over several
+// warps (always the case when split > 1) is summed with float atomics in a caller-provided
+// zeroed workspace; the warp that contributes last converts it and clears the workspace.
 #include "common.cuh"
-#include "sm100.cuh"
 #include <algorithm>
 
 namespace qwx {
 namespace {
 
-using namespace sm100;
-
-constexpr int W4_BN = 128;          // channels per tile
-constexpr int W4_BK = 128;          // K per unit
-constexpr int kUnitBytes = W4_BN * W4_BK / 2;
-constexpr int kGroupThreads = 128;  // one unpack group = 4 warps = one thread per channel row
-constexpr int kRawStageBytes = kUnitBytes + kGroupThreads * 4;   // + one scale word per thread
-constexpr int kMaxSlots = 3;        // operand slots = unpack groups = MMA issuers, upper bound
-constexpr int kWSlotBytes = W4_BN * W4_BK * 2;   // two 16 KB swizzle atoms
-constexpr int kUnpackWarp0 = 4;
-constexpr int kW4Threads = (kUnpackWarp0 + 4 * kMaxSlots) * 32;   // 512
-
-struct W4Control {
-  uint64_t ready[kMaxSlots];   // 128 unpack arrivals + the activation tile's bytes
-  uint64_t free_[kMaxSlots];   // tcgen05.commit of the unit that used the slot
-  uint64_t acc_full[2], acc_free[2];
-  uint64_t epi_done, fin_done;
-  uint32_t tmem_base;
-  int abort;
-  int finalize;
-};
+constexpr int kStrip = 16;          // channels per work item: the M of mma.m16n8k16
+constexpr int kChunkK = 128;        // K per work item: eight K16 tiles, 2 x 16 bytes per lane, one scale
+constexpr int kScaleK = 128;        // partial sums are scaled every 128 K
+constexpr int kW4Warps = 16;
+constexpr int kW4Threads = kW4Warps * 32;
+constexpr size_t kSmemCap = 226 * 1024;
+// Chunks (1 KB each) a warp keeps in flight in its private cp.async ring: loaded HBM latency is
+// a few microseconds, so an SM needs on the order of 100 KB in flight to stream at its share
+// of the bandwidth.  More tokens leave less room beside the activation slice.
+__host__ __device__ constexpr int w4_depth(int nt) { return nt == 1 ? 8 : (nt == 2 ? 6 : 4); }
+__host__ __device__ constexpr size_t w4_ring_bytes(int nt) { return (size_t)kW4Warps * w4_depth(nt) * 1024; }
 
 struct W4Params {
-  const uint8_t* wp;      // packed units, [n_tiles][k_blocks][8 KB]
+  const uint4* wp;        // packed chunks, [N / 16][K / 128][2][32 lanes] x 16 bytes
   const void* scale;      // [K / tile, N], f32 or bf16
   int scale_dtype;
-  int64_t M, N, K;
+  const __nv_bfloat16* a; // [M, K]
+  int M;
+  int64_t N, K;
   int tile;               // scale tile along K (multiple of 128)
-  int mpad;               // tokens padded to 16 / 32 / 64 / 128: the MMA N extent
-  int slots;              // operand slots in use = unpack groups = MMA issuers in use
-  int depth;              // packed-weight units each group keeps in flight (3)
+  int split;              // K slices
+  int ks;                 // K per slice
+  int pitch;              // bytes between token rows of the shared activation slice
   void* out;
   int out_dtype;
   float* ws;              // [M, N] partial sums, zero on entry, left zero
-  int* counters;          // [n_tiles], zero on entry, left zero
-  int32_t* error_flag;
-  int n_tiles, k_blocks;
+  int* counters;          // [N / 16], zero on entry, left zero
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+template <int OFF>
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4 + %5];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
 }
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
+template <int OFF>
+__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t (&r)[2]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2 + %3];"
+               : "=r"(r[0]), "=r"(r[1]) : "r"(addr), "n"(OFF));
 }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7])
-      : "r"(taddr)
-      : "memory");
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Eight offset-binary nibbles (value + 8), stored in the order k0 k2 k4 k6 k1 k3 k5 k7, to four
-// bf16x2 words (k0 k1)(k2 k3)(k4 k5)(k6 k7), each multiplied by the bf16 scale.  0x4300 | u is
-// the bf16 number 128 + u; subtracting 136 gives the signed code exactly.
-__device__ __forceinline__ void unpack8(uint32_t w, __nv_bfloat162 s2, uint32_t (&o)[4]) {
+// Eight offset-binary nibbles (value + 8) of one lane and one K16 tile -> the four A-fragment
+// registers.  Nibble j sits under nibble j + 4 of the same register: 0x4300 | u is the bf16
+// number 128 + u, and subtracting 136 gives the signed code exactly.
+__device__ __forceinline__ void unpack_fragment(uint32_t w, uint32_t (&a)[4]) {
   const __nv_bfloat162 bias = __floats2bfloat162_rn(136.f, 136.f);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     uint32_t v = ((w >> (4 * j)) & 0x000f000fu) | 0x43004300u;
-    __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&v);
-    h = __hmul2(__hsub2(h, bias), s2);
-    o[j] = *reinterpret_cast<uint32_t*>(&h);
+    __nv_bfloat162 h = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);
+    a[j] = *reinterpret_cast<uint32_t*>(&h);
   }
 }
 
-// Does issuer `t` own a unit of the segment that starts `first_local` units into the CTA's
-// range and is `units` long?  (Units go to issuers round-robin by their local index.)
-__device__ __forceinline__ bool issuer_in_segment(int t, int issuers, int first_local, int units) {
-  if (units >= issuers) return true;
-  int d = t - first_local % issuers;
-  if (d < 0) d += issuers;
-  return d < units;
+__device__ __forceinline__ float load_scale_w4(const void* p, int dtype, int64_t i) {
+  if (dtype == QWX_F32) return __ldg(reinterpret_cast<const float*>(p) + i);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
 }
 
-__global__ void __launch_bounds__(kW4Threads, 1)
-gemm_w4_kernel(const __grid_constant__ CUtensorMap tma_act, const W4Params p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t act_bytes = 2u * p.mpad * 128u;   // activation tile of one unit (two atoms)
-  const uint32_t w_off = 0;
-  const uint32_t act_off = w_off + p.slots * kWSlotBytes;
-  const uint32_t raw_off = act_off + p.slots * act_bytes;
-  const uint32_t ctl_off = raw_off + p.slots * p.depth * kRawStageBytes;
-  W4Control* ctl = reinterpret_cast<W4Control*>(base_ptr + ctl_off);
-  volatile int* abort = &ctl->abort;
-
+template <int NT>   // token tiles of 8: the activation is padded to NT * 8 rows
+__global__ void __launch_bounds__(kW4Threads, 1) gemm_w4_kernel(const W4Params p) {
+  extern __shared__ __align__(16) uint8_t act[];
+  constexpr int MPAD = NT * 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Units are numbered tile-major; the host guarantees that the count fits 31 bits, so all the
-  // per-unit bookkeeping below is 32-bit and incremental (no divisions in the loops).
-  const int total_units = p.n_tiles * p.k_blocks;
-  const int g_begin = (int)((int64_t)total_units * blockIdx.x / gridDim.x);
-  const int g_end = (int)((int64_t)total_units * (blockIdx.x + 1) / gridDim.x);
-  const int kb_begin = g_begin % p.k_blocks, tile_begin = g_begin / p.k_blocks;
-  // Tensor memory: [2 segment buffers][issuers][mpad columns] of float32 accumulators.
-  const uint32_t set_cols = (uint32_t)(p.slots * p.mpad);
-  uint32_t tmem_cols = 32;
-  while (tmem_cols < 2 * set_cols) tmem_cols <<= 1;
+  const int g = lane >> 2, t = lane & 3;
+  const int slice = blockIdx.x % p.split;
+  const int cta_in_slice = blockIdx.x / p.split;
+  const int ctas_per_slice = gridDim.x / p.split;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kMaxSlots; ++s) {
-      mbar_init(smem_u32(&ctl->ready[s]), kGroupThreads + 1);
-      mbar_init(smem_u32(&ctl->free_[s]), 1);
+  // ---- the CTA's activation slice: tokens x ks, rows `pitch` bytes apart (16 bytes of padding
+  // keep the eight rows of an ldmatrix in different banks); rows beyond M are zero ----
+  const int vec_per_row = p.ks / 8;
+  for (int idx = threadIdx.x; idx < MPAD * vec_per_row; idx += kW4Threads) {
+    const int token = idx / vec_per_row, cv = idx - token * vec_per_row;
+    uint8_t* dst = act + (size_t)token * p.pitch + cv * 16;
+    if (token < p.M) {
+      const __nv_bfloat16* src = p.a + (int64_t)token * p.K + (int64_t)slice * p.ks + cv * 8;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                       (uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+    } else {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&ctl->acc_full[a]), p.slots);
-      mbar_init(smem_u32(&ctl->acc_free[a]), kGroupThreads / 32);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  // ---- this warp's contiguous range of chunks, strip-major inside the slice ----
+  const int cps = p.ks / kChunkK;                       // chunks per strip in one slice
+  const int chunks_per_strip = (int)(p.K / kChunkK);    // ... in all slices
+  const int total = (int)(p.N / kStrip) * cps;          // the host checks that this fits
+  const int nwarps = ctas_per_slice * kW4Warps;
+  const int wg = cta_in_slice * kW4Warps + warp;
+  const int c_begin = (int)((int64_t)total * wg / nwarps);
+  const int c_end = (int)((int64_t)total * (wg + 1) / nwarps);
+
+  // Fetch cursor: two 16-byte loads per chunk and lane, plus the scales of this lane's two
+  // channels for the chunk's K tile.  The loads land in registers that are first read
+  // kPrefetch chunks later.
+  constexpr int D = w4_depth(NT);
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(act) + (uint32_t)(MPAD * p.pitch) +
+                        (uint32_t)(warp * D * 1024 + lane * 16);   // this lane's 16 bytes of stage 0, half 0
+  float slo[D], shi[D];
+  int f_c = c_begin;
+  int f_strip = c_begin / cps;
+  int f_kc = c_begin - f_strip * cps;
+  const uint4* f_w = p.wp + (((int64_t)f_strip * chunks_per_strip + slice * cps + f_kc) * 64 + lane);
+  // scale cursor: element index of channel g of the strip in the scale row of the chunk's K tile
+  const int blocks_per_scale = p.tile / kChunkK;
+  int f_left = blocks_per_scale - (slice * cps + f_kc) % blocks_per_scale;   // chunks left in the row
+  int64_t f_s = (int64_t)((slice * cps + f_kc) / blocks_per_scale) * p.N + f_strip * kStrip + g;
+  auto fetch = [&](int stage, float& lo, float& hi) {
+    if (f_c < c_end) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring + stage * 1024), "l"(f_w) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring + stage * 1024 + 512), "l"(f_w + 32) : "memory");
+      lo = load_scale_w4(p.scale, p.scale_dtype, f_s);
+      hi = load_scale_w4(p.scale, p.scale_dtype, f_s + 8);
+      ++f_c;
+      f_w += 64;
+      if (--f_left == 0) { f_left = blocks_per_scale; f_s += p.N; }
+      if (++f_kc == cps) {
+        f_kc = 0;
+        ++f_strip;
+        f_w += (int64_t)(chunks_per_strip - cps) * 64;
+        f_left = blocks_per_scale - (slice * cps) % blocks_per_scale;
+        f_s = (int64_t)((slice * cps) / blocks_per_scale) * p.N + f_strip * kStrip + g;
+      }
     }
-    mbar_init(smem_u32(&ctl->epi_done), kGroupThreads);
-    mbar_init(smem_u32(&ctl->fin_done), 1);
-    ctl->abort = 0;
-    ctl->finalize = 0;
-    fence_barrier_init();
-    prefetch_tensormap(&tma_act);
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), tmem_cols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // the activation slice is the oldest commit group: waiting until at most D groups pend
+  // completes it
+#pragma unroll
+  for (int u = 0; u < D; ++u) fetch(u, slo[u], shi[u]);
+  asm volatile("cp.async.wait_group %0;" ::"n"(D) : "memory");
   __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = ctl->tmem_base;
 
-  if (warp == 0) {
-    // ---------------- activation tiles: one per unit, into the unit's operand slot ----------
-    if (lane == 0) {
-      int u = 0, kb = kb_begin;
-      uint32_t uphase = 0;
-      for (int g = g_begin; g < g_end; ++g) {
-        if (!mbar_wait(smem_u32(&ctl->free_[u]), uphase ^ 1u, abort)) break;
-        const uint32_t bar = smem_u32(&ctl->ready[u]);
-        const uint32_t dst = base + act_off + u * act_bytes;
-        mbar_expect_tx(bar, act_bytes);
-        tma_load_2d(dst, &tma_act, kb * W4_BK, 0, bar);
-        tma_load_2d(dst + p.mpad * 128, &tma_act, kb * W4_BK + 64, 0, bar);
-        if (++u == p.slots) { u = 0; uphase ^= 1u; }
-        if (++kb == p.k_blocks) kb = 0;
-      }
-      if (*abort) {
-        // give copies in flight time to land before the CTA retires
-        for (int s = 0; s < p.slots; ++s)
-          for (int it = 0; it < 20000; ++it)
-            if (mbar_try_wait(smem_u32(&ctl->ready[s]), 0) || mbar_try_wait(smem_u32(&ctl->ready[s]), 1)) break;
-      }
-    }
-    __syncwarp();
-  } else if (warp <= p.slots) {
-    // ---------------- MMA issuers ----------------
-    // An issuing thread pays a few hundred cycles per mbarrier wait and per commit, far more
-    // than the eight MMAs of a unit cost the tensor pipe, so several warps issue: issuer j
-    // serves operand slot j (every unit whose local index is j mod slots) and adds into its own
-    // accumulator columns.  Because a slot has one issuer, that thread observes every phase of
-    // the slot's barrier in order (a parity wait must never skip a phase).  Per unit: one wait,
-    // eight MMAs, one commit.  Descriptors are built once and advanced by adding to their low word
-    // (the start-address field cannot carry into the next field below 256 KB).
-    const int me = warp - 1;
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(1, 1, 1, 0, 0, W4_BN, (uint32_t)p.mpad);
-      const uint64_t wdesc0 = make_smem_desc(base + w_off, 16, 1024);
-      const uint64_t adesc0 = make_smem_desc(base + act_off, 16, 1024);
-      const uint32_t act_atom = (uint32_t)(p.mpad * 128) >> 4;
-      const uint32_t bar_ready = smem_u32(&ctl->ready[0]), bar_free = smem_u32(&ctl->free_[0]);
-      int u = 0, acc = 0, kb = kb_begin;
-      uint32_t uphase = 0, acc_phase = 0;
-      bool mine_in_segment = false;
-      for (int g = g_begin; g < g_end; ++g) {
-        const int seg_first = max(g_begin, g - kb);
-        const int seg_last = min(g_end - 1, g + (p.k_blocks - 1 - kb));
-        // every issuer watches every segment's accumulator hand-over, in order
-        if (g == seg_first && !mbar_wait(smem_u32(&ctl->acc_free[acc]), acc_phase ^ 1u, abort)) break;
-        if (u == me) {
-          const bool first_of_mine = g - p.slots < seg_first;
-          if (!mbar_wait(bar_ready + u * 8, uphase, abort)) break;
-          tc_fence_after();
-          const uint64_t da = wdesc0 + (uint64_t)(u * (kWSlotBytes >> 4));
-          const uint64_t db = adesc0 + (uint64_t)(u * (act_bytes >> 4));
-          const uint32_t d_tmem = tmem_base + acc * set_cols + me * p.mpad;
-#pragma unroll
-          for (int kk = 0; kk < W4_BK / 16; ++kk) {
-            const uint32_t atom = kk >> 2, sub = ((kk & 3) * 32) >> 4;
-            mma_ss<MmaKind::kF16>(d_tmem, da + atom * ((W4_BN * 128) >> 4) + sub,
-                                  db + atom * act_atom + sub, idesc, !(first_of_mine && kk == 0));
-          }
-          mma_commit(bar_free + u * 8);
-          mine_in_segment = true;
-        }
-        if (g == seg_last) {
-          // every issuer reports on the segment: a commit if it has MMAs in it, else an arrive
-          if (mine_in_segment) mma_commit(smem_u32(&ctl->acc_full[acc]));
-          else mbar_arrive(smem_u32(&ctl->acc_full[acc]));
-          mine_in_segment = false;
-          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
-        }
-        if (++u == p.slots) { u = 0; uphase ^= 1u; }
-        if (++kb == p.k_blocks) kb = 0;
-      }
-    }
-    __syncwarp();
-  } else if (warp >= kUnpackWarp0 && warp < kUnpackWarp0 + 4 * p.slots) {
-    // ---------------- weight stream, unpack, epilogue ----------------
-    // Group j (4 warps, one thread per channel row) owns every unit whose local index is
-    // j mod slots and always fills operand slot j.  While one group sits in a barrier wait or
-    // a proxy fence the others convert, which is what keeps the issue slots busy.  Group 0
-    // additionally runs the epilogue of every tile segment.
-    const int group = (warp - kUnpackWarp0) >> 2;
-    const int n = threadIdx.x & 127;                  // channel row inside the tile
-    const int quarter = warp & 3;                     // tensor-memory lane quarter (group 0)
-    const int scale_elem = p.scale_dtype == QWX_F32 ? 4 : 2;
-    const uint32_t my_off = n * 16;                   // chunk j of this row: + j * 2048
-    const uint32_t bar_free = smem_u32(&ctl->free_[group]);
-    const uint32_t bar_ready = smem_u32(&ctl->ready[group]);
+  // per-lane byte offset of its ldmatrix row: matrices 0..3 = (tokens 0-7, k 0-7), (tokens 0-7,
+  // k 8-15), (tokens 8-15, k 0-7), (tokens 8-15, k 8-15)
+  const int lm = lane >> 3, lr = lane & 7;
+  const uint32_t act_lane = (uint32_t)__cvta_generic_to_shared(act) +
+                            (uint32_t)(((lm >> 1) * 8 + lr) * p.pitch + (lm & 1) * 16);
 
-    // Prefetch cursor over this group's units (local index group, group + slots, ...): one
-    // commit group per unit = the row's four 16-byte chunks + the 4-byte word holding the
-    // channel's scale for the unit's K tile (two bf16 scales share a word).
-    const int blocks_per_scale = p.tile / W4_BK;
-    const int64_t scale_row_bytes = p.N * scale_elem;
-    const int64_t scale_col_bytes = scale_elem == 4 ? (int64_t)n * 4 : (int64_t)(n & ~1) * 2;
-    int f_g = g_begin + group;
-    int f_kb = kb_begin + group, f_tile = tile_begin;
-    while (f_kb >= p.k_blocks) { f_kb -= p.k_blocks; ++f_tile; }
-    int f_stage = 0;
-    auto fetch = [&]() {
-      if (f_g < g_end) {
-        const uint8_t* src = p.wp + (int64_t)f_g * kUnitBytes + my_off;
-        const uint32_t dst = base + raw_off + (group * p.depth + f_stage) * kRawStageBytes;
+  float acc[NT][4], run[NT][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) cp_async16(dst + my_off + j * 2048, src + j * 2048);
-        const char* sp = reinterpret_cast<const char*>(p.scale) +
-                         (int64_t)(f_kb / blocks_per_scale) * scale_row_bytes +
-                         (int64_t)f_tile * W4_BN * scale_elem + scale_col_bytes;
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + kUnitBytes + n * 4),
-                     "l"(sp) : "memory");
-        f_g += p.slots;
-        f_kb += p.slots;
-        while (f_kb >= p.k_blocks) { f_kb -= p.k_blocks; ++f_tile; }
-      }
-      if (++f_stage == p.depth) f_stage = 0;
-      cp_async_commit();
-    };
-    for (int d = 0; d < p.depth; ++d) fetch();
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[n][j] = run[n][j] = 0.f;
 
-    int rs = 0, acc = 0, owner = 0;
-    uint32_t uphase = 0, acc_phase = 0, epi_phase = 0;
-    int seg_units = 0, seg_first_local = 0;
-    bool ok = true;
-    int tile = tile_begin, kb = kb_begin;
-    for (int g = g_begin; g < g_end && ok; ++g, kb = (kb + 1 == p.k_blocks ? (++tile, 0) : kb + 1)) {
-      const bool first = (g == g_begin) || kb == 0;
-      const bool last = (g == g_end - 1) || kb == p.k_blocks - 1;
-      if (first) { seg_units = 0; seg_first_local = g - g_begin; }
-      ++seg_units;
+  int strip = c_begin / cps;
+  int kc = c_begin - strip * cps;
+  int contributed = 0;
 
-      if (owner == group) {
-        // this thread's own copies of the unit have landed once at most depth - 1 groups pend
-        cp_async_wait<2>();   // depth is 3
-        const uint8_t* raw = base_ptr + raw_off + (group * p.depth + rs) * kRawStageBytes;
-        uint32_t words[16];
+  for (int base = c_begin; base < c_end; base += D) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 c = *reinterpret_cast<const uint4*>(raw + my_off + j * 2048);
-          words[4 * j] = c.x; words[4 * j + 1] = c.y; words[4 * j + 2] = c.z; words[4 * j + 3] = c.w;
-        }
-        const uint32_t sw = *reinterpret_cast<const uint32_t*>(raw + kUnitBytes + n * 4);
-        fetch();                       // refill the slice just read
-        if (++rs == p.depth) rs = 0;
-
-        ok = mbar_wait(bar_free, uphase ^ 1u, abort);
-        if (!ok) break;
-        uphase ^= 1u;
-        __nv_bfloat16 sb;  // the scale as bf16 (f32 scales are rounded)
-        if (scale_elem == 4) sb = __float2bfloat16_rn(__uint_as_float(sw));
-        else sb = __ushort_as_bfloat16((unsigned short)((n & 1) ? (sw >> 16) : (sw & 0xffffu)));
-        const __nv_bfloat162 s2 = __halves2bfloat162(sb, sb);
-        uint8_t* wrow = base_ptr + w_off + group * kWSlotBytes + (n >> 3) * 1024 + (n & 7) * 128;
+    for (int u = 0; u < D; ++u) {
+      const int c = base + u;
+      if (c >= c_end) break;
+      const float s_lo = slo[u], s_hi = shi[u];
+      asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
+      uint4 wq[2];
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(wq[0].x), "=r"(wq[0].y), "=r"(wq[0].z), "=r"(wq[0].w) : "r"(ring + u * 1024) : "memory");
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(wq[1].x), "=r"(wq[1].y), "=r"(wq[1].z), "=r"(wq[1].w) : "r"(ring + u * 1024 + 512) : "memory");
+      fetch(u, slo[u], shi[u]);   // chunk c + D, into the ring stage just read
+      const uint32_t kaddr = act_lane + (uint32_t)(kc * kChunkK) * 2u;
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {   // words 0-7: K 0..63 (atom 0), words 8-15: atom 1
-          uint32_t o[4];
-          unpack8(words[c], s2, o);
-          *reinterpret_cast<uint4*>(wrow + (c >> 3) * (W4_BN * 128) + (((c & 7) ^ (n & 7)) * 16)) =
-              make_uint4(o[0], o[1], o[2], o[3]);
-        }
-        fence_proxy_async();
-        mbar_arrive(bar_ready);
-      }
-      if (++owner == p.slots) owner = 0;
-
-      if (!last || group != 0) continue;
-      // ---- epilogue of the segment (tile, kb - seg_units + 1 .. kb), by group 0 ----
-      ok = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort);
-      if (!ok) break;
-      tc_fence_after();
-      const bool whole = seg_units == p.k_blocks;
-      const int64_t channel = (int64_t)tile * W4_BN + quarter * 32 + lane;
-      for (int col = 0; col < p.mpad; col += 8) {
-        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int t = 0; t < p.slots; ++t) {   // add up the issuers' partial accumulators
-          if (!issuer_in_segment(t, p.slots, seg_first_local, seg_units)) continue;
-          uint32_t r[8];
-          tmem_ld_32x32b_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * set_cols +
-                                t * p.mpad + col, r);
-          tmem_ld_wait();
+      for (int i = 0; i < 8; ++i) {
+        const uint4& q4 = wq[i >> 2];
+        const uint32_t word = (i & 3) == 0 ? q4.x : ((i & 3) == 1 ? q4.y : ((i & 3) == 2 ? q4.z : q4.w));
+        uint32_t a[4];
+        unpack_fragment(word, a);
+        if constexpr (NT == 1) {
+          uint32_t b[2];
+          if (i == 0) ldmatrix_x2<0>(kaddr, b);
+          else if (i == 1) ldmatrix_x2<32>(kaddr, b);
+          else if (i == 2) ldmatrix_x2<64>(kaddr, b);
+          else if (i == 3) ldmatrix_x2<96>(kaddr, b);
+          else if (i == 4) ldmatrix_x2<128>(kaddr, b);
+          else if (i == 5) ldmatrix_x2<160>(kaddr, b);
+          else if (i == 6) ldmatrix_x2<192>(kaddr, b);
+          else ldmatrix_x2<224>(kaddr, b);
+          mma_bf16(acc[0], a, b[0], b[1]);
+        } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) sum[j] += __uint_as_float(r[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int64_t m = col + j;
-          if (m >= p.M) continue;
-          const float v = sum[j];
-          if (whole) {
-            if (p.out_dtype == QWX_BF16)
-              reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.N + channel] = __float2bfloat16_rn(v);
-            else
-              reinterpret_cast<float*>(p.out)[m * p.N + channel] = v;
-          } else {
-            atomicAdd(p.ws + m * p.N + channel, v);
+          for (int pr = 0; pr < NT / 2; ++pr) {
+            uint32_t b[4];
+            const uint32_t ka = kaddr + (uint32_t)(pr * 16 * p.pitch);
+            if (i == 0) ldmatrix_x4<0>(ka, b);
+            else if (i == 1) ldmatrix_x4<32>(ka, b);
+            else if (i == 2) ldmatrix_x4<64>(ka, b);
+            else if (i == 3) ldmatrix_x4<96>(ka, b);
+            else if (i == 4) ldmatrix_x4<128>(ka, b);
+            else if (i == 5) ldmatrix_x4<160>(ka, b);
+            else if (i == 6) ldmatrix_x4<192>(ka, b);
+            else ldmatrix_x4<224>(ka, b);
+            mma_bf16(acc[2 * pr], a, b[0], b[1]);
+            mma_bf16(acc[2 * pr + 1], a, b[2], b[3]);
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_free[acc]));
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      ++contributed;
 
-      if (!whole) {
-        // Count this CTA's K blocks for the tile; whoever completes the tile converts it.
-        __threadfence();
-        mbar_arrive(smem_u32(&ctl->epi_done));
-        if (n == 0) {
-          ok = mbar_wait(smem_u32(&ctl->epi_done), epi_phase, abort);
-          if (ok) {
-            const int old = atomicAdd(p.counters + tile, seg_units);
+      // the chunk is one scale block: scale its partial sums into the running sums
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        run[n][0] = __fmaf_rn(acc[n][0], s_lo, run[n][0]);
+        run[n][1] = __fmaf_rn(acc[n][1], s_lo, run[n][1]);
+        run[n][2] = __fmaf_rn(acc[n][2], s_hi, run[n][2]);
+        run[n][3] = __fmaf_rn(acc[n][3], s_hi, run[n][3]);
+        acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+      }
+      const bool range_end = c == c_end - 1;
+      if (kc == cps - 1 || range_end) {
+        // ---- this warp is done with the strip ----
+        const bool whole = contributed == chunks_per_strip;
+        const int64_t ch = (int64_t)strip * kStrip + g;
+        bool fin = whole;
+        if (!whole) {
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int tok = n * 8 + 2 * t + (j & 1);
+              if (tok < p.M) atomicAdd(p.ws + (int64_t)tok * p.N + ch + (j >> 1) * 8, run[n][j]);
+            }
+          __threadfence();
+          __syncwarp();
+          int last = 0;
+          if (lane == 0) {
+            const int old = atomicAdd(p.counters + strip, contributed);
+            last = old + contributed == chunks_per_strip;
+            if (last) p.counters[strip] = 0;
+          }
+          fin = __shfl_sync(0xffffffffu, last, 0) != 0;
+          if (fin) {
+            // whoever completes the strip converts it and leaves the workspace zero
             __threadfence();
-            ctl->finalize = (old + seg_units == p.k_blocks) ? 1 : 0;
-            if (ctl->finalize) p.counters[tile] = 0;
-          }
-          mbar_arrive(smem_u32(&ctl->fin_done));
-        }
-        ok = mbar_wait(smem_u32(&ctl->fin_done), epi_phase, abort);
-        epi_phase ^= 1u;
-        if (!ok) break;
-        if (ctl->finalize) {
-          for (int64_t m = 0; m < p.M; ++m) {
-            float* wsp = p.ws + m * p.N + channel;
-            const float v = __ldcg(wsp);
-            *wsp = 0.f;
-            if (p.out_dtype == QWX_BF16)
-              reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.N + channel] = __float2bfloat16_rn(v);
-            else
-              reinterpret_cast<float*>(p.out)[m * p.N + channel] = v;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int tok = n * 8 + 2 * t + (j & 1);
+                float* w = p.ws + (int64_t)tok * p.N + ch + (j >> 1) * 8;
+                run[n][j] = tok < p.M ? __ldcg(w) : 0.f;
+              }
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int tok = n * 8 + 2 * t + (j & 1);
+                if (tok < p.M) p.ws[(int64_t)tok * p.N + ch + (j >> 1) * 8] = 0.f;
+              }
           }
         }
+        if (fin) {
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int tok = n * 8 + 2 * t + (j & 1);
+              if (tok >= p.M) continue;
+              const int64_t at = (int64_t)tok * p.N + ch + (j >> 1) * 8;
+              if (p.out_dtype == QWX_BF16)
+                reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(run[n][j]);
+              else
+                reinterpret_cast<float*>(p.out)[at] = run[n][j];
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) run[n][j] = 0.f;
+        contributed = 0;
       }
+      if (++kc == cps) { kc = 0; ++strip; }
     }
-    cp_async_wait<0>();  // nothing of this thread may still be landing when the CTA retires
   }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
-  }
-  if (threadIdx.x == 0 && ctl->abort && p.error_flag) atomicExch(p.error_flag, QWX_ERR_DEVICE_WAIT);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
-// Logical codes q[K, N] (one sign-extended int4 per byte) -> packed units.
-__global__ void pack_w4_kernel(const int8_t* __restrict__ q, int64_t K, int64_t N, int k_blocks,
+// Logical codes q[K, N] (one sign-extended int4 per byte) -> fragment-ordered chunks.  A chunk
+// is two 512-byte halves; word i (0..3) of lane (g, t) in half h covers K tile 4 h + i of the
+// chunk; its nibble j holds channel strip * 16 + g + 8 * (j & 1) at
+// k = 2 t + 8 * ((j >> 1) & 1) + (j >> 2) of the tile.
+__global__ void pack_w4_kernel(const int8_t* __restrict__ q, int64_t K, int64_t N,
                                uint32_t* __restrict__ out, int64_t total_words) {
-  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= total_words) return;
-  // word index inside a unit: ((j * 128 + n) * 4 + w); unit index: tile * k_blocks + kb
-  const int w = (int)(t & 3);
-  const int n = (int)((t >> 2) & 127);
-  const int j = (int)((t >> 9) & 3);
-  const int64_t unit = t >> 11;
-  const int64_t tile = unit / k_blocks, kb = unit % k_blocks;
-  const int64_t col = tile * W4_BN + n;
-  const int64_t k0 = kb * W4_BK + j * 32 + w * 8;
+  const int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= total_words) return;
+  const int i = (int)(w & 3);
+  const int lane = (int)((w >> 2) & 31);
+  const int half = (int)((w >> 7) & 1);
+  const int64_t chunk = w >> 8;                 // strip * (K / 128) + kc
+  const int64_t cpsa = K / kChunkK;
+  const int64_t strip = chunk / cpsa, kc = chunk % cpsa;
+  const int g = lane >> 2, t = lane & 3;
   uint32_t word = 0;
-  const int order[8] = {0, 2, 4, 6, 1, 3, 5, 7};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int64_t k = k0 + order[i];
-    int v = (col < N && k < K) ? (int)q[k * N + col] : 0;
-    word |= (uint32_t)((v + 8) & 0xf) << (4 * i);
+  for (int j = 0; j < 8; ++j) {
+    const int64_t ch = strip * kStrip + g + 8 * (j & 1);
+    const int64_t k = kc * kChunkK + (half * 4 + i) * 16 + 2 * t + 8 * ((j >> 1) & 1) + (j >> 2);
+    const int v = (ch < N && k < K) ? (int)q[k * N + ch] : 0;
+    word |= (uint32_t)((v + 8) & 0xf) << (4 * j);
   }
-  out[t] = word;
+  out[w] = word;
 }
 
 int sm_count_w4() {
@@ -441,19 +360,17 @@ int sm_count_w4() {
   return n;
 }
 
-// Operand slots (= unpack groups = issuing warps) and prefetch depth per token count: what fits
-// 227 KB of shared memory and 512 tensor-memory columns (2 segment buffers x slots x mpad).
-void w4_config(int mpad, int* slots, int* depth) {
-  if (mpad <= 64) { *slots = 3; *depth = 3; }
-  else { *slots = 2; *depth = 3; }
+// Fewest K slices (a divisor of K / 128) whose activation slice fits shared memory.
+int w4_split(int mpad, int64_t K, size_t cap) {
+  const int64_t blocks = K / kScaleK;
+  for (int64_t d = 1; d <= blocks; ++d) {
+    if (blocks % d) continue;
+    if ((size_t)mpad * ((size_t)(K / d) * 2 + 16) <= cap) return (int)d;
+  }
+  return 0;
 }
 
-size_t w4_smem_bytes(int mpad) {
-  int slots, depth;
-  w4_config(mpad, &slots, &depth);
-  return 1024 + (size_t)slots * (kWSlotBytes + 2 * mpad * 128) +
-         (size_t)slots * depth * kRawStageBytes + sizeof(W4Control);
-}
+constexpr int kMaxTokensPerLaunch = 32;
 
 }  // namespace
 }  // namespace qwx
@@ -463,81 +380,87 @@ using namespace qwx;
 extern "C" {
 
 size_t qwx_w4_packed_bytes(int64_t K, int64_t N) {
-  if (K <= 0 || N <= 0 || K % W4_BK) return 0;
-  const int64_t n_tiles = (N + W4_BN - 1) / W4_BN;
-  return (size_t)(n_tiles * (K / W4_BK) * kUnitBytes);
+  if (K <= 0 || N <= 0 || K % kScaleK) return 0;
+  const int64_t strips = (N + kStrip - 1) / kStrip;
+  return (size_t)(strips * (K / kChunkK) * 1024);
 }
 
 int qwx_pack_w4(const void* q, int64_t K, int64_t N, void* packed, qwx_stream_t stream) {
   if (!q || !packed) return QWX_ERR_NULL;
-  if (K <= 0 || N <= 0 || K % W4_BK) return QWX_ERR_SHAPE;
-  const int64_t n_tiles = (N + W4_BN - 1) / W4_BN;
-  const int64_t words = n_tiles * (K / W4_BK) * (kUnitBytes / 4);
+  if (K <= 0 || N <= 0 || K % kScaleK) return QWX_ERR_SHAPE;
+  const int64_t strips = (N + kStrip - 1) / kStrip;
+  const int64_t words = strips * (K / kChunkK) * 256;
   pack_w4_kernel<<<(unsigned)((words + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-      (const int8_t*)q, K, N, (int)(K / W4_BK), (uint32_t*)packed, words);
+      (const int8_t*)q, K, N, (uint32_t*)packed, words);
   QWX_CHECK_LAUNCH();
   return QWX_OK;
 }
 
 size_t qwx_gemm_a16w4_workspace_bytes(int64_t M, int64_t N) {
   if (M <= 0 || N <= 0) return 0;
-  const int64_t n_tiles = (N + W4_BN - 1) / W4_BN;
-  return (size_t)(M * N * 4 + n_tiles * 4);
+  const int64_t strips = (N + kStrip - 1) / kStrip;
+  return (size_t)(M * N * 4 + strips * 4);
 }
 
 int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int scale_dtype,
                    int64_t M, int64_t N, int64_t K, int64_t k_tile, void* out, int out_dtype,
                    void* workspace, size_t workspace_bytes, int workspace_is_zero,
                    int32_t* error_flag, qwx_stream_t stream) {
+  (void)error_flag;   // no device-side waits in this kernel
   if (!a || !w_packed || !scale || !out || !workspace) return QWX_ERR_NULL;
   if (M <= 0 || N <= 0 || K <= 0) return QWX_ERR_SHAPE;
   if (M > 128) return QWX_ERR_UNSUPPORTED;            // larger batches: call per 128 rows
-  if (K % W4_BK || N % W4_BN) return QWX_ERR_UNSUPPORTED;
-  if (k_tile <= 0 || K % k_tile || k_tile % W4_BK) return QWX_ERR_UNSUPPORTED;
+  if (K % kScaleK || N % kStrip) return QWX_ERR_UNSUPPORTED;
+  if (k_tile <= 0 || K % k_tile || k_tile % kScaleK) return QWX_ERR_UNSUPPORTED;
   if (scale_dtype != QWX_F32 && scale_dtype != QWX_BF16) return QWX_ERR_DTYPE;
   if (out_dtype != QWX_BF16 && out_dtype != QWX_F32) return QWX_ERR_DTYPE;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w_packed) & 15) ||
       (reinterpret_cast<uintptr_t>(scale) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15))
     return QWX_ERR_ALIGN;
   if (workspace_bytes < qwx_gemm_a16w4_workspace_bytes(M, N)) return QWX_ERR_WORKSPACE;
+  if ((N / kStrip) * (K / kChunkK) > INT32_MAX / 2) return QWX_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   if (!workspace_is_zero &&
       cudaMemsetAsync(workspace, 0, qwx_gemm_a16w4_workspace_bytes(M, N), st) != cudaSuccess)
     return QWX_ERR_LAUNCH;
 
-  const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-  CUtensorMap ta;
-  if (!get_encode_tiled()) return QWX_ERR_NO_DEVICE;
-  if (!encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, (uint64_t)M, (uint64_t)K, mpad, 64))
-    return QWX_ERR_LAUNCH;
-
-  W4Params p;
-  p.wp = (const uint8_t*)w_packed;
-  p.scale = scale; p.scale_dtype = scale_dtype;
-  p.M = M; p.N = N; p.K = K; p.tile = (int)k_tile; p.mpad = mpad;
-  p.out = out; p.out_dtype = out_dtype;
-  p.ws = (float*)workspace;
-  p.counters = (int*)((char*)workspace + M * N * 4);
-  p.error_flag = error_flag;
-  w4_config(mpad, &p.slots, &p.depth);
-  p.n_tiles = (int)(N / W4_BN);
-  p.k_blocks = (int)(K / W4_BK);
-
-  const size_t smem = w4_smem_bytes(mpad);
-  static bool configured = false;
+  static bool configured = false;  // idempotent attributes; a benign race sets them twice
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_w4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)std::max(w4_smem_bytes(16), w4_smem_bytes(64))) != cudaSuccess)
+    const int cap = (int)kSmemCap;
+    if (cudaFuncSetAttribute(gemm_w4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_w4_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_w4_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess)
       return QWX_ERR_LAUNCH;
     configured = true;
   }
   const int sms = sm_count_w4();
   if (sms <= 0) return QWX_ERR_NO_DEVICE;
-  const int64_t units = (int64_t)p.n_tiles * p.k_blocks;
-  if (units > (1 << 30)) return QWX_ERR_UNSUPPORTED;
-  const int grid = (int)(units < sms ? units : sms);
-  gemm_w4_kernel<<<grid, kW4Threads, smem, st>>>(ta, p);
-  QWX_CHECK_LAUNCH();
+  const int out_elem = out_dtype == QWX_BF16 ? 2 : 4;
+
+  // The warp-level MMA holds up to 32 tokens: more tokens stream the weight once per 32.
+  for (int64_t m0 = 0; m0 < M; m0 += kMaxTokensPerLaunch) {
+    const int rows = (int)(M - m0 < kMaxTokensPerLaunch ? M - m0 : kMaxTokensPerLaunch);
+    const int nt = rows <= 8 ? 1 : (rows <= 16 ? 2 : 4);
+    const int split = w4_split(nt * 8, K, kSmemCap - w4_ring_bytes(nt));
+    if (split <= 0 || split > sms) return QWX_ERR_UNSUPPORTED;
+    W4Params p;
+    p.wp = (const uint4*)w_packed;
+    p.scale = scale; p.scale_dtype = scale_dtype;
+    p.a = (const __nv_bfloat16*)a + m0 * K;
+    p.M = rows; p.N = N; p.K = K; p.tile = (int)k_tile;
+    p.split = split;
+    p.ks = (int)(K / split);
+    p.pitch = p.ks * 2 + 16;
+    p.out = (char*)out + m0 * N * out_elem; p.out_dtype = out_dtype;
+    p.ws = (float*)workspace + m0 * N;
+    p.counters = (int*)((char*)workspace + M * N * 4);
+    const int grid = (sms / split) * split;
+    const size_t smem = (size_t)nt * 8 * p.pitch + w4_ring_bytes(nt);
+    if (nt == 1) gemm_w4_kernel<1><<<grid, kW4Threads, smem, st>>>(p);
+    else if (nt == 2) gemm_w4_kernel<2><<<grid, kW4Threads, smem, st>>>(p);
+    else gemm_w4_kernel<4><<<grid, kW4Threads, smem, st>>>(p);
+    QWX_CHECK_LAUNCH();
+  }
   return QWX_OK;
 }
 

@@ -29,7 +29,9 @@ CASES = [
     (16, 8192, 4096, 128, 'float32'),     # ~14 units per CTA: rings and operand slots wrap
     (128, 2048, 2048, 128, 'bfloat16'),   # 128 tokens, several units per CTA
     (3, 1024, 8192, 256, 'float32'),      # short tiles: a CTA crosses several tile segments
-    (33, 512, 4096, 128, 'float32'),      # 64-token padding, segments shorter than the slot count
+    (33, 512, 4096, 128, 'float32'),      # two launches: 32 tokens + 1 token
+    (5, 14336, 512, 128, 'float32'),      # K / 128 = 112: slices must divide it
+    (32, 8192, 1024 + 16, 128, 'bfloat16'),  # four K slices; N a multiple of 16 only
 ]
 
 
@@ -72,15 +74,20 @@ def test_a16w4_matches_oracle(case):
   assert np.all(np.abs(s - r) <= 1e-2 + 2e-2 * np.abs(r))
 
 
-def test_a16w4_float32_output_is_tight():
+@pytest.mark.parametrize('sdt', ['float32', 'bfloat16'])
+def test_a16w4_float32_output_is_tight(sdt):
   M, K, N = 16, 2048, 512
   rng = np.random.default_rng(5)
   w = (0.02 * rng.standard_normal((K, N))).astype(np.float32).astype(ml_dtypes.bfloat16)
   a = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.bfloat16)
-  wo = oq.quantize_api(w, 'int4', channelwise_axes=[1], tiled_axes={0: 128})
-  # W~ = bf16(q * s) exactly as the kernel forms it, float64 accumulation as the yardstick
-  wt = oq.dequantize(wo).astype(np.float64)
+  sd = np.float32 if sdt == 'float32' else ml_dtypes.bfloat16
+  wo = oq.quantize_api(w, 'int4', channelwise_axes=[1], tiled_axes={0: 128}, scale_dtype=sd)
+  # The kernel multiplies exact code products by the scale in float32: W~ = q * s without an
+  # intermediate rounding (what the reference computes when the scale is float32); float64
+  # accumulation is the yardstick.
+  wt = wo.qvalue.astype(np.float64) * np.repeat(wo.scale.astype(np.float64), 128, axis=0)
   want = a.astype(np.float64) @ wt
-  wq = bq.quantize_api(h.to_torch(w), 'int4', channelwise_axes=[1], tiled_axes={0: 128})
+  wq = bq.quantize_api(h.to_torch(w), 'int4', channelwise_axes=[1], tiled_axes={0: 128},
+                       scale_dtype=torch.float32 if sdt == 'float32' else torch.bfloat16)
   got = bdg.dot_general(h.to_torch(a), wq, DN, preferred_element_type=torch.float32)
-  assert np.abs(got.cpu().numpy() - want).max() <= 2e-4 * np.abs(want).max()
+  assert np.abs(got.cpu().numpy() - want).max() <= 2e-5 * np.abs(want).max()
