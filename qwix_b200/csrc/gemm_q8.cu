@@ -413,6 +413,13 @@ int sm_count() {
 }  // namespace
 }  // namespace qwx
 
+namespace qwx {
+int gemm_q8_pair_launch(const void* a, const void* b, int code_dtype, int b_layout, int64_t M,
+                        int64_t N, int64_t K, const void* sa, const void* sb, int scale_dtype,
+                        void* out, int out_dtype, int epilogue, int32_t* error_flag, int sms,
+                        cudaStream_t st);
+}
+
 using namespace qwx;
 
 // Split-K is worth it when the tiles cannot occupy the SMs: cut K so that tiles x splits comes
@@ -506,6 +513,10 @@ static int gemm_q8_impl(const void* a, const void* b, int code_dtype, int b_layo
       num_tiles *= splits;
     }
   }
+  // Two or more 128-row tiles: the CTA-pair kernel, which moves a third less data per SM.
+  if (p.splits == 1 && M > BM)
+    return gemm_q8_pair_launch(a, b, code_dtype, b_layout, M, N, K, sa, sb, scale_dtype, out,
+                               out_dtype, epilogue, error_flag, sms, st);
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);
   if (code_dtype == QWX_S8) {
     return b_layout == QWX_B_NK ? launch<MmaKind::kI8, QWX_B_NK>(ta, tb, p, grid, st)
