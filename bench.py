@@ -31,9 +31,9 @@ if ROOT not in sys.path:
 
 M, K, N = 4096, 8192, 8192
 OPS_PER_STEP = 2 * M * N * K
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_q8_kernel launch at this size,
-# from the ncu capture summarised in profiles/gemm_q8_w8a8_prefill.md (mean of two launches).
-GEMM_DRAM_TRAFFIC_BYTES = 153_155_000
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_q8_pair_kernel launch at this size,
+# from the ncu capture summarised in profiles/gemm_q8_pair_w8a8_prefill.md (mean of two launches).
+GEMM_DRAM_TRAFFIC_BYTES = 159_363_000
 NSETS = 3  # buffer sets cycled through so that no step finds its inputs in the 126 MB L2
 
 
@@ -73,7 +73,17 @@ class ClockSampler:
     for line in self.proc.stdout:
       self.rows.append([c.strip() for c in line.split(',')])
 
-  def stop(self) -> dict:
+  def wait_first(self, timeout_s: float = 4.0):
+    """Blocks until nvidia-smi has printed its first row (its start-up takes longer than a
+    short timed region)."""
+    t0 = time.time()
+    while self.proc is not None and not self.rows and time.time() - t0 < timeout_s:
+      time.sleep(0.02)
+
+  def mark(self) -> int:
+    return len(self.rows)
+
+  def stop(self, first: int = 0) -> dict:
     if self.proc is None:
       return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
     self.proc.terminate()
@@ -84,7 +94,7 @@ class ClockSampler:
     self.thread.join(timeout=2)
     sm, mx, reasons = [], [], set()
     names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
-    for r in self.rows:
+    for r in self.rows[first:]:
       if len(r) < 6:
         continue
       try:
@@ -355,13 +365,15 @@ def main():
     torch.cuda.synchronize()
 
   # ---- device-resident throughput (`value`) + per-kernel durations for the roofline ----
+  sampler = ClockSampler(local_rank)
+  sampler.start()
+  sampler.wait_first()
   for i in range(args.warmup):
     step(i)
   barrier()
-  sampler = ClockSampler(local_rank)
-  sampler.start()
   ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
   barrier()
+  mark0 = sampler.mark()
   ev[0].record()
   for i in range(args.steps):
     d = dev[i % NSETS]
@@ -371,7 +383,19 @@ def main():
     ev[3 * i + 2].record()
     ev[3 * i + 3].record()
   barrier()
-  clocks = sampler.stop()
+  mark1 = sampler.mark()
+  # nvidia-smi samples every 100 ms and the timed region may be shorter than that: the same
+  # steps keep running, untimed, until a few samples under this load exist.
+  t_load = time.time()
+  i = args.steps
+  while sampler.mark() - mark0 < 6 and time.time() - t_load < 1.5:
+    for _ in range(50):
+      step(i)
+      i += 1
+    torch.cuda.synchronize()
+  clocks = sampler.stop(mark0)
+  clocks['samples_in_timed_region'] = mark1 - mark0
+  clocks['window'] = 'timed region plus an untimed continuation of the same steps (100 ms sampling)'
   total_ms = ev[0].elapsed_time(ev[3 * args.steps])
   quant_ms = sum(ev[3 * i].elapsed_time(ev[3 * i + 1]) for i in range(args.steps)) / args.steps
   gemm_ms = sum(ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(args.steps)) / args.steps
@@ -454,7 +478,7 @@ def main():
       'roofline': {
           'bound': 'tensor', 'achieved': achieved, 'peak': peak_tops, 'unit': 'TOP/s',
           'frac': achieved / peak_tops, 'traffic': GEMM_DRAM_TRAFFIC_BYTES,
-          'kernel': 'gemm_q8_kernel<i8>', 'kernel_ms': gemm_ms,
+          'kernel': 'gemm_q8_pair_kernel<i8>', 'kernel_ms': gemm_ms,
           'peak_source': f"2 x bf16_tflops{'' if burst else '_sustained'} of MEASURED_PEAKS.json "
                          f"({peaks['source']}; int8 issues at twice the bf16 rate)",
           'library_int8_gemm_tops': library_tops,
