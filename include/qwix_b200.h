@@ -199,6 +199,33 @@ int qwx_gemm_q8_tiled(const void* a, const void* b, int code_dtype, int b_layout
 int qwx_code_sums(const void* codes, int64_t rows, int64_t cols, int k_axis, int64_t k_tile,
                   int t_major, int32_t* out, qwx_stream_t stream);
 
+/* Element-wise stages of a Llama-style decoder layer fused with the per-token int8
+ * quantization of the next projection's activation.  The quantization half is
+ * qarray.quantize with per-token absmax scales (qarray.py:638-644; the activation side of
+ * boxed_param.py:416-455): scale[row] = bf16(absmax / 127.5) (1 below 2^-63), codes by the
+ * strict recipe.  The element-wise halves (RMSNorm, SwiGLU, rotary embedding, KV-cache
+ * write) are model code and have no counterpart in qwix; every rounding of their unfused
+ * bf16/float32 composition is kept.  All tensors bf16, row-major; q int8; scale bf16 [rows].
+ *
+ * qwx_add_rmsnorm_quantize: x' = bf16(x + delta) (delta may be NULL: x' = x), written to x_out
+ *   when delta is given; y = bf16((f32(x') * rsqrt(mean(x'^2) + eps)) * f32(weight)); y_out
+ *   and/or (q, scale) receive the result.  d a multiple of 8, at most 8192.
+ * qwx_silu_mul_quantize: gu is [rows, 2 f] = [gate | up]; y = bf16(bf16(silu(gate)) * up).
+ * qwx_rope_cache: qkv [B, T, (hq + 2 hkv) * hd]; heads are rotated with the float32 tables
+ *   cos/sin [positions, hd / 2] at position pos + t (pos_dev, a device int64, replaces pos
+ *   when not NULL: the form a CUDA graph can replay); q goes to q_out [B, hq, T, hd], k and v
+ *   to cache_k / cache_v [B, hkv, S, hd] views with the given batch and head strides
+ *   (elements) at sequence index pos + t. */
+int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weight, double eps,
+                             int64_t rows, int64_t d, void* x_out, void* y_out, void* q,
+                             void* scale, qwx_stream_t stream);
+int qwx_silu_mul_quantize(const void* gu, int64_t rows, int64_t f, void* y_out, void* q,
+                          void* scale, qwx_stream_t stream);
+int qwx_rope_cache(const void* qkv, int64_t B, int64_t T, int hq, int hkv, int hd,
+                   const float* cos_t, const float* sin_t, int64_t pos, const int64_t* pos_dev,
+                   void* q_out, void* cache_k, void* cache_v, int64_t cache_batch_stride,
+                   int64_t cache_head_stride, qwx_stream_t stream);
+
 /* Weight-only int4 GEMM, the fused form of dot_general._slow_dot_general
  * (dot_general.py:264-275, chosen at :444-452 when the activation is not quantized):
  *   out[m, n] = sum_k a[m, k] * ( q[k, n] * scale[k / k_tile, n] )

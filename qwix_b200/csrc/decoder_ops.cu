@@ -1,0 +1,355 @@
+// Element-wise stages of a decoder layer fused with the per-token int8 quantization that
+// feeds the next quantized projection.  The quantization half is qarray.quantize with
+// per-token absmax scales (qwix/_src/core/qarray.py:638-644, the activation side of
+// qwix/_src/providers/boxed_param.py:416-455); the element-wise halves are model code that
+// lives outside qwix (RMSNorm, SwiGLU, rotary embedding of a Llama-style decoder) and are
+// fused here only because every one of them is a full HBM pass over the activations:
+//
+//   add_rmsnorm      x' = bf16(x + delta);  y = bf16( (f32(x') * rsqrt(mean(x'^2) + eps)) * f32(w) )
+//   silu_mul         y = bf16( bf16(silu(g)) * u ),  silu(g) = g / (1 + exp(-g)) in float32
+//   rope_cache       q, k rotated (x1 cos - x2 sin | x2 cos + x1 sin, float32, separate
+//                    roundings), q written head-major, k and v written into the KV cache
+//
+// each followed, when asked, by scale = bf16(absmax(y) / 127.5) (1 if below 2^-63),
+// code = sat_int8(round_half_even(bf16(y / scale))) per row -- the strict recipe of
+// quantize.cu.  Every rounding of the unfused PyTorch composition is kept, so results differ
+// from it only through the order of the float32 sum of squares.
+#include "common.cuh"
+
+namespace qwx {
+namespace {
+
+constexpr int kDThreads = 256;
+constexpr int kDVec = 4;   // 16-byte vectors per thread for register-resident rows (d <= 8192)
+
+__device__ __forceinline__ float block_sum(float v, float* red, int tid) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((tid & 31) == 0) red[tid >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < kDThreads / 32; ++i) t += red[i];
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ uint32_t block_max_bits(uint32_t v, uint32_t* red, int tid) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((tid & 31) == 0) red[tid >> 5] = v;
+  __syncthreads();
+  uint32_t t = 0;
+#pragma unroll
+  for (int i = 0; i < kDThreads / 32; ++i) t = max(t, red[i]);
+  __syncthreads();
+  return t;
+}
+
+// |a|, |b| of a packed bf16 pair as comparable bit patterns (NaN sorts last)
+__device__ __forceinline__ uint32_t abs_bits2(uint32_t w) {
+  return max((w << 16) & 0x7fffffffu, w & 0x7fff0000u);
+}
+
+struct RowQuantizer {
+  float s;
+  bool fast;
+  __nv_bfloat162 r2, ns2;
+  __device__ __forceinline__ explicit RowQuantizer(uint32_t absmax_bits) {
+    const float absmax = __uint_as_float(absmax_bits);
+    s = round_to<BF16>(__fdiv_rn(absmax, 127.5f));
+    if (s < 0x1p-63f) s = 1.0f;
+    const float as = fabsf(s);
+    fast = as > 0x1p-100f && as < 0x1p100f && absmax_bits < 0x7f800000u;
+    const __nv_bfloat16 sb = __float2bfloat16_rn(s);
+    const __nv_bfloat16 rb = __float2bfloat16_rn(__frcp_rn(s));
+    r2 = __halves2bfloat162(rb, rb);
+    ns2 = __hneg2(__halves2bfloat162(sb, sb));
+  }
+  // eight bf16 values (four packed words) -> eight int8 codes
+  __device__ __forceinline__ uint2 codes(const uint32_t (&w)[4]) const {
+    uint32_t packed[2];
+    if (fast) {
+      // Correctly rounded bf16 quotients from three packed bf16 FMAs (Markstein's division,
+      // checked exhaustively over bf16 significands), then round-half-even and saturate.
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        int c[4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(&w[2 * half + j]);
+          const __nv_bfloat162 q0 = __hmul2(xv, r2);
+          const __nv_bfloat162 rem = __hfma2(q0, ns2, xv);
+          const __nv_bfloat162 z = __hfma2(rem, r2, q0);
+          const uint32_t zw = *reinterpret_cast<const uint32_t*>(&z);
+          asm("{ .reg .b16 lo, hi;\n\t mov.b32 {lo, hi}, %2;\n\t"
+              " cvt.rni.s32.bf16 %0, lo;\n\t cvt.rni.s32.bf16 %1, hi; }"
+              : "=r"(c[2 * j]), "=r"(c[2 * j + 1]) : "r"(zw));
+        }
+        uint32_t hi16;
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi16) : "r"(c[3]), "r"(c[2]), "r"(0u));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed[half]) : "r"(c[1]), "r"(c[0]), "r"(hi16));
+      }
+    } else {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t pair = w[2 * half + (e >> 1)];
+          const float xv = __uint_as_float((e & 1) ? (pair & 0xffff0000u) : (pair << 16));
+          const float y = round_to<BF16>(__fdiv_rn(xv, s));
+          word |= (uint32_t)(to_code<S8>(y) & 0xff) << (8 * e);
+        }
+        packed[half] = word;
+      }
+    }
+    return make_uint2(packed[0], packed[1]);
+  }
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// One CTA per row, rows of up to kDThreads * kDVec * 8 values held in registers.
+__global__ void __launch_bounds__(kDThreads)
+add_rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ delta,
+                   const uint4* __restrict__ weight, float eps, int64_t rows, int nvec,
+                   uint4* __restrict__ x_out, uint4* __restrict__ y_out, uint2* __restrict__ q,
+                   __nv_bfloat16* __restrict__ scale) {
+  __shared__ float red_f[kDThreads / 32];
+  __shared__ uint32_t red_u[kDThreads / 32];
+  const int tid = threadIdx.x;
+  const float inv_d = 1.0f / (float)(nvec * 8);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    uint4 cur[kDVec];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < kDVec; ++it) {
+      const int vi = tid + it * kDThreads;
+      if (vi >= nvec) continue;
+      uint4 u = x[row * nvec + vi];
+      if (delta) {
+        // the residual stream is a bf16 tensor: x' = bf16(x + delta)
+        const uint4 dl = delta[row * nvec + vi];
+        float a[8], b[8];
+        unpack_bf16x8(u, a);
+        unpack_bf16x8(dl, b);
+        u = make_uint4(pack_bf16(a[0] + b[0], a[1] + b[1]), pack_bf16(a[2] + b[2], a[3] + b[3]),
+                       pack_bf16(a[4] + b[4], a[5] + b[5]), pack_bf16(a[6] + b[6], a[7] + b[7]));
+        if (x_out) x_out[row * nvec + vi] = u;
+      }
+      cur[it] = u;
+      float v[8];
+      unpack_bf16x8(u, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = __fmaf_rn(v[j], v[j], ss);
+    }
+    ss = block_sum(ss, red_f, tid);
+    const float rs = rsqrtf(__fadd_rn(__fmul_rn(ss, inv_d), eps));
+
+    uint32_t bits = 0;
+#pragma unroll
+    for (int it = 0; it < kDVec; ++it) {
+      const int vi = tid + it * kDThreads;
+      if (vi >= nvec) continue;
+      float v[8], w[8];
+      unpack_bf16x8(cur[it], v);
+      unpack_bf16x8(__ldg(weight + vi), w);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[j] = pack_bf16(__fmul_rn(__fmul_rn(v[2 * j], rs), w[2 * j]),
+                         __fmul_rn(__fmul_rn(v[2 * j + 1], rs), w[2 * j + 1]));
+        bits = max(bits, abs_bits2(o[j]));
+      }
+      cur[it] = make_uint4(o[0], o[1], o[2], o[3]);
+      if (y_out) y_out[row * nvec + vi] = cur[it];
+    }
+    if (q == nullptr) continue;
+    bits = block_max_bits(bits, red_u, tid);
+    const RowQuantizer rq(bits);
+    if (tid == 0) scale[row] = __float2bfloat16_rn(rq.s);
+#pragma unroll
+    for (int it = 0; it < kDVec; ++it) {
+      const int vi = tid + it * kDThreads;
+      if (vi >= nvec) continue;
+      const uint32_t w[4] = {cur[it].x, cur[it].y, cur[it].z, cur[it].w};
+      q[row * nvec + vi] = rq.codes(w);
+    }
+  }
+}
+
+// One CTA per row of [gate | up]; the product row is staged in shared memory (f * 2 bytes)
+// between the absmax pass and the quantizing pass.
+__global__ void __launch_bounds__(kDThreads)
+silu_mul_kernel(const uint4* __restrict__ gu, int64_t rows, int fvec, uint4* __restrict__ y_out,
+                uint2* __restrict__ q, __nv_bfloat16* __restrict__ scale) {
+  extern __shared__ uint4 yrow[];
+  __shared__ uint32_t red_u[kDThreads / 32];
+  const int tid = threadIdx.x;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* g = gu + row * 2 * fvec;
+    const uint4* u = g + fvec;
+    uint32_t bits = 0;
+    for (int vi = tid; vi < fvec; vi += kDThreads) {
+      float a[8], b[8];
+      unpack_bf16x8(g[vi], a);
+      unpack_bf16x8(u[vi], b);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float s0 = a[2 * j] / (1.0f + expf(-a[2 * j]));
+        float s1 = a[2 * j + 1] / (1.0f + expf(-a[2 * j + 1]));
+        s0 = round_to<BF16>(s0);     // F.silu returns a bf16 tensor
+        s1 = round_to<BF16>(s1);
+        o[j] = pack_bf16(__fmul_rn(s0, b[2 * j]), __fmul_rn(s1, b[2 * j + 1]));
+        bits = max(bits, abs_bits2(o[j]));
+      }
+      const uint4 out = make_uint4(o[0], o[1], o[2], o[3]);
+      if (y_out) y_out[row * fvec + vi] = out;
+      if (q) yrow[vi] = out;
+    }
+    if (q == nullptr) continue;
+    bits = block_max_bits(bits, red_u, tid);   // also orders the shared-memory row
+    const RowQuantizer rq(bits);
+    if (tid == 0) scale[row] = __float2bfloat16_rn(rq.s);
+    for (int vi = tid; vi < fvec; vi += kDThreads) {
+      const uint4 v = yrow[vi];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      q[row * fvec + vi] = rq.codes(w);
+    }
+    __syncthreads();   // the row buffer is reused by the next row
+  }
+}
+
+// One thread per (batch, token, head, 8 of the head's first-half values): rotates q and k
+// heads, copies v heads.  qkv: [B, T, (hq + 2 hkv) * hd]; q_out: [B, hq, T, hd];
+// cache_k / cache_v: [B, hkv, S, hd] views given by their batch and head strides (elements).
+__global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t B, int64_t T,
+                                  int hq, int hkv, int hd, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, int64_t pos,
+                                  const int64_t* __restrict__ pos_dev,
+                                  __nv_bfloat16* __restrict__ q_out,
+                                  __nv_bfloat16* __restrict__ cache_k,
+                                  __nv_bfloat16* __restrict__ cache_v, int64_t cache_bs,
+                                  int64_t cache_hs) {
+  const int half = hd / 2, per_head = half / 8;
+  const int heads = hq + 2 * hkv;
+  const int64_t total = B * T * heads * per_head;
+  const int64_t p0 = pos_dev ? *pos_dev : pos;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % per_head);
+    const int h = (int)((i / per_head) % heads);
+    const int64_t t = (i / ((int64_t)per_head * heads)) % T;
+    const int64_t b = i / ((int64_t)per_head * heads * T);
+    const __nv_bfloat16* src = qkv + ((b * T + t) * heads + h) * hd + c * 8;
+    const uint4 u1 = *reinterpret_cast<const uint4*>(src);
+    const uint4 u2 = *reinterpret_cast<const uint4*>(src + half);
+    __nv_bfloat16* dst;
+    if (h < hq) dst = q_out + ((b * hq + h) * T + t) * hd + c * 8;
+    else if (h < hq + hkv) dst = cache_k + b * cache_bs + (h - hq) * cache_hs + (p0 + t) * hd + c * 8;
+    else dst = cache_v + b * cache_bs + (h - hq - hkv) * cache_hs + (p0 + t) * hd + c * 8;
+    if (h >= hq + hkv) {
+      *reinterpret_cast<uint4*>(dst) = u1;
+      *reinterpret_cast<uint4*>(dst + half) = u2;
+      continue;
+    }
+    float x1[8], x2[8];
+    unpack_bf16x8(u1, x1);
+    unpack_bf16x8(u2, x2);
+    const float* cs = cos_t + (p0 + t) * half + c * 8;
+    const float* sn = sin_t + (p0 + t) * half + c * 8;
+    uint32_t o1[4], o2[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float r1[2], r2[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float cv = cs[2 * j + e], sv = sn[2 * j + e];
+        r1[e] = __fsub_rn(__fmul_rn(x1[2 * j + e], cv), __fmul_rn(x2[2 * j + e], sv));
+        r2[e] = __fadd_rn(__fmul_rn(x2[2 * j + e], cv), __fmul_rn(x1[2 * j + e], sv));
+      }
+      o1[j] = pack_bf16(r1[0], r1[1]);
+      o2[j] = pack_bf16(r2[0], r2[1]);
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    *reinterpret_cast<uint4*>(dst + half) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+  }
+}
+
+}  // namespace
+}  // namespace qwx
+
+using namespace qwx;
+
+extern "C" {
+
+int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weight, double eps,
+                             int64_t rows, int64_t d, void* x_out, void* y_out, void* q,
+                             void* scale, qwx_stream_t stream) {
+  if (!x || !weight || (!y_out && !q) || (q && !scale) || (delta && !x_out)) return QWX_ERR_NULL;
+  if (rows <= 0 || d <= 0 || d % 8) return QWX_ERR_SHAPE;
+  if (d > (int64_t)kDThreads * kDVec * 8) return QWX_ERR_UNSUPPORTED;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) |
+                        reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(x_out) |
+                        reinterpret_cast<uintptr_t>(y_out);
+  if ((all & 15) || (reinterpret_cast<uintptr_t>(q) & 7)) return QWX_ERR_ALIGN;
+  const int64_t cap = 148 * 8;
+  const unsigned grid = (unsigned)(rows < cap ? rows : cap);
+  add_rmsnorm_kernel<<<grid, kDThreads, 0, (cudaStream_t)stream>>>(
+      (const uint4*)x, (const uint4*)delta, (const uint4*)weight, (float)eps, rows, (int)(d / 8),
+      (uint4*)x_out, (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+int qwx_silu_mul_quantize(const void* gu, int64_t rows, int64_t f, void* y_out, void* q,
+                          void* scale, qwx_stream_t stream) {
+  if (!gu || (!y_out && !q) || (q && !scale)) return QWX_ERR_NULL;
+  if (rows <= 0 || f <= 0 || f % 8) return QWX_ERR_SHAPE;
+  const size_t smem = q ? (size_t)f * 2 : 0;
+  if (smem > 200 * 1024) return QWX_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(gu) & 15) || (reinterpret_cast<uintptr_t>(y_out) & 15) ||
+      (reinterpret_cast<uintptr_t>(q) & 7))
+    return QWX_ERR_ALIGN;
+  static bool configured = false;  // idempotent attribute; a benign race sets it twice
+  if (!configured) {
+    if (cudaFuncSetAttribute(silu_mul_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024) != cudaSuccess)
+      return QWX_ERR_LAUNCH;
+    configured = true;
+  }
+  const int64_t cap = 148 * 4;
+  const unsigned grid = (unsigned)(rows < cap ? rows : cap);
+  silu_mul_kernel<<<grid, kDThreads, smem, (cudaStream_t)stream>>>(
+      (const uint4*)gu, rows, (int)(f / 8), (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+int qwx_rope_cache(const void* qkv, int64_t B, int64_t T, int hq, int hkv, int hd, const float* cos_t,
+                   const float* sin_t, int64_t pos, const int64_t* pos_dev, void* q_out,
+                   void* cache_k, void* cache_v, int64_t cache_batch_stride,
+                   int64_t cache_head_stride, qwx_stream_t stream) {
+  if (!qkv || !cos_t || !sin_t || !q_out || !cache_k || !cache_v) return QWX_ERR_NULL;
+  if (B <= 0 || T <= 0 || hq <= 0 || hkv <= 0 || hd <= 0 || hd % 16) return QWX_ERR_SHAPE;
+  if (cache_batch_stride % 8 || cache_head_stride % 8) return QWX_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+       reinterpret_cast<uintptr_t>(cache_k) | reinterpret_cast<uintptr_t>(cache_v)) & 15)
+    return QWX_ERR_ALIGN;
+  const int64_t total = B * T * (hq + 2 * hkv) * (hd / 16);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  rope_cache_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)qkv, B, T, hq, hkv, hd, cos_t, sin_t, pos, pos_dev,
+      (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v, cache_batch_stride,
+      cache_head_stride);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+}  // extern "C"

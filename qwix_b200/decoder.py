@@ -25,6 +25,7 @@ import torch
 import torch.nn.functional as F
 
 import qwix_b200 as qwix
+from qwix_b200 import fused
 from qwix_b200 import nn
 from qwix_b200 import ops
 from qwix_b200.core import qarray
@@ -121,6 +122,8 @@ class RowParallelDense(nn.Dense):
     kernel = self.kernel
     if (self.exact_act_scale and self.comm.size > 1 and rule is not None
         and rule.act_qtype is not None and isinstance(kernel, ptq.WithAux)):
+      if isinstance(x, fused.LazyAct):
+        x = x.materialize()
       how = qarray.HowToQuantize(qtype=rule.act_qtype, channelwise_axes=list(range(x.ndim - 1)),
                                  calibration_method=rule.act_calibration_method or 'absmax')
       cal = qarray.calibrate(x, how)
@@ -156,6 +159,17 @@ class Attention(torch.nn.Module):
     B, T, _ = x.shape
     hd = self.cfg.head_dim
     qkv = self.qkv(x)
+    if isinstance(x, fused.LazyAct):
+      # cos / sin are the whole tables here: the kernel indexes them by position, rotates q
+      # and k and writes k and v straight into the cache
+      q = fused.rope_cache(qkv, self.hq, self.hkv, hd, cos, sin, pos, cache_k, cache_v)
+      if isinstance(pos, torch.Tensor):
+        mask = (torch.arange(cache_k.shape[2], device=qkv.device) <= pos).view(1, 1, 1, -1)
+        out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
+      else:
+        out = F.scaled_dot_product_attention(q, cache_k[:, :, :pos + T], cache_v[:, :, :pos + T],
+                                             is_causal=pos == 0, enable_gqa=True)
+      return self.o(out.transpose(1, 2).reshape(B, T, self.hq * hd))
     q, k, v = qkv.split([self.hq * hd, self.hkv * hd, self.hkv * hd], dim=-1)
     q = q.view(B, T, self.hq, hd).transpose(1, 2)
     k = k.view(B, T, self.hkv, hd).transpose(1, 2)
@@ -200,6 +214,8 @@ class FeedForward(torch.nn.Module):
 
   def forward(self, x):
     gu = self.gate_up(x)
+    if isinstance(x, fused.LazyAct):
+      return self.down(fused.SiluMul(gu))
     g, u = gu.split(self.local, dim=-1)
     return self.down(F.silu(g) * u)
 
@@ -216,6 +232,16 @@ class Block(torch.nn.Module):
   def forward(self, x, cos, sin, ck, cv, pos):
     x = x + self.attn(self.attn_norm(x), cos, sin, ck, cv, pos)
     return x + self.ffn(self.ffn_norm(x))
+
+  def forward_fused(self, x, delta, cos, sin, ck, cv, pos):
+    """The same layer with the residual add, the norm and the activation quantization of the
+    next projection in one kernel each.  Takes the residual stream x and the not yet added
+    output `delta` of the previous layer's MLP; returns the new pair."""
+    a = fused.AddRmsNorm(x, delta, self.attn_norm.scale, self.attn_norm.eps)
+    attn_out = self.attn(a, cos, sin, ck, cv, pos)
+    f = fused.AddRmsNorm(a.residual, attn_out, self.ffn_norm.scale, self.ffn_norm.eps)
+    ffn_out = self.ffn(f)
+    return f.residual, ffn_out
 
 
 class Decoder(torch.nn.Module):
@@ -241,6 +267,7 @@ class Decoder(torch.nn.Module):
                             device=self.device)
     self._init_weights(seed, t, r)
     self.cache = None
+    self.fuse = True   # fused element-wise kernels on CUDA bf16 tensors (same arithmetic)
 
   # -- weights ---------------------------------------------------------------------------
 
@@ -319,11 +346,21 @@ class Decoder(torch.nn.Module):
       cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
     else:
       cos, sin = self.cos[pos:pos + T], self.sin[pos:pos + T]
-    for i, blk in enumerate(self.layers):
-      ck = self.cache[i, 0, batch_offset:batch_offset + B]
-      cv = self.cache[i, 1, batch_offset:batch_offset + B]
-      x = blk(x, cos, sin, ck, cv, pos)
-    x = self.final_norm(x[:, -1:] if last_only else x)
+    if self.fuse and x.is_cuda and x.dtype == torch.bfloat16:
+      delta = None
+      for i, blk in enumerate(self.layers):
+        ck = self.cache[i, 0, batch_offset:batch_offset + B]
+        cv = self.cache[i, 1, batch_offset:batch_offset + B]
+        x, delta = blk.forward_fused(x, delta, self.cos, self.sin, ck, cv, pos)
+      if last_only:
+        x, delta = x[:, -1:], delta[:, -1:]
+      x = fused.AddRmsNorm(x, delta, self.final_norm.scale, self.final_norm.eps)
+    else:
+      for i, blk in enumerate(self.layers):
+        ck = self.cache[i, 0, batch_offset:batch_offset + B]
+        cv = self.cache[i, 1, batch_offset:batch_offset + B]
+        x = blk(x, cos, sin, ck, cv, pos)
+      x = self.final_norm(x[:, -1:] if last_only else x)
     logits = self.lm_head(x)
     return self.comm.all_gather_last(logits).float()
 

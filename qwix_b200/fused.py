@@ -1,0 +1,123 @@
+"""Fused element-wise stages of a decoder layer: the activation of a quantized projection is
+produced and quantized in one kernel.
+
+A `LazyAct` stands for "the bf16 tensor this stage would produce".  Model code hands it to a
+projection (`qwix_b200.nn.Dense`, or anything that ends in `ops.dot_general`) like a tensor.
+The provider decides what is needed: under a rule that quantizes activations to int8 with
+per-token absmax scales (`boxed_param.py:416-455` calling `qarray.quantize`, qarray.py:638-644)
+the kernel emits the QArray directly; otherwise the bf16 tensor is materialised.  Either way
+the arithmetic is that of the unfused composition.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from qwix_b200 import _lib
+from qwix_b200.core import qarray
+from qwix_b200.core.qarray import QArray
+
+
+class LazyAct:
+  """An activation [.., features] that has not been computed yet."""
+
+  shape: tuple
+  dtype = torch.bfloat16
+
+  @property
+  def ndim(self) -> int:
+    return len(self.shape)
+
+  def _fusable(self, how: qarray.HowToQuantize) -> bool:
+    method = (how.calibration_method or 'absmax').lower()
+    return (how.qtype == 'int8' and method == 'absmax' and not how.tiled_axes
+            and sorted(how.channelwise_axes) == list(range(self.ndim - 1)))
+
+  def quantized(self, how: qarray.HowToQuantize, _qarray_module=qarray) -> QArray:
+    if not self._fusable(how):
+      return _qarray_module.quantize(self.materialize(), how)
+    rows = 1
+    for n in self.shape[:-1]:
+      rows *= n
+    dev = self.device
+    q = torch.empty(self.shape, dtype=torch.int8, device=dev)
+    scale = torch.empty(tuple(self.shape[:-1]) + (1,), dtype=torch.bfloat16, device=dev)
+    self._run(None, q, scale)
+    return QArray(qvalue=q, scale=scale, zero_point=None, qtype='int8')
+
+  def materialize(self) -> torch.Tensor:
+    y = torch.empty(self.shape, dtype=torch.bfloat16, device=self.device)
+    self._run(y, None, None)
+    return y
+
+  def _run(self, y, q, scale):
+    raise NotImplementedError
+
+
+class AddRmsNorm(LazyAct):
+  """RMSNorm(x + delta) * weight; after it has been consumed, `.residual` is bf16(x + delta)
+  (x itself when delta is None)."""
+
+  def __init__(self, x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
+               eps: float):
+    _lib.require_cuda(x, delta, weight)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+      raise ValueError('AddRmsNorm takes bfloat16 tensors.')
+    self.x = x.contiguous()
+    self.delta = None if delta is None else delta.contiguous()
+    self.weight, self.eps = weight.contiguous(), float(eps)
+    self.shape, self.device = tuple(x.shape), x.device
+    self.residual = self.x if delta is None else None
+
+  def _run(self, y, q, scale):
+    d = self.shape[-1]
+    rows = self.x.numel() // d
+    x_out = None
+    if self.delta is not None:
+      x_out = torch.empty_like(self.x) if self.residual is None else self.residual
+    _lib.check(_lib.lib().qwx_add_rmsnorm_quantize(
+        _lib.ptr(self.x), _lib.ptr(self.delta), _lib.ptr(self.weight), self.eps, rows, d,
+        _lib.ptr(x_out), _lib.ptr(y), _lib.ptr(q), _lib.ptr(scale),
+        _lib.stream_ptr(self.device)), 'add_rmsnorm_quantize')
+    if self.delta is not None:
+      self.residual = x_out
+
+
+class SiluMul(LazyAct):
+  """silu(gate) * up for gu = [.., 2 f] holding [gate | up]."""
+
+  def __init__(self, gu: torch.Tensor):
+    _lib.require_cuda(gu)
+    if gu.dtype != torch.bfloat16 or gu.shape[-1] % 16:
+      raise ValueError('SiluMul takes a bfloat16 tensor whose last extent is 2 f, f % 8 == 0.')
+    self.gu = gu.contiguous()
+    self.f = gu.shape[-1] // 2
+    self.shape, self.device = tuple(gu.shape[:-1]) + (self.f,), gu.device
+
+  def _run(self, y, q, scale):
+    rows = self.gu.numel() // (2 * self.f)
+    _lib.check(_lib.lib().qwx_silu_mul_quantize(
+        _lib.ptr(self.gu), rows, self.f, _lib.ptr(y), _lib.ptr(q), _lib.ptr(scale),
+        _lib.stream_ptr(self.device)), 'silu_mul_quantize')
+
+
+def rope_cache(qkv: torch.Tensor, hq: int, hkv: int, hd: int, cos: torch.Tensor,
+               sin: torch.Tensor, pos, cache_k: torch.Tensor, cache_v: torch.Tensor) -> torch.Tensor:
+  """Rotates the q and k heads of qkv [B, T, (hq + 2 hkv) * hd] with the float32 tables
+  cos/sin [positions, hd / 2], writes k and v into the cache views [B, hkv, S, hd] at
+  positions pos .. pos + T - 1 and returns q as [B, hq, T, hd].  `pos` is an int or a
+  one-element int64 device tensor."""
+  _lib.require_cuda(qkv, cos, sin, cache_k, cache_v)
+  B, T, _ = qkv.shape
+  if (cache_k.stride(3) != 1 or cache_k.stride(2) != hd or cache_v.stride() != cache_k.stride()
+      or cos.dtype != torch.float32 or not cos.is_contiguous() or not sin.is_contiguous()):
+    raise ValueError('rope_cache: unexpected cache or table layout.')
+  qkv = qkv.contiguous()
+  q = torch.empty((B, hq, T, hd), dtype=qkv.dtype, device=qkv.device)
+  pos_dev = pos if isinstance(pos, torch.Tensor) else None
+  _lib.check(_lib.lib().qwx_rope_cache(
+      _lib.ptr(qkv), B, T, hq, hkv, hd, _lib.ptr(cos), _lib.ptr(sin),
+      0 if pos_dev is not None else int(pos), _lib.ptr(pos_dev), _lib.ptr(q), _lib.ptr(cache_k),
+      _lib.ptr(cache_v), cache_k.stride(0), cache_k.stride(1), _lib.stream_ptr(qkv.device)),
+      'rope_cache')
+  return q

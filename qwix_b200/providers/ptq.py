@@ -16,6 +16,7 @@ from typing import Any, Callable, Generic, Mapping, Sequence, TypeVar
 import torch
 
 from qwix_b200 import _context
+from qwix_b200 import fused
 from qwix_b200 import qconfig
 from qwix_b200.core import dot as dot_lib
 from qwix_b200.core import dot_general as dot_general_lib
@@ -95,6 +96,8 @@ class BoxedParamProvider(qconfig.QuantizationProvider):
                         calibration_method=rule.act_calibration_method)
       lhs = quantize_act(lhs, lhs_how, rule, op_id + '_lhs',
                          _qarray_module=self._qarray_module)
+    elif isinstance(lhs, fused.LazyAct):  # weight-only rule: the activation stays floating
+      lhs = lhs.materialize()
     return lhs, rhs
 
   def dot_general(self, lhs, rhs, dimension_numbers, precision=None,
@@ -102,7 +105,7 @@ class BoxedParamProvider(qconfig.QuantizationProvider):
     """boxed_param.py:109-171."""
     rule, op_id = self._get_current_rule_and_op_id('dot_general')
     if rule is None or rule.weight_qtype is None:
-      rhs = _plain(rhs)
+      lhs, rhs = _plain(lhs), _plain(rhs)
       return dot_general_lib._plain_dot_general(lhs, rhs, dimension_numbers,
                                                 preferred_element_type)
     get_how = functools.partial(dot_general_lib.get_how_to_quantize,
@@ -153,6 +156,8 @@ class PtqProvider(BoxedParamProvider):
 
 
 def _plain(x):
+  if isinstance(x, fused.LazyAct):
+    return x.materialize()
   if isinstance(x, WithAux):
     x = x.array
   return qarray.dequantize(x) if isinstance(x, qarray.QArray) else x
@@ -161,7 +166,13 @@ def _plain(x):
 def quantize_act(array: torch.Tensor, how: qarray.HowToQuantize,
                  rule: qconfig.QuantizationRule, act_name: str, *,
                  _qarray_module=qarray) -> qarray.QArray:
-  """boxed_param.py:416-455 -- dynamic range, or a static scale kept on the module."""
+  """boxed_param.py:416-455 -- dynamic range, or a static scale kept on the module.  A
+  fused.LazyAct (an activation whose producing kernel can quantize on the way out) is asked
+  for the QArray directly."""
+  if isinstance(array, fused.LazyAct):
+    if not rule.act_static_scale:
+      return array.quantized(how, _qarray_module=_qarray_module)
+    array = array.materialize()
   if not rule.act_static_scale:
     return _qarray_module.quantize(array, how)
   module = _context.current_module()

@@ -1,0 +1,105 @@
+"""GPU parity of the fused decoder stages against their unfused PyTorch composition and
+against the quantizer applied to their own floating-point output."""
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from qwix_b200 import fused
+from qwix_b200.core import qarray as bq
+
+pytestmark = pytest.mark.gpu
+
+HOW = lambda nd: bq.HowToQuantize(qtype='int8', channelwise_axes=list(range(nd - 1)))
+
+
+def _rmsnorm(x, w, eps):
+  v = x.float()
+  v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+  return (v * w.float()).to(x.dtype)
+
+
+@pytest.mark.parametrize('shape', [(32, 1, 4096), (3, 50, 1024), (2, 7, 8192), (5, 136)])
+@pytest.mark.parametrize('with_delta', [False, True])
+def test_add_rmsnorm_matches_unfused(shape, with_delta):
+  g = torch.Generator(device='cuda').manual_seed(sum(shape))
+  x = torch.randn(shape, device='cuda', generator=g).to(torch.bfloat16)
+  x[..., :3] *= 30
+  x[0].reshape(-1, shape[-1])[0] = 0       # a zero row: y = 0, scale 1, codes 0
+  delta = (0.5 * torch.randn(shape, device='cuda', generator=g)).to(torch.bfloat16) if with_delta else None
+  w = (1 + 0.1 * torch.randn(shape[-1], device='cuda', generator=g)).to(torch.bfloat16)
+  eps = 1e-5
+  xs = x + delta if with_delta else x
+  want = _rmsnorm(xs, w, eps)
+
+  a = fused.AddRmsNorm(x, delta, w, eps)
+  y = a.materialize()
+  assert torch.equal(a.residual, xs)
+  # only the order of the float32 sum of squares differs: at most one bf16 ulp, almost never
+  diff = (y.float() - want.float()).abs()
+  assert torch.all(diff <= 2.0 ** -7 * want.float().abs().clamp_min(2.0 ** -20))
+  assert (y == want).float().mean() > 0.995
+
+  b = fused.AddRmsNorm(x, delta, w, eps)
+  qa = b.quantized(HOW(len(shape)))
+  ref = bq.quantize(y, HOW(len(shape)))        # the quantizer on the kernel's own output
+  assert torch.equal(qa.qvalue, ref.qvalue)
+  assert torch.equal(qa.scale.view(torch.int16), ref.scale.view(torch.int16))
+  assert qa.scale.shape == ref.scale.shape
+  assert torch.equal(b.residual, xs)
+
+
+@pytest.mark.parametrize('shape', [(32, 1, 2 * 14336), (4, 33, 2 * 1024), (6, 2 * 72)])
+def test_silu_mul_matches_unfused(shape):
+  g = torch.Generator(device='cuda').manual_seed(sum(shape))
+  gu = (2 * torch.randn(shape, device='cuda', generator=g)).to(torch.bfloat16)
+  f = shape[-1] // 2
+  want = F.silu(gu[..., :f]) * gu[..., f:]
+  y = fused.SiluMul(gu).materialize()
+  mism = (y != want)
+  # expf / division are the same float32 operations: identical up to rare last-bit cases
+  assert mism.float().mean() < 1e-3
+  assert torch.all((y.float() - want.float()).abs() <= 2.0 ** -7 * want.float().abs().clamp_min(2.0 ** -30))
+  qa = fused.SiluMul(gu).quantized(HOW(len(shape)))
+  ref = bq.quantize(y, HOW(len(shape)))
+  assert torch.equal(qa.qvalue, ref.qvalue)
+  assert torch.equal(qa.scale.view(torch.int16), ref.scale.view(torch.int16))
+
+
+def test_lazy_act_other_rules_fall_back():
+  gu = torch.randn((4, 2 * 256), device='cuda').to(torch.bfloat16)
+  how = bq.HowToQuantize(qtype='int8', channelwise_axes=[0], tiled_axes={1: 128})
+  qa = fused.SiluMul(gu).quantized(how)
+  ref = bq.quantize(fused.SiluMul(gu).materialize(), how)
+  assert torch.equal(qa.qvalue, ref.qvalue) and qa.scale.shape == ref.scale.shape
+
+
+@pytest.mark.parametrize('tensor_pos', [False, True])
+def test_rope_cache_matches_unfused(tensor_pos):
+  B, T, hq, hkv, hd, S = 3, (1 if tensor_pos else 5), 4, 2, 128, 40
+  g = torch.Generator(device='cuda').manual_seed(1)
+  qkv = torch.randn((B, T, (hq + 2 * hkv) * hd), device='cuda', generator=g).to(torch.bfloat16)
+  pos = 7
+  ang = torch.arange(S, device='cuda', dtype=torch.float32)[:, None] * (
+      1.0 / (10000.0 ** (torch.arange(0, hd, 2, device='cuda', dtype=torch.float32) / hd)))[None, :]
+  cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+  cache = torch.zeros((2, B + 2, hkv, S, hd), dtype=torch.bfloat16, device='cuda')
+  ck, cv = cache[0, 1:1 + B], cache[1, 1:1 + B]          # views with a batch offset
+  p = torch.tensor([pos], device='cuda') if tensor_pos else pos
+  q = fused.rope_cache(qkv, hq, hkv, hd, cos, sin, p, ck, cv)
+
+  def rope(x, c, s):
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+  qq, kk, vv = qkv.split([hq * hd, hkv * hd, hkv * hd], dim=-1)
+  qq = qq.view(B, T, hq, hd).transpose(1, 2)
+  kk = kk.view(B, T, hkv, hd).transpose(1, 2)
+  vv = vv.view(B, T, hkv, hd).transpose(1, 2)
+  c, s = cos[pos:pos + T], sin[pos:pos + T]
+  assert torch.equal(q, rope(qq, c, s))
+  assert torch.equal(ck[:, :, pos:pos + T], rope(kk, c, s))
+  assert torch.equal(cv[:, :, pos:pos + T], vv)
+  # nothing else in the cache was touched
+  assert int(cache.count_nonzero()) == int(ck[:, :, pos:pos + T].count_nonzero() + cv[:, :, pos:pos + T].count_nonzero())
