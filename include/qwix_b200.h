@@ -172,6 +172,19 @@ int qwx_gemm_q8_ws(const void* a, const void* b, int code_dtype, int b_layout,
                    void* workspace, size_t workspace_bytes, int workspace_is_zero,
                    int32_t* error_flag, qwx_stream_t stream);
 
+/* The same product for at most 32 rows of int8 activations against an int8 weight held
+ * [N, K] (the decode step of a served model): a warp-level kernel that streams the weight
+ * once with no per-tile set-up.  K a multiple of 256, N of 16.  out_dtype as qwx_gemm_q8
+ * (QWX_S32 with both scales NULL for the raw accumulator); int32 partial sums are exact, so
+ * the result is bit-identical to qwx_gemm_q8.  workspace: qwx_gemm_q8_skinny_workspace_bytes
+ * bytes, zero on entry (workspace_is_zero = 0 clears it first), left zero.  The reference
+ * has no counterpart: XLA picks its own kernel for the shape. */
+size_t qwx_gemm_q8_skinny_workspace_bytes(int64_t M, int64_t N);
+int qwx_gemm_q8_skinny(const void* a, const void* w, int64_t M, int64_t N, int64_t K,
+                       const void* sa, const void* sb, int scale_dtype, void* out, int out_dtype,
+                       int epilogue, void* workspace, size_t workspace_bytes,
+                       int workspace_is_zero, qwx_stream_t stream);
+
 /* The general dequantize-on-output contraction of dot_general._fast_dot_general
  * (dot_general.py:135-261): scales that change along K (sub-channel quantization, the tiled
  * contracting axis of :187-203 and the tile sum of :259) and the zero-point correction of an

@@ -23,6 +23,10 @@ from qwix_b200.core.qarray import QArray
 # Tiles smaller than this on a contracting axis force the dequantize-first path
 # (dot_general.py:402-404).
 MIN_TILE_SIZE_TO_DEQUANT_ON_OUTPUT = 128
+# Rows up to which an [N, K] int8 weight takes the warp-level kernel: measured against the
+# split-K tcgen05 kernel it wins up to 8 rows (9-17 us against 15-23 us on 16-58 MB weights,
+# 6.0 against 5.0 TB/s on 525 MB) and loses from 32 rows on, where its MMAs crowd the loads.
+SKINNY_MAX_ROWS = 8
 
 # 'f32': float(acc) * sa * sb in float32, rounded once (default).  'reference': every step
 # rounds to the result dtype in the reference's order (dot_general.py:255-261).
@@ -232,6 +236,17 @@ def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
           scale_code, _lib.ptr(None if corr_row is None else corr_row[b]),
           _lib.ptr(None if corr_col is None else corr_col[b]), _lib.ptr(out[b]),
           _out_code(out_t), epi, _lib.ptr(err), stream), 'dot_general')
+  elif (code == _lib.S8 and layout == _lib.B_NK and M <= SKINNY_MAX_ROWS and K % 256 == 0
+        and N % 16 == 0):
+    # decode-shaped: the warp-level kernel streams the [N, K] weight once
+    ws_bytes = L.qwx_gemm_q8_skinny_workspace_bytes(M, N)
+    ws = _splitk_workspace(lq.device, ws_bytes, 'skinny')
+    for b in range(B):
+      _lib.check(L.qwx_gemm_q8_skinny(
+          _lib.ptr(a3[b]), _lib.ptr(b3[b]), M, N, K,
+          _lib.ptr(None if ls is None else ls[b]), _lib.ptr(None if rs is None else rs[b]),
+          scale_code, _lib.ptr(out[b]), _out_code(out_t), epi, _lib.ptr(ws), ws.numel(), 1,
+          stream), 'dot_general')
   else:
     ws_bytes = L.qwx_gemm_q8_workspace_bytes(M, N, K)
     ws = _splitk_workspace(lq.device, ws_bytes) if ws_bytes else None
@@ -249,11 +264,11 @@ _ws_lock = threading.Lock()
 _ws_cache: dict = {}
 
 
-def _splitk_workspace(device, nbytes: int) -> torch.Tensor:
-  """Zero-filled scratch for the split-K form of the GEMM, one per (device, stream).  The
-  kernel leaves it zero and calls on one stream run in order, so it is cleared only when it
-  is created or grown."""
-  key = (device, torch.cuda.current_stream(device).cuda_stream)
+def _splitk_workspace(device, nbytes: int, kind: str = 'split') -> torch.Tensor:
+  """Zero-filled scratch for the split-K and the decode-shaped form of the GEMM, one per
+  (device, stream, kind).  The kernels leave what they need zero and calls on one stream run
+  in order, so it is cleared only when it is created or grown."""
+  key = (device, torch.cuda.current_stream(device).cuda_stream, kind)
   with _ws_lock:
     ws = _ws_cache.get(key)
     if ws is None or ws.numel() < nbytes:

@@ -310,6 +310,10 @@ class Decoder(torch.nn.Module):
         cal = {k: self.comm.all_reduce_max(v) for k, v in cal.items()}
         scale, _ = qarray.compute_scale_zero_point(cal, qtype)
         qa = qarray.quantize_with_scale_zero_point(w, qtype, scale, None)
+      # Store the codes [N, K] (K contiguous): the layout the decode-step kernel streams; the
+      # logical [K, N] qvalue is its transposed view and the prefill kernels take either order.
+      qa = qarray.QArray(qvalue=qa.qvalue.t().contiguous().t(), scale=qa.scale,
+                         zero_point=qa.zero_point, qtype=qa.qtype)
       del mod._parameters['kernel']
       mod.kernel = ptq.WithAux(qa, how)
 

@@ -115,6 +115,66 @@ def test_split_k_workspace_query_and_errors():
   assert rc == 6  # QWX_ERR_WORKSPACE
 
 
+SKINNY_SHAPES = [(1, 4096, 4096), (8, 512, 1024), (17, 48, 14336), (32, 6144, 4096), (32, 1024, 14336),
+                 (5, 16, 256), (32, 128256 // 8, 512)]
+
+
+@pytest.mark.parametrize('mnk', SKINNY_SHAPES, ids=[f'{m}x{n}x{k}' for m, n, k in SKINNY_SHAPES])
+def test_skinny_int8_bit_exact(mnk):
+  """The warp-level decode kernel ([N, K] weight, at most 32 rows): raw accumulators against
+  NumPy, scaled bf16 output against the tcgen05 kernel, workspace reusable."""
+  M, N, K = mnk
+  rng = np.random.default_rng(M + N + K)
+  a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+  w = rng.integers(-128, 128, (N, K), dtype=np.int8)
+  want = a.astype(np.int32) @ w.astype(np.int32).T
+  at, wt = h.to_torch(a), h.to_torch(w)
+  L = _lib.lib()
+  need = L.qwx_gemm_q8_skinny_workspace_bytes(M, N)
+  ws = torch.zeros(need, dtype=torch.uint8, device='cuda')
+  out = torch.empty((M, N), dtype=torch.int32, device='cuda')
+  _lib.check(L.qwx_gemm_q8_skinny(_lib.ptr(at), _lib.ptr(wt), M, N, K, None, None, _lib.F32,
+                                  _lib.ptr(out), _lib.S32, 0, _lib.ptr(ws), need, 1,
+                                  _lib.stream_ptr()), 'skinny')
+  torch.cuda.synchronize()
+  assert np.array_equal(out.cpu().numpy(), want)
+  assert int(ws.count_nonzero().item()) == 0
+  sa = (torch.rand(M, device='cuda') + 0.5).to(torch.bfloat16)
+  sb = (torch.rand(N, device='cuda') * 1e-3).to(torch.bfloat16)
+  got = torch.empty((M, N), dtype=torch.bfloat16, device='cuda')
+  _lib.check(L.qwx_gemm_q8_skinny(_lib.ptr(at), _lib.ptr(wt), M, N, K, _lib.ptr(sa), _lib.ptr(sb),
+                                  _lib.BF16, _lib.ptr(got), _lib.BF16, 0, _lib.ptr(ws), need, 1,
+                                  _lib.stream_ptr()), 'skinny')
+  ref = torch.empty_like(got)
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  _lib.check(L.qwx_gemm_q8(_lib.ptr(at), _lib.ptr(wt), _lib.S8, _lib.B_NK, M, N, K, 0, _lib.ptr(sa), 0,
+                           _lib.ptr(sb), 0, _lib.BF16, _lib.ptr(ref), _lib.BF16, 0, _lib.ptr(err),
+                           _lib.stream_ptr()), 'gemm')
+  torch.cuda.synchronize()
+  assert torch.equal(got.view(torch.int16), ref.view(torch.int16))
+  assert int(ws.count_nonzero().item()) == 0
+
+
+def test_dot_general_takes_the_skinny_kernel_for_nk_weights():
+  M, K, N = 8, 1024, 512
+  rng = np.random.default_rng(2)
+  x = rng.standard_normal((M, K)).astype(np.float32)
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32)
+  kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=None, qtype='int8')
+  xo = oq.quantize(x, odg.get_how_to_quantize(for_lhs=True, **kw))
+  wo = oq.quantize(w, odg.get_how_to_quantize(for_lhs=False, **kw))
+  want = odg.dot_general(xo, wo, DN)
+  xq = bq.quantize(h.to_torch(x), bdg.get_how_to_quantize(for_lhs=True, **kw))
+  wq = bq.quantize(h.to_torch(w), bdg.get_how_to_quantize(for_lhs=False, **kw))
+  # the same codes stored [N, K]: the logical [K, N] qvalue is a transposed view
+  wq_nk = bq.QArray(qvalue=wq.qvalue.t().contiguous().t(), scale=wq.scale, zero_point=None,
+                    qtype=wq.qtype)
+  got_kn = bdg.dot_general(xq, wq, DN)
+  got_nk = bdg.dot_general(xq, wq_nk, DN)
+  assert torch.equal(got_kn, got_nk)
+  _close(got_nk, want)
+
+
 SHAPES = [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (384, 768, 4096),
           (100, 200 + 8, 256 + 16), (1, 16, 128), (130, 272, 144), (512, 1024, 8192)]
 
