@@ -7,6 +7,7 @@
 //
 //   add_rmsnorm      x' = bf16(x + delta);  y = bf16( (f32(x') * rsqrt(mean(x'^2) + eps)) * f32(w) )
 //   silu_mul         y = bf16( bf16(silu(g)) * u ),  silu(g) = g / (1 + exp(-g)) in float32
+//                    (fast exp and division: differs from libm in about 1 value in 10^4)
 //   rope_cache       q, k rotated (x1 cos - x2 sin | x2 cos + x1 sin, float32, separate
 //                    roundings), q written head-major, k and v written into the KV cache
 //
@@ -201,8 +202,10 @@ silu_mul_kernel(const uint4* __restrict__ gu, int64_t rows, int fvec, uint4* __r
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float s0 = a[2 * j] / (1.0f + expf(-a[2 * j]));
-        float s1 = a[2 * j + 1] / (1.0f + expf(-a[2 * j + 1]));
+        // exp and the quotient with the fast float32 forms (2 ulp each): the bf16 rounding
+        // that follows hides them except in about one value in 10^4
+        float s0 = __fdividef(a[2 * j], 1.0f + __expf(-a[2 * j]));
+        float s1 = __fdividef(a[2 * j + 1], 1.0f + __expf(-a[2 * j + 1]));
         s0 = round_to<BF16>(s0);     // F.silu returns a bf16 tensor
         s1 = round_to<BF16>(s1);
         o[j] = pack_bf16(__fmul_rn(s0, b[2 * j]), __fmul_rn(s1, b[2 * j + 1]));
