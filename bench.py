@@ -205,6 +205,36 @@ def reference_arm(args, rank: int):
 # BASELINE configs[4]: Llama-3-8B-shaped w8a8 decoder, tensor-parallel over the ranks
 # ---------------------------------------------------------------------------------------------
 
+def _decoder_kernel_breakdown(ptq_model, tokens, batch, layers):
+  """Device time per kernel of one eager decode step and of one prefill chunk (PyTorch
+  profiler); prints two tables.  For profiles/, not a timed result."""
+  from torch.profiler import profile, ProfilerActivity
+  dec = ptq_model.model
+
+  def table(prof, n, title):
+    rows = {}
+    for e in prof.events():
+      if e.device_type.name == 'CUDA':
+        r = rows.setdefault(e.name[:100], [0, 0.0])
+        r[0] += 1
+        r[1] += e.device_time
+    total = sum(v[1] for v in rows.values())
+    print(f'---- {title}: {total / n:.1f} us of kernels ({layers} layers) ----')
+    for k, v in sorted(rows.items(), key=lambda kv: -kv[1][1])[:24]:
+      print(f'{v[0] / n:7.1f} x {v[1] / v[0]:8.1f} us = {v[1] / n:9.1f} us  {k}')
+
+  runner = dec._step_graphs[batch]
+  with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+    for _ in range(3):
+      runner.step()
+    torch.cuda.synchronize()
+  table(prof, 3, 'one decode step, eager')
+  with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+    ptq_model(tokens[:4], 0, 0)
+    torch.cuda.synchronize()
+  table(prof, 1, f'one prefill chunk of 4 x {tokens.shape[1]} tokens')
+
+
 def decoder_workload(args):
   """batch x prompt-token prefill plus `decode` greedy tokens per sequence; tokens/s of the
   whole job.  Not the line the round-end driver reads (that is the GEMM workload)."""
@@ -237,6 +267,9 @@ def decoder_workload(args):
 
   # warm-up: every kernel shape of the real run, and the one-time capture of the decode step
   D.generate(ptq_model, tokens, steps=3, prefill_batch=4)
+  if args.kernel_breakdown:
+    _decoder_kernel_breakdown(ptq_model, tokens, args.batch, cfg.layers)
+    return
   runs, phases = [], {}
   for _ in range(max(1, min(args.steps, 3))):
     sync()
@@ -291,6 +324,9 @@ def main():
   ap.add_argument('--prompt', type=int, default=2048)
   ap.add_argument('--decode', type=int, default=128)
   ap.add_argument('--exact-act-scale', action='store_true')
+  ap.add_argument('--kernel-breakdown', action='store_true',
+                  help='decoder workload: print device time per kernel of a decode step and a '
+                       'prefill chunk instead of timing the run')
   args = ap.parse_args()
   if args.workload == 'decoder':
     return decoder_workload(args)
