@@ -205,6 +205,87 @@ def reference_arm(args, rank: int):
 # BASELINE configs[4]: Llama-3-8B-shaped w8a8 decoder, tensor-parallel over the ranks
 # ---------------------------------------------------------------------------------------------
 
+def _time_calls(fn, steps, warmup):
+  for i in range(warmup):
+    fn(i)
+  torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for i in range(steps):
+    fn(i)
+  e1.record()
+  torch.cuda.synchronize()
+  return e0.elapsed_time(e1) / steps
+
+
+def w4_workload(args):
+  """BASELINE configs[2]: int4 weight-only decode GEMM, W [8192, 28672] with 128-wide scale
+  tiles, bf16 activations of 1 / 16 / 128 tokens (--m).  One extra bench line, HBM-bound."""
+  from qwix_b200 import _lib
+  from qwix_b200.core import qarray as bq, weight_only
+  torch.cuda.set_device(0)
+  Kw, Nw, Mw = 8192, 28672, args.m or 16
+  L = _lib.lib()
+  sets = []
+  for i in range(3):   # 3 x 125 MB of weights cycled: no step finds its weight in L2
+    w = torch.randn(Kw, Nw, device='cuda', dtype=torch.bfloat16, generator=torch.Generator('cuda').manual_seed(3 + i)) * 0.02
+    wq = bq.quantize_api(w, 'int4', channelwise_axes=[1], tiled_axes={0: 128}, scale_dtype=torch.float32)
+    weight_only.prepare(wq)
+    sets.append(wq)
+    del w
+  a = torch.randn(Mw, Kw, device='cuda', dtype=torch.bfloat16, generator=torch.Generator('cuda').manual_seed(4))
+  out = torch.empty(Mw, Nw, device='cuda', dtype=torch.bfloat16)
+  ws = torch.zeros(L.qwx_gemm_a16w4_workspace_bytes(Mw, Nw), dtype=torch.uint8, device='cuda')
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+
+  def call(i):
+    wq = sets[i % len(sets)]
+    _lib.check(L.qwx_gemm_a16w4(_lib.ptr(a), _lib.ptr(wq._w4_packed), _lib.ptr(wq._w4_scale), _lib.F32,
+                                Mw, Nw, Kw, 128, _lib.ptr(out), _lib.BF16, _lib.ptr(ws), ws.numel(), 1,
+                                _lib.ptr(err), _lib.stream_ptr()), 'gemm_a16w4')
+  ms = _time_calls(call, args.steps, max(args.warmup, 3))
+  nbytes = Kw * Nw // 2 + (Kw // 128) * Nw * 4 + Mw * Kw * 2 + Mw * Nw * 2
+  peaks = _peaks()
+  print(json.dumps({
+      'metric': 'int4 weight-only GEMM GB/s', 'value': nbytes / ms / 1e6, 'unit': 'GB/s', 'n_gpus': 1,
+      'steps': args.steps, 'ms_per_step': ms, 'higher_is_better': True, 'dtype': 'bf16 x int4',
+      'data': 'synthetic',
+      'config': {'workload': 'a16w4 decode GEMM, BASELINE configs[2]', 'M': Mw, 'K': Kw, 'N': Nw,
+                 'scale_tile': 128, 'l2': '3 weight sets (375 MB) cycled'},
+      'roofline': {'bound': 'hbm', 'achieved': nbytes / ms / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
+                   'frac': nbytes / ms / 1e6 / peaks['hbm_gbs'], 'traffic': None,
+                   'kernel': 'gemm_w4_kernel', 'peak_source': peaks['source']}}))
+
+
+def hadamard_workload(args):
+  """BASELINE configs[3]: A [8192, 4096] bf16 rotated by 128-point Hadamard blocks, quantized
+  to e4m3 per row, times the offline-rotated e4m3 weight [4096, 14336]."""
+  from qwix_b200.contrib import hadamard as bhd
+  torch.cuda.set_device(0)
+  Mh, Kh, Nh = 8192, 4096, 14336
+  acts = [(0.5 * torch.distributions.StudentT(3.0).sample((Mh, Kh))).to(torch.bfloat16).cuda()
+          for _ in range(3)]
+  w = (torch.randn(Kh, Nh, generator=torch.Generator().manual_seed(6)) * 0.02).to(torch.bfloat16).cuda()
+  wq = bhd.quantize_rotated_weight(w)
+  ms = _time_calls(lambda i: bhd.hadamard_quantize_multiply(acts[i % 3], wq), args.steps, max(args.warmup, 3))
+  ms_q = _time_calls(lambda i: bhd.hadamard_quantize(acts[i % 3]), args.steps, max(args.warmup, 3))
+  flops = 2.0 * Mh * Nh * Kh
+  peaks = _peaks()
+  peak = 2 * peaks['bf16_burst']
+  print(json.dumps({
+      'metric': 'Hadamard-quantized fp8 GEMM TFLOP/s', 'value': flops / ms / 1e9, 'unit': 'TFLOP/s',
+      'n_gpus': 1, 'steps': args.steps, 'ms_per_step': ms, 'higher_is_better': True, 'dtype': 'e4m3',
+      'data': 'synthetic',
+      'config': {'workload': 'rotate + e4m3 quantize + GEMM, BASELINE configs[3]', 'M': Mh, 'K': Kh,
+                 'N': Nh, 'block': 128, 'l2': '3 activation sets (201 MB) cycled'},
+      'roofline': {'bound': 'tensor', 'achieved': flops / ms / 1e9, 'peak': peak, 'unit': 'TFLOP/s',
+                   'frac': flops / ms / 1e9 / peak, 'traffic': None,
+                   'kernel': 'hadamard_quantize_blocks_kernel + gemm_q8_pair_kernel<f8f6f4>',
+                   'rotate_quantize_ms': ms_q, 'rotate_quantize_gbs': Mh * Kh * 3 / ms_q / 1e6,
+                   'hbm_peak_gbs': peaks['hbm_gbs'],
+                   'peak_source': '2 x bf16_tflops (burst), ' + peaks['source']}}))
+
+
 def _decoder_kernel_breakdown(ptq_model, tokens, batch, layers):
   """Device time per kernel of one eager decode step and of one prefill chunk (PyTorch
   profiler); prints two tables.  For profiles/, not a timed result."""
@@ -317,7 +398,7 @@ def main():
   ap.add_argument('--no-cpu-baseline', action='store_true')
   ap.add_argument('--m', type=int, default=None,
                   help='token rows per step (profiling aid; the benchmark uses 4096)')
-  ap.add_argument('--workload', default='gemm', choices=['gemm', 'decoder'],
+  ap.add_argument('--workload', default='gemm', choices=['gemm', 'decoder', 'w4', 'hadamard'],
                   help="'decoder': BASELINE configs[4], tensor-parallel over the launched ranks")
   ap.add_argument('--layers', type=int, default=32)
   ap.add_argument('--batch', type=int, default=32)
@@ -330,6 +411,10 @@ def main():
   args = ap.parse_args()
   if args.workload == 'decoder':
     return decoder_workload(args)
+  if args.workload == 'w4':
+    return w4_workload(args)
+  if args.workload == 'hadamard':
+    return hadamard_workload(args)
   args.warmup = max(args.warmup, 3)
   if args.m is not None:
     global M, OPS_PER_STEP
