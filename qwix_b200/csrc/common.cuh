@@ -164,4 +164,22 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+
+// Function attributes (the dynamic shared-memory limit) are per device: a launch site keeps
+// one of these and sets its attributes the first time it runs on each device.  The flags are
+// idempotent; a benign race sets an attribute twice.
+struct PerDeviceOnce {
+  bool done[64] = {};
+  // true when the caller still has to configure the current device
+  bool first() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return true;
+    return !done[d];
+  }
+  void mark() {
+    int d = 0;
+    if (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 64) done[d] = true;
+  }
+};
+
 }  // namespace qwx

@@ -319,12 +319,12 @@ int qwx_silu_mul_quantize(const void* gu, int64_t rows, int64_t f, void* y_out, 
   if ((reinterpret_cast<uintptr_t>(gu) & 15) || (reinterpret_cast<uintptr_t>(y_out) & 15) ||
       (reinterpret_cast<uintptr_t>(q) & 7))
     return QWX_ERR_ALIGN;
-  static bool configured = false;  // idempotent attribute; a benign race sets it twice
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(silu_mul_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              200 * 1024) != cudaSuccess)
       return QWX_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   const int64_t cap = 148 * 4;
   const unsigned grid = (unsigned)(rows < cap ? rows : cap);

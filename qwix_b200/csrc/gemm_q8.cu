@@ -388,12 +388,12 @@ template <MmaKind KIND, int BLAYOUT>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
            cudaStream_t st) {
   auto kern = gemm_q8_kernel<KIND, BLAYOUT>;
-  static bool configured = false;  // idempotent attribute; a benign race sets it twice
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) !=
         cudaSuccess)
       return QWX_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   kern<<<grid, kGemmThreads, kSmemBytes, st>>>(ta, tb, p);
   QWX_CHECK_LAUNCH();

@@ -326,12 +326,12 @@ template <MmaKind KIND, int BLAYOUT>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const PairParams& p, int grid,
                 cudaStream_t st) {
   auto kern = gemm_q8_pair_kernel<KIND, BLAYOUT>;
-  static bool configured = false;  // idempotent attribute; a benign race sets it twice
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kPSmemBytes) != cudaSuccess)
       return QWX_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   kern<<<grid, kPThreads, kPSmemBytes, st>>>(ta, tb, p);
   QWX_CHECK_LAUNCH();

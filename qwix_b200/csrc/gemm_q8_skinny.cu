@@ -297,14 +297,14 @@ int qwx_gemm_q8_skinny(const void* a, const void* w, int64_t M, int64_t N, int64
   if (!workspace_is_zero && cudaMemsetAsync(workspace, 0, need, st) != cudaSuccess)
     return QWX_ERR_LAUNCH;
 
-  static bool configured = false;  // idempotent attributes; a benign race sets them twice
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     const int cap = (int)kSActCap + 1024;
     if (cudaFuncSetAttribute(gemm_q8_skinny_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
         cudaFuncSetAttribute(gemm_q8_skinny_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
         cudaFuncSetAttribute(gemm_q8_skinny_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess)
       return QWX_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   const int sms = sm_count_s();
   if (sms <= 0) return QWX_ERR_NO_DEVICE;

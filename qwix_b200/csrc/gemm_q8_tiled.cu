@@ -367,12 +367,12 @@ template <MmaKind KIND, int BLAYOUT>
 int launch_tiled(const CUtensorMap& ta, const CUtensorMap& tb, const TiledParams& p, int grid,
                  cudaStream_t st) {
   auto kern = gemm_q8_tiled_kernel<KIND, BLAYOUT>;
-  static bool configured = false;  // idempotent attribute; a benign race sets it twice
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kSmemBytesT) != cudaSuccess)
       return QWX_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   kern<<<grid, kThreadsT, kSmemBytesT, st>>>(ta, tb, p);
   QWX_CHECK_LAUNCH();

@@ -424,14 +424,14 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
       cudaMemsetAsync(workspace, 0, qwx_gemm_a16w4_workspace_bytes(M, N), st) != cudaSuccess)
     return QWX_ERR_LAUNCH;
 
-  static bool configured = false;  // idempotent attributes; a benign race sets them twice
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     const int cap = (int)kSmemCap;
     if (cudaFuncSetAttribute(gemm_w4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
         cudaFuncSetAttribute(gemm_w4_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
         cudaFuncSetAttribute(gemm_w4_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess)
       return QWX_ERR_LAUNCH;
-    configured = true;
+    configured.mark();
   }
   const int sms = sm_count_w4();
   if (sms <= 0) return QWX_ERR_NO_DEVICE;

@@ -398,14 +398,14 @@ int qwx_hadamard_quantize(const void* x, int x_dtype, int64_t rows, int64_t K, i
     const int64_t groups = (rows * nblk + 31) / 32;
     int64_t ctas = (groups + kBWarps - 1) / kBWarps;
     if (ctas > 148 * 2) ctas = 148 * 2;
-    static bool configured = false;  // idempotent attribute; a benign race sets it twice
-    if (!configured) {
+    static PerDeviceOnce configured;
+    if (configured.first()) {
       if (cudaFuncSetAttribute(hadamard_quantize_blocks_kernel<E4M3>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBSmemBytes) != cudaSuccess ||
           cudaFuncSetAttribute(hadamard_quantize_blocks_kernel<S8>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBSmemBytes) != cudaSuccess)
         return QWX_ERR_LAUNCH;
-      configured = true;
+      configured.mark();
     }
     if (qtype == QWX_E4M3)
       hadamard_quantize_blocks_kernel<E4M3><<<(unsigned)ctas, kBThreads, kBSmemBytes, st>>>(

@@ -852,13 +852,13 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
       const int64_t cap = 148 * 4;
       const unsigned grid = (unsigned)(segments < cap ? segments : cap);
       const size_t ring_bytes = (size_t)kRowDepth * (tc / 8) * 16;
-      static bool configured = false;  // idempotent attribute; a benign race sets it twice
-      if (!configured) {
+      static PerDeviceOnce configured;
+      if (configured.first()) {
         if (cudaFuncSetAttribute(quantize_rows_bf16_s8_kernel,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kRowDepth * kThreads * kRowVec * 16) != cudaSuccess)
           return (int)QWX_ERR_LAUNCH;
-        configured = true;
+        configured.mark();
       }
       quantize_rows_bf16_s8_kernel<<<grid, kThreads, ring_bytes, st>>>(
           (const uint4*)x, segments, (int)(tc / 8), (uint2*)q, (__nv_bfloat16*)scale);
