@@ -293,3 +293,56 @@ def test_pallas_scale_block_specs(case):
   assert list(new.scale.block_shape) == case['scale_block_shape']
   assert list(new.scale.index_map(*case['index'])) == case['scale_index']
   assert qpl.dot_general is bdg.loop_dot_general and qpl.QArray is bq.QArray
+
+
+def test_scales_along_k_layout():
+  """How a scale (or zero point) with tiled contracting axes is laid out for the GEMM kernels:
+  [batch, free, K tiles], with the tile length along the flattened K."""
+  from qwix_b200.core import dot_general as dg
+  from qwix_b200.core.qarray import QArray
+  # one contracting axis, 128-wide tiles
+  x = QArray(qvalue=torch.zeros(6, 512, dtype=torch.int8),
+             scale=torch.arange(6 * 4, dtype=torch.float32).reshape(6, 4), zero_point=None, qtype='int8')
+  t, k_tile = dg._along_k(x.scale, x, [1], [], [0])
+  assert t.shape == (1, 6, 4) and k_tile == 128
+  assert torch.equal(t[0], x.scale)
+  # untiled: one run of K
+  y = QArray(qvalue=torch.zeros(6, 512, dtype=torch.int8), scale=torch.ones(6, 1), zero_point=None, qtype='int8')
+  t, k_tile = dg._along_k(y.scale, y, [1], [], [0])
+  assert t.shape == (1, 6, 1) and k_tile == 512
+  # two contracting axes (4, 256), the last tiled by 128: runs are numbered (first axis, tile)
+  z = QArray(qvalue=torch.zeros(6, 4, 256, dtype=torch.int8),
+             scale=torch.arange(6 * 2, dtype=torch.float32).reshape(6, 1, 2), zero_point=None, qtype='int8')
+  t, k_tile = dg._along_k(z.scale, z, [1, 2], [], [0])
+  assert t.shape == (1, 6, 8) and k_tile == 128
+  assert torch.equal(t[0, 1], torch.tensor([2., 3.] * 4))
+  # the same axes contracted in the other order: the tiled axis is outermost, runs are longer
+  t, k_tile = dg._along_k(z.scale, z, [2, 1], [], [0])
+  assert t.shape == (1, 6, 2) and k_tile == 128 * 4
+  # a weight [K, N] with sub-channel tiles: free axis second, batch absent
+  w = QArray(qvalue=torch.zeros(512, 5, dtype=torch.int8),
+             scale=torch.arange(4 * 5, dtype=torch.float32).reshape(4, 5), zero_point=None, qtype='int8')
+  t, k_tile = dg._along_k(w.scale, w, [0], [], [1])
+  assert t.shape == (1, 5, 4) and k_tile == 128
+  assert torch.equal(t[0], w.scale.t())
+  # refining per-tile values to a finer common tiling
+  assert torch.equal(dg._refine(torch.tensor([[[1., 2.]]]), 256, 128), torch.tensor([[[1., 1., 2., 2.]]]))
+
+
+def test_lazy_activation_protocol_is_host_only_until_consumed():
+  """fused.LazyAct: shape / ndim / which quantization recipes the producing kernel can emit."""
+  from qwix_b200 import fused
+  from qwix_b200.core import qarray as q
+
+  class Fake(fused.LazyAct):
+    def __init__(self):
+      self.shape, self.device = (2, 3, 64), torch.device('cpu')
+  f = Fake()
+  assert f.ndim == 3 and f.dtype == torch.bfloat16
+  assert f._fusable(q.HowToQuantize(qtype='int8', channelwise_axes=[0, 1]))
+  assert not f._fusable(q.HowToQuantize(qtype='int8', channelwise_axes=[0]))            # per-row of axis 0 only
+  assert not f._fusable(q.HowToQuantize(qtype='int4', channelwise_axes=[0, 1]))
+  assert not f._fusable(q.HowToQuantize(qtype='int8', channelwise_axes=[0, 1], tiled_axes={2: 32}))
+  assert not f._fusable(q.HowToQuantize(qtype='int8', channelwise_axes=[0, 1], calibration_method='minmax'))
+  with pytest.raises(RuntimeError):      # CPU tensors never reach a kernel
+    fused.AddRmsNorm(torch.zeros(2, 8, dtype=torch.bfloat16), None, torch.ones(8, dtype=torch.bfloat16), 1e-5)
