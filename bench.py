@@ -238,8 +238,14 @@ def w4_workload(args):
   ws = torch.zeros(L.qwx_gemm_a16w4_workspace_bytes(Mw, Nw), dtype=torch.uint8, device='cuda')
   err = torch.zeros(1, dtype=torch.int32, device='cuda')
 
+  from qwix_b200.core import dot_general as bdg
+  dn = (((1,), (0,)), ((), ()))
+  fused_path = weight_only.eligible(a, sets[0], dn)
+
   def call(i):
     wq = sets[i % len(sets)]
+    if not fused_path:   # more tokens than the fused kernel serves: dequantize + library GEMM
+      return bdg.dot_general(a, wq, dn, preferred_element_type=torch.bfloat16)
     _lib.check(L.qwx_gemm_a16w4(_lib.ptr(a), _lib.ptr(wq._w4_packed), _lib.ptr(wq._w4_scale), _lib.F32,
                                 Mw, Nw, Kw, 128, _lib.ptr(out), _lib.BF16, _lib.ptr(ws), ws.numel(), 1,
                                 _lib.ptr(err), _lib.stream_ptr()), 'gemm_a16w4')
@@ -254,7 +260,8 @@ def w4_workload(args):
                  'scale_tile': 128, 'l2': '3 weight sets (375 MB) cycled'},
       'roofline': {'bound': 'hbm', 'achieved': nbytes / ms / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                    'frac': nbytes / ms / 1e6 / peaks['hbm_gbs'], 'traffic': None,
-                   'kernel': 'gemm_w4_kernel', 'peak_source': peaks['source']}}))
+                   'kernel': 'gemm_w4_kernel' if fused_path else 'dequantize_kernel + library bf16 GEMM',
+                   'peak_source': peaks['source']}}))
 
 
 def hadamard_workload(args):
