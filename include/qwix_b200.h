@@ -155,12 +155,13 @@ int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_layout,
 /* The same product with a caller-provided workspace, for decode-shaped problems (a few rows
  * of activations against a large weight) whose output tiles are fewer than the SMs: K is cut
  * into ranges so that every SM streams a share of the weight, each range writes its partial
- * sums to a slab of the workspace, and the CTA that completes a tile adds the slabs in range
- * order, scales and stores.  Results are bit-identical to qwx_gemm_q8 for int8 codes and
+ * sums to a slab of the workspace, and once all ranges of a tile are there its CTAs (a
+ * cooperative launch: all resident) each add the slabs of a share of the tile's columns in
+ * range order, scale and store.  Results are bit-identical to qwx_gemm_q8 for int8 codes and
  * repeatable for e4m3 codes (float32 partial sums are added in a fixed order).
  * qwx_gemm_q8_workspace_bytes returns 0 when the shape would not be cut (the call then
  * behaves exactly like qwx_gemm_q8 and workspace may be NULL).  The workspace opens with
- * one int32 counter per output tile; these must be zero on entry (workspace_is_zero = 0
+ * two int32 counters per output tile; these must be zero on entry (workspace_is_zero = 0
  * makes the call clear them first) and are left zero on return, so one buffer cleared once
  * serves every call on a stream.  The reference has no counterpart: XLA picks its own split
  * of the contraction (dot_general.py:253-258 hands it one lax.dot_general). */

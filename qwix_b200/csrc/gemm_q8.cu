@@ -61,7 +61,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int splits;          // K is cut in `splits` ranges; 1 = every CTA owns whole tiles
   uint32_t* ws;        // splits > 1: [splits][tiles][BN][BM] partial sums (int32 or float32 bits)
-  int* counters;       // splits > 1: [tiles], zero on entry
+  int* counters;       // splits > 1: [tiles][2], zero on entry
 };
 
 __device__ __forceinline__ float load_scale(const void* p, int dtype, int64_t i) {
@@ -74,6 +74,26 @@ __device__ __forceinline__ float round_out(float v, int out_dtype) {
   if (out_dtype == QWX_BF16) return round_to<BF16>(v);
   if (out_dtype == QWX_F16) return round_to<F16>(v);
   return v;
+}
+
+// Polls a global counter (written with atomics by other CTAs of this cooperative launch) until
+// it reaches `target`; bounded like every other wait of this file.
+__device__ __forceinline__ bool wait_count(const int* ctr, int target, volatile int* abort) {
+  const long long t0 = clock64();
+#pragma unroll 1
+  for (uint32_t it = 1;; ++it) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= target) return true;
+    __nanosleep(64);
+    if ((it & 63u) == 0) {
+      if (*abort) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *abort = 1;
+        return false;
+      }
+    }
+  }
 }
 
 template <MmaKind KIND, int BLAYOUT>
@@ -216,7 +236,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     uint32_t acc_phase = 0;
     bool ok = true;
     const bool reference = p.epilogue == QWX_EPI_REFERENCE;
-    uint32_t epi_phase = 0;
+    uint32_t epi_phase = 0, fin_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int t = tile / p.splits;
       const int m0 = (t % p.tiles_m) * BM;
@@ -295,6 +315,61 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
       };
 
+      // The same for 8 consecutive columns (the split-K finish).
+      auto emit8 = [&](const uint32_t (&r)[8], int64_t m, float sa, int64_t ncol, const float* sbv) {
+        const bool full = ncol + 8 <= p.N;
+        if (p.out_dtype == QWX_S32) {
+          int32_t* o = reinterpret_cast<int32_t*>(p.out) + m * p.N + ncol;
+          if (full && (p.N & 3) == 0) {
+            *reinterpret_cast<uint4*>(o) = make_uint4(r[0], r[1], r[2], r[3]);
+            *reinterpret_cast<uint4*>(o + 4) = make_uint4(r[4], r[5], r[6], r[7]);
+          } else {
+            for (int j = 0; j < 8 && ncol + j < p.N; ++j) o[j] = (int32_t)r[j];
+          }
+          return;
+        }
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float a = KIND == MmaKind::kI8 ? (float)(int32_t)r[j] : __uint_as_float(r[j]);
+          if (reference) {
+            a = round_out(a, p.out_dtype);
+            a = round_out(__fmul_rn(a, sa), p.out_dtype);
+            a = round_out(__fmul_rn(a, sbv[j]), p.out_dtype);
+          } else {
+            a = __fmul_rn(__fmul_rn(a, sa), sbv[j]);
+          }
+          v[j] = a;
+        }
+        if (p.out_dtype == QWX_F32) {
+          float* o = reinterpret_cast<float*>(p.out) + m * p.N + ncol;
+          if (full && (p.N & 3) == 0) {
+            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          } else {
+            for (int j = 0; j < 8 && ncol + j < p.N; ++j) o[j] = v[j];
+          }
+        } else {
+          uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + m * p.N + ncol;
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (p.out_dtype == QWX_BF16) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+              __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+          }
+          if (full && (p.N & 7) == 0) {
+            *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+          } else {
+            for (int j = 0; j < 8 && ncol + j < p.N; ++j) o[j] = (uint16_t)(w[j >> 1] >> ((j & 1) * 16));
+          }
+        }
+      };
+
       // Split-K: this item's partial sums go to a private slab, laid out as the accumulator
       // comes out of tensor memory ([column][tile row]) so that every store is coalesced.
       uint32_t* slab = nullptr;
@@ -320,56 +395,71 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
 
       if (p.splits > 1) {
-        // Count this K range for the tile.  The CTA that completes the tile adds the ranges'
-        // slabs in range order (so float sums do not depend on timing) and runs the ordinary
-        // epilogue; (row group, column chunk) pairs are dealt round-robin to the four warps.
+        // Publish this K range, wait until every range of the tile has been published (the
+        // launch is cooperative: all CTAs are resident), then finish a share of the tile:
+        // CTA `split` takes the 32-column chunks c = split, split + splits, ...; warp q the
+        // eight columns q * 8 .. q * 8 + 7 of each, every lane one row, adding the ranges'
+        // slabs in range order (so float sums do not depend on timing).
+        const int split = tile % p.splits;
+        int* arrived = p.counters + 2 * t;
         __threadfence();
         mbar_arrive(smem_u32(&ctl->epi_done));
         if (q == 0 && lane == 0) {
-          bool done = mbar_wait(smem_u32(&ctl->epi_done), epi_phase, abort);
-          if (done) {
-            const int old = atomicAdd(p.counters + t, 1);
-            __threadfence();
-            ctl->finalize = (old + 1 == p.splits) ? 1 : 0;
-            if (ctl->finalize) p.counters[t] = 0;
-          }
+          if (mbar_wait(smem_u32(&ctl->epi_done), epi_phase, abort)) atomicAdd(arrived, 1);
           mbar_arrive(smem_u32(&ctl->fin_done));
         }
-        if (lane == 0) ok = mbar_wait(smem_u32(&ctl->fin_done), epi_phase, abort);
+        if (lane == 0) {
+          ok = mbar_wait(smem_u32(&ctl->fin_done), fin_phase, abort);
+          if (ok) ok = wait_count(arrived, p.splits, abort);
+        }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         epi_phase ^= 1u;
+        fin_phase ^= 1u;
         if (!ok) break;
-        if (ctl->finalize) {
-          const int64_t rows_left = p.M - m0;
-          const int groups = (int)(rows_left >= BM ? BM / 32 : (rows_left + 31) / 32);
-          const size_t split_stride = (size_t)(p.tiles_m * p.tiles_n) * (size_t)(BM * BN);
-          const uint32_t* base = p.ws + (size_t)t * (size_t)(BM * BN);
+        __threadfence();
+
+        const int64_t rows_left = p.M - m0;
+        const int groups = (int)(rows_left >= BM ? BM / 32 : (rows_left + 31) / 32);
+        const size_t split_stride = (size_t)(p.tiles_m * p.tiles_n) * (size_t)(BM * BN);
+        const uint32_t* base = p.ws + (size_t)t * (size_t)(BM * BN);
 #pragma unroll 1
-          for (int u = q; u < groups * (BN / 32); u += 4) {
-            const int g = u % groups, c = u / groups;
-            const int64_t ncol = (int64_t)n0 + c * 32;
+        for (int c = split; c < BN / 32; c += p.splits) {
+          const int64_t ncol = (int64_t)n0 + c * 32 + q * 8;
+          if (ncol >= p.N) break;
+#pragma unroll 1
+          for (int g = 0; g < groups; ++g) {
             const int64_t mr = (int64_t)m0 + g * 32 + lane;
-            if (ncol >= p.N || mr >= p.M) continue;
-            const uint32_t* w = base + (size_t)(c * 32) * BM + g * 32 + lane;
-            uint32_t r[32];
+            if (mr >= p.M) continue;
+            const uint32_t* w = base + (size_t)(c * 32 + q * 8) * BM + g * 32 + lane;
+            uint32_t r[8];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __ldcg(w + j * BM);
+            for (int j = 0; j < 8; ++j) r[j] = __ldcg(w + j * BM);
+#pragma unroll 4
             for (int sp = 1; sp < p.splits; ++sp) {
               w += split_stride;
-              uint32_t v[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __ldcg(w + j * BM);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (KIND == MmaKind::kI8) r[j] += v[j];
-                else r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(v[j])));
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t v = __ldcg(w + j * BM);
+                if (KIND == MmaKind::kI8) r[j] += v;
+                else r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(v)));
               }
             }
             const float sar = p.sa ? load_scale(p.sa, p.scale_dtype, mr) : 1.0f;
-            emit32(r, mr, sar, ncol, &ctl->sb[q][acc][c * 32]);
+            emit8(r, mr, sar, ncol, &ctl->sb[q][acc][c * 32 + q * 8]);
           }
         }
+        // The CTA that leaves the tile last clears its two counters for the next launch.
         __syncwarp();
+        mbar_arrive(smem_u32(&ctl->epi_done));
+        if (q == 0 && lane == 0) {
+          if (mbar_wait(smem_u32(&ctl->epi_done), epi_phase, abort)) {
+            if (atomicAdd(arrived + 1, 1) + 1 == p.splits) {
+              arrived[0] = 0;
+              arrived[1] = 0;
+            }
+          }
+        }
+        epi_phase ^= 1u;
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
@@ -394,6 +484,25 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
         cudaSuccess)
       return QWX_ERR_LAUNCH;
     configured.mark();
+  }
+  if (p.splits > 1) {
+    // the CTAs of a tile wait for one another: a cooperative launch guarantees that all of
+    // them are resident (the grid is at most one CTA per SM)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, p) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return QWX_ERR_LAUNCH;
+    }
+    return QWX_OK;
   }
   kern<<<grid, kGemmThreads, kSmemBytes, st>>>(ta, tb, p);
   QWX_CHECK_LAUNCH();
@@ -424,9 +533,9 @@ using namespace qwx;
 
 // Split-K is worth it when the tiles cannot occupy the SMs: cut K so that tiles x splits comes
 // close to the SM count, keeping at least four 128-wide K blocks per range.
-// The workspace opens with one int32 counter per tile (rounded up to 256 bytes), zero between
-// calls; the partial-sum slabs follow and need no initialisation.
-static size_t counter_bytes(int64_t tiles) { return ((size_t)tiles * 4 + 255) & ~(size_t)255; }
+// The workspace opens with two int32 counters per tile (ranges published, CTAs finished; rounded
+// up to 256 bytes), zero between calls; the partial-sum slabs follow and need no initialisation.
+static size_t counter_bytes(int64_t tiles) { return ((size_t)tiles * 8 + 255) & ~(size_t)255; }
 
 static int choose_splits(int64_t tiles, int kblocks, int sms) {
   if (tiles * 2 > sms) return 1;
