@@ -367,6 +367,8 @@ def decoder_workload(args):
     e[1].record()
     sync()
     runs.append(max_over_ranks(e[0].elapsed_time(e[1]), dist, device))
+  from qwix_b200 import _lib
+  _lib.raise_on_device_error()   # no bounded wait inside a kernel ran out
   ms = min(runs)
   total_tokens = args.batch * (args.prompt + args.decode)
   if rank == 0:

@@ -227,7 +227,7 @@ int qwx_code_sums(const void* codes, int64_t rows, int64_t cols, int k_axis, int
  * qwx_silu_mul_quantize: gu is [rows, 2 f] = [gate | up]; y = bf16(bf16(silu(gate)) * up).
  * qwx_rope_cache: qkv [B, T, (hq + 2 hkv) * hd]; heads are rotated with the float32 tables
  *   cos/sin [positions, hd / 2] at position pos + t (pos_dev, a device int64, replaces pos
- *   when not NULL: the form a CUDA graph can replay); q goes to q_out [B, hq, T, hd], k and v
+ *   when not NULL: the form a CUDA graph can replay); q goes to q_out [B, T, hq, hd], k and v
  *   to cache_k / cache_v [B, hkv, S, hd] views with the given batch and head strides
  *   (elements) at sequence index pos + t. */
 int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weight, double eps,

@@ -110,6 +110,33 @@ def stream_ptr(device=None):
   return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+_error_flags: dict = {}
+
+
+def error_flag(device) -> torch.Tensor:
+  """The device int32 that kernels with bounded waits write when a wait runs out, one per
+  device for the life of the process (allocating and clearing one per call would be a kernel
+  launch per GEMM).  It is never cleared: `raise_on_device_error` reports a failure once it
+  happened."""
+  device = torch.device(device)
+  key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+  flag = _error_flags.get(key)
+  if flag is None:
+    flag = _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+  return flag
+
+
+def raise_on_device_error(device=None):
+  """Synchronises and raises if any kernel of this process reported a wait that ran out."""
+  for key, flag in list(_error_flags.items()):
+    if device is not None and torch.device(device).index not in (None, key[1]):
+      continue
+    code = int(flag.item())
+    if code:
+      raise RuntimeError(f'a device-side wait ran out on cuda:{key[1]} (status {code}: '
+                         f'{lib().qwx_status_string(code).decode()})')
+
+
 def require_cuda(*tensors):
   for t in tensors:
     if t is not None and not t.is_cuda:

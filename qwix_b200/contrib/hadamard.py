@@ -102,7 +102,7 @@ def hadamard_quantize_multiply(x: torch.Tensor, wq: QArray, signs_in=None, signs
   L = _lib.lib()
   ws = torch.empty(L.qwx_hadamard_gemm_workspace_bytes(m, k), dtype=torch.uint8, device=x.device)
   out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-  err = torch.zeros(1, dtype=torch.int32, device=x.device)
+  err = _lib.error_flag(x.device)
   oc = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}[out_dtype]
   _lib.check(L.qwx_hadamard_gemm(
       _lib.ptr(x), m, k, _lib.ptr(si), _lib.ptr(so), _lib.ptr(wq.qvalue.contiguous()),

@@ -206,7 +206,7 @@ def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
   raw = ls is None and rs is None and code == _lib.S8
   out_t = torch.int32 if raw else res_t
   out = torch.empty((B, M, N), dtype=out_t, device=lq.device)
-  err = torch.zeros(1, dtype=torch.int32, device=lq.device)
+  err = _lib.error_flag(lq.device)
   epi = _lib.EPI_REFERENCE if EPILOGUE == 'reference' else _lib.EPI_F32
   L = _lib.lib()
   stream = _lib.stream_ptr(lq.device)

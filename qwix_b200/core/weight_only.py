@@ -83,7 +83,7 @@ def matmul(lhs: torch.Tensor, rhs: QArray, out_dtype: torch.dtype) -> torch.Tens
   x = lhs.reshape(-1, K).contiguous()
   rows = x.shape[0]
   out = torch.empty((rows, N), dtype=out_dtype, device=x.device)
-  err = torch.zeros(1, dtype=torch.int32, device=x.device)
+  err = _lib.error_flag(x.device)
   L = _lib.lib()
   tile = K // rhs.scale.shape[0]
   oc = _lib.BF16 if out_dtype == torch.bfloat16 else _lib.F32

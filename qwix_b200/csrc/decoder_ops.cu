@@ -9,7 +9,7 @@
 //   silu_mul         y = bf16( bf16(silu(g)) * u ),  silu(g) = g / (1 + exp(-g)) in float32
 //                    (fast exp and division: differs from libm in about 1 value in 10^4)
 //   rope_cache       q, k rotated (x1 cos - x2 sin | x2 cos + x1 sin, float32, separate
-//                    roundings), q written head-major, k and v written into the KV cache
+//                    roundings), q written token-major, k and v written into the KV cache
 //
 // each followed, when asked, by scale = bf16(absmax(y) / 127.5) (1 if below 2^-63),
 // code = sat_int8(round_half_even(bf16(y / scale))) per row -- the strict recipe of
@@ -229,7 +229,7 @@ silu_mul_kernel(const uint4* __restrict__ gu, int64_t rows, int fvec, uint4* __r
 }
 
 // One thread per (batch, token, head, 8 of the head's first-half values): rotates q and k
-// heads, copies v heads.  qkv: [B, T, (hq + 2 hkv) * hd]; q_out: [B, hq, T, hd];
+// heads, copies v heads.  qkv: [B, T, (hq + 2 hkv) * hd]; q_out: [B, T, hq, hd];
 // cache_k / cache_v: [B, hkv, S, hd] views given by their batch and head strides (elements).
 __global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t B, int64_t T,
                                   int hq, int hkv, int hd, const float* __restrict__ cos_t,
@@ -253,7 +253,7 @@ __global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t
     const uint4 u1 = *reinterpret_cast<const uint4*>(src);
     const uint4 u2 = *reinterpret_cast<const uint4*>(src + half);
     __nv_bfloat16* dst;
-    if (h < hq) dst = q_out + ((b * hq + h) * T + t) * hd + c * 8;
+    if (h < hq) dst = q_out + ((b * T + t) * hq + h) * hd + c * 8;
     else if (h < hq + hkv) dst = cache_k + b * cache_bs + (h - hq) * cache_hs + (p0 + t) * hd + c * 8;
     else dst = cache_v + b * cache_bs + (h - hq - hkv) * cache_hs + (p0 + t) * hd + c * 8;
     if (h >= hq + hkv) {

@@ -649,12 +649,22 @@ dequantize_kernel(const void* __restrict__ q, View vw, const void* __restrict__ 
       for (int j = 0; j < 8; ++j)
         code[j] = (O == Out::kE4M3) ? e4m3_to_float(b[j]) : (float)(int8_t)b[j];
     }
+    // scale group of each of the eight columns: one division, then a running remainder
+    int64_t g = gbase + col / vw.tc;
+    int64_t left = vw.tc - (col - (col / vw.tc) * vw.tc);   // columns left in this group
+    float sc = load1<S>(scale, g);
+    float zp = has_zp ? (float)zero_point[g] : 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int64_t g = gbase + min(col + j, vw.C - 1) / vw.tc;
       float cv = round_to<S>(code[j]);
-      if (has_zp) cv = round_to<S>(__fsub_rn(cv, (float)zero_point[g]));
-      v[j] = round_to<S>(__fmul_rn(cv, load1<S>(scale, g)));
+      if (has_zp) cv = round_to<S>(__fsub_rn(cv, zp));
+      v[j] = round_to<S>(__fmul_rn(cv, sc));
+      if (--left == 0 && col + j + 1 < vw.C) {
+        ++g;
+        left = vw.tc;
+        sc = load1<S>(scale, g);
+        if (has_zp) zp = (float)zero_point[g];
+      }
     }
     if (vec_ok) store8<S>(out, off, v);
     else for (int j = 0; j < nvalid; ++j) store1<S>(out, off + j, v[j]);

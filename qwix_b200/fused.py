@@ -105,19 +105,21 @@ def rope_cache(qkv: torch.Tensor, hq: int, hkv: int, hd: int, cos: torch.Tensor,
                sin: torch.Tensor, pos, cache_k: torch.Tensor, cache_v: torch.Tensor) -> torch.Tensor:
   """Rotates the q and k heads of qkv [B, T, (hq + 2 hkv) * hd] with the float32 tables
   cos/sin [positions, hd / 2], writes k and v into the cache views [B, hkv, S, hd] at
-  positions pos .. pos + T - 1 and returns q as [B, hq, T, hd].  `pos` is an int or a
-  one-element int64 device tensor."""
+  positions pos .. pos + T - 1 and returns q as a [B, hq, T, hd] view of token-major storage
+  [B, T, hq, hd] (so that an attention kernel that keeps the query's layout hands back
+  [B, T, hq * hd] without a transposing copy).  `pos` is an int or a one-element int64 device
+  tensor."""
   _lib.require_cuda(qkv, cos, sin, cache_k, cache_v)
   B, T, _ = qkv.shape
   if (cache_k.stride(3) != 1 or cache_k.stride(2) != hd or cache_v.stride() != cache_k.stride()
       or cos.dtype != torch.float32 or not cos.is_contiguous() or not sin.is_contiguous()):
     raise ValueError('rope_cache: unexpected cache or table layout.')
   qkv = qkv.contiguous()
-  q = torch.empty((B, hq, T, hd), dtype=qkv.dtype, device=qkv.device)
+  q = torch.empty((B, T, hq, hd), dtype=qkv.dtype, device=qkv.device)
   pos_dev = pos if isinstance(pos, torch.Tensor) else None
   _lib.check(_lib.lib().qwx_rope_cache(
       _lib.ptr(qkv), B, T, hq, hkv, hd, _lib.ptr(cos), _lib.ptr(sin),
       0 if pos_dev is not None else int(pos), _lib.ptr(pos_dev), _lib.ptr(q), _lib.ptr(cache_k),
       _lib.ptr(cache_v), cache_k.stride(0), cache_k.stride(1), _lib.stream_ptr(qkv.device)),
       'rope_cache')
-  return q
+  return q.transpose(1, 2)
