@@ -319,10 +319,11 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
 // absmax is not finite (inf / NaN inputs) or whose scale leaves the fast range take the general
 // per-element recipe.
 
-constexpr int kRowVec = 4;  // 16-byte vectors per thread: rows up to 256 * 4 * 8 = 8192 elements
+// kRowVec: 16-byte vectors per thread; rows up to 256 * kRowVec * 8 elements (4: 8192, 8: 16384)
 constexpr int kRowDepth = 4;  // rows per CTA in the shared-memory ring: one in use, three in flight
 
-__global__ void __launch_bounds__(kThreads, 3)
+template <int kRowVec>
+__global__ void __launch_bounds__(kThreads, kRowVec == 4 ? 3 : 2)
 quantize_rows_bf16_s8_kernel(const uint4* __restrict__ x, int64_t segments, int nvec,
                              uint2* __restrict__ q, __nv_bfloat16* __restrict__ scale) {
   extern __shared__ uint4 ring[];   // [kRowDepth][nvec]; thread t only touches vectors t + 256 i
@@ -858,20 +859,28 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
   if (tp == 1 && tr == 1 && tc % 8 == 0 && aligned16(x) && aligned16(q)) {
     const int64_t segments = P * R * (C / tc);
     if (x_dtype == QWX_BF16 && qtype == QWX_S8 && method == QWX_ABSMAX && !has_arg &&
-        rounding == QWX_STRICT && tc > 32 * 8 * kCache && tc <= kThreads * kRowVec * 8) {
-      const int64_t cap = 148 * 4;
+        rounding == QWX_STRICT && tc > 32 * 8 * kCache && tc <= kThreads * 8 * 8) {
+      const bool wide = tc > kThreads * 4 * 8;   // rows of 8193..16384 values: 8 vectors per thread
+      const int64_t cap = 148 * (wide ? 2 : 4);
       const unsigned grid = (unsigned)(segments < cap ? segments : cap);
       const size_t ring_bytes = (size_t)kRowDepth * (tc / 8) * 16;
       static PerDeviceOnce configured;
       if (configured.first()) {
-        if (cudaFuncSetAttribute(quantize_rows_bf16_s8_kernel,
+        if (cudaFuncSetAttribute(quantize_rows_bf16_s8_kernel<4>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kRowDepth * kThreads * kRowVec * 16) != cudaSuccess)
+                                 kRowDepth * kThreads * 4 * 16) != cudaSuccess ||
+            cudaFuncSetAttribute(quantize_rows_bf16_s8_kernel<8>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kRowDepth * kThreads * 8 * 16) != cudaSuccess)
           return (int)QWX_ERR_LAUNCH;
         configured.mark();
       }
-      quantize_rows_bf16_s8_kernel<<<grid, kThreads, ring_bytes, st>>>(
-          (const uint4*)x, segments, (int)(tc / 8), (uint2*)q, (__nv_bfloat16*)scale);
+      if (wide)
+        quantize_rows_bf16_s8_kernel<8><<<grid, kThreads, ring_bytes, st>>>(
+            (const uint4*)x, segments, (int)(tc / 8), (uint2*)q, (__nv_bfloat16*)scale);
+      else
+        quantize_rows_bf16_s8_kernel<4><<<grid, kThreads, ring_bytes, st>>>(
+            (const uint4*)x, segments, (int)(tc / 8), (uint2*)q, (__nv_bfloat16*)scale);
       QWX_CHECK_LAUNCH();
       return (int)QWX_OK;
     }

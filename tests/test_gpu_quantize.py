@@ -28,6 +28,9 @@ CASES = [
     ((64, 1024), (0,), {}, 'per-token rows (warp per row)'),
     ((16, 8192), (0,), {}, 'per-token rows (CTA per row)'),
     ((8, 16384), (0,), {}, 'rows longer than the register cache'),
+    ((700, 14336), (0,), {}, 'rows of 14336: several rows per persistent CTA'),
+    ((9, 8200), (0,), {}, 'rows just past 8192'),
+    ((3, 16392), (0,), {}, 'rows just past 16384: general kernel'),
     ((256, 512), (1,), {}, 'per-output-channel columns'),
     ((512, 384), (1,), {0: 128}, 'sub-channel tiles along K'),
     ((32, 1024), (0,), {1: 128}, 'sub-channel tiles along the row'),
@@ -59,7 +62,7 @@ def test_quantize_absmax_matches_oracle(case, qtype, dtype):
 
 @pytest.mark.parametrize('dtype', ['float32', 'bfloat16'])
 @pytest.mark.parametrize('method', ['minmax', 'minmax,0.9', 'absmax,0.8'])
-@pytest.mark.parametrize('case', CASES[:8], ids=[c[3] for c in CASES[:8]])
+@pytest.mark.parametrize('case', CASES[:3] + CASES[6:11], ids=[c[3] for c in CASES[:3] + CASES[6:11]])
 def test_quantize_other_calibrations(case, method, dtype):
   shape, cw, tiled, _ = case
   x = _data(shape, dtype, seed=7)
