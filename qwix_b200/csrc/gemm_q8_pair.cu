@@ -68,21 +68,12 @@ struct PairParams {
   int epilogue;
   int32_t* error_flag;
   int tiles_m, tiles_n;    // 256 x 256 tiles
-  int stream_out;          // output larger than L2 can keep: evict-first stores
 };
 
 __device__ __forceinline__ float load_scale_p(const void* p, int dtype, int64_t i) {
   if (dtype == QWX_F32) return reinterpret_cast<const float*>(p)[i];
   if (dtype == QWX_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
   return __half2float(reinterpret_cast<const __half*>(p)[i]);
-}
-
-// 16-byte output store.  A result too large to stay in L2 is written evict-first, so that its
-// write-back to HBM happens while this tensor-bound kernel runs instead of being left to
-// whatever kernel comes next.
-__device__ __forceinline__ void store16(void* ptr, uint4 v, bool streaming) {
-  if (streaming) __stcs(reinterpret_cast<uint4*>(ptr), v);
-  else *reinterpret_cast<uint4*>(ptr) = v;
 }
 
 __device__ __forceinline__ float round_out_p(float v, int out_dtype) {
@@ -261,7 +252,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
           if (ncol + 32 <= p.N && (p.N & 3) == 0) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
-              store16(o + j, make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]), p.stream_out);
+              *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
           } else {
             for (int j = 0; j < 32 && ncol + j < p.N; ++j) o[j] = (int32_t)r[j];
           }
@@ -285,7 +276,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
           if (ncol + 32 <= p.N && (p.N & 3) == 0) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
-              store16(o + j, make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3])), p.stream_out);
+              *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
           } else {
             for (int j = 0; j < 32 && ncol + j < p.N; ++j) o[j] = v[j];
           }
@@ -305,7 +296,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
           if (ncol + 32 <= p.N && (p.N & 7) == 0) {
 #pragma unroll
             for (int j = 0; j < 16; j += 4)
-              store16(o + 2 * j, make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]), p.stream_out);
+              *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
           } else {
             for (int j = 0; j < 32 && ncol + j < p.N; ++j)
               o[j] = (uint16_t)(w[j >> 1] >> ((j & 1) * 16));
@@ -369,7 +360,6 @@ int gemm_q8_pair_launch(const void* a, const void* b, int code_dtype, int b_layo
   p.error_flag = error_flag;
   p.tiles_m = (int)((M + 2 * PM - 1) / (2 * PM));
   p.tiles_n = (int)((N + PN - 1) / PN);
-  p.stream_out = M * N * (out_dtype == QWX_BF16 || out_dtype == QWX_F16 ? 2 : 4) > (int64_t)48 << 20;
   const int64_t num_tiles = (int64_t)p.tiles_m * p.tiles_n;
   if (num_tiles > INT32_MAX / 2) return QWX_ERR_SHAPE;
   const int64_t pairs = num_tiles < sms / 2 ? num_tiles : sms / 2;
