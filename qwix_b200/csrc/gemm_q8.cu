@@ -535,7 +535,13 @@ using namespace qwx;
 // close to the SM count, keeping at least four 128-wide K blocks per range.
 // The workspace opens with two int32 counters per tile (ranges published, CTAs finished; rounded
 // up to 256 bytes), zero between calls; the partial-sum slabs follow and need no initialisation.
-static size_t counter_bytes(int64_t tiles) { return ((size_t)tiles * 8 + 255) & ~(size_t)255; }
+// The region has one size for every shape: callers reuse one workspace for calls with different
+// tile counts, and the slabs of one call must never lie where another call keeps its counters
+// (K is only cut when the tiles fill at most half of the SMs, so 1 KB holds all counters).
+static size_t counter_bytes(int64_t tiles) {
+  const size_t need = (size_t)tiles * 8;
+  return need <= 1024 ? 1024 : ((need + 255) & ~(size_t)255);
+}
 
 static int choose_splits(int64_t tiles, int kblocks, int sms) {
   if (tiles * 2 > sms) return 1;

@@ -83,6 +83,23 @@ def test_split_k_int8_bit_exact_and_workspace_reusable(mnk, layout):
   assert int(ws[:tiles * 8].count_nonzero().item()) == 0   # tile counters are left zero
 
 
+def test_split_k_workspace_shared_between_shapes():
+  """One zeroed buffer serves calls with different tile counts: the counters of one call never
+  lie where another call left partial sums."""
+  L = _lib.lib()
+  shapes = [(32, 3072, 4096), (32, 14336, 4096), (32, 4096, 2048), (32, 14336, 4096), (32, 3072, 4096)]
+  need = max(L.qwx_gemm_q8_workspace_bytes(*s) for s in shapes)
+  ws = torch.zeros(need, dtype=torch.uint8, device='cuda')
+  for i, (M, N, K) in enumerate(shapes):
+    rng = np.random.default_rng(i)
+    a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    b = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    want = a.astype(np.int32) @ b.astype(np.int32).T
+    got, _, n = _splitk_gemm(h.to_torch(a), h.to_torch(b), _lib.B_NK, ws=ws)
+    assert n > 0
+    assert np.array_equal(got.cpu().numpy(), want), f'call {i} {M}x{N}x{K}'
+
+
 def test_split_k_fp8():
   M, N, K = 16, 1024, 4096
   rng = np.random.default_rng(5)
@@ -104,7 +121,7 @@ def test_split_k_workspace_query_and_errors():
   assert L.qwx_gemm_q8_workspace_bytes(4096, 8192, 8192) == 0      # enough tiles already
   assert L.qwx_gemm_q8_workspace_bytes(32, 4096, 256) == 0         # K too short to cut
   need = L.qwx_gemm_q8_workspace_bytes(32, 4096, 4096)
-  assert need == 256 + 8 * 16 * 128 * 256 * 4, need   # 16 tiles, K cut in 8
+  assert need == 1024 + 8 * 16 * 128 * 256 * 4, need   # counters + 16 tiles x 8 ranges of slabs
   a = torch.zeros((32, 4096), dtype=torch.int8, device='cuda')
   b = torch.zeros((4096, 4096), dtype=torch.int8, device='cuda')
   out = torch.empty((32, 4096), dtype=torch.int32, device='cuda')
