@@ -233,6 +233,23 @@ int qwx_code_sums(const void* codes, int64_t rows, int64_t cols, int k_axis, int
 int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weight, double eps,
                              int64_t rows, int64_t d, void* x_out, void* y_out, void* q,
                              void* scale, qwx_stream_t stream);
+/* qwx_add_rmsnorm_quantize with the all-reduce of a row-parallel projection folded in: delta
+ * is the sum over `world` ranks of bf16 partial outputs that every rank keeps in a buffer the
+ * other ranks have mapped (partials[r], flags[r]: rank r's buffers as mapped in this process,
+ * e.g. through CUDA IPC / symmetric memory over NVLink).  The kernel reads the partials with
+ * peer loads, adds them in rank order in float32 and rounds once to bf16 (what an all-reduce
+ * delivers), then proceeds as above.  flags[r]: int32 [max_ctas][world], zero before the first
+ * call on every rank; launches: this rank's int32 [max_ctas], zero before the first call.
+ * Every rank must make the same sequence of calls with the same rows, and a partial buffer
+ * may be rewritten only after one further call of this function (callers alternate two
+ * buffers).  The hand-shake between ranks is bounded; if a peer never arrives the call
+ * reports QWX_ERR_DEVICE_WAIT through error_flag and writes nothing.  No counterpart in the
+ * reference (GSPMD inserts the all-reduce there, flax_util.py:354-357). */
+int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, void* const* flags,
+                                  int world, int rank, int* launches, int max_ctas,
+                                  const void* weight, double eps, int64_t rows, int64_t d,
+                                  void* x_out, void* y_out, void* q, void* scale,
+                                  int32_t* error_flag, qwx_stream_t stream);
 int qwx_silu_mul_quantize(const void* gu, int64_t rows, int64_t f, void* y_out, void* q,
                           void* scale, qwx_stream_t stream);
 int qwx_rope_cache(const void* qkv, int64_t B, int64_t T, int hq, int hkv, int hd,

@@ -59,6 +59,8 @@ _SIGNATURES = {
                                  _int, _vp, _vp, _vp, _int, _int, _vp, _vp]),
     'qwx_code_sums': (_int, [_vp, _i64, _i64, _int, _i64, _int, _vp, _vp]),
     'qwx_add_rmsnorm_quantize': (_int, [_vp, _vp, _vp, _dbl, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    'qwx_add_rmsnorm_quantize_peer': (_int, [_vp, _vp, _vp, _int, _int, _vp, _int, _vp, _dbl, _i64, _i64,
+                                             _vp, _vp, _vp, _vp, _vp, _vp]),
     'qwx_silu_mul_quantize': (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     'qwx_rope_cache': (_int, [_vp, _i64, _i64, _int, _int, _int, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                               _i64, _i64, _vp]),

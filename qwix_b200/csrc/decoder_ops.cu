@@ -183,6 +183,130 @@ add_rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ delta,
   }
 }
 
+// ---- the same stage fused with the all-reduce of a row-parallel projection ---------------------
+//
+// Under tensor parallelism the `delta` of add_rmsnorm is the sum over ranks of the partial
+// outputs of a row-parallel GEMM.  Every rank leaves its partial (bf16) in a buffer that the
+// other ranks have mapped (symmetric memory over NVLink); this kernel reads all of them with
+// plain peer loads, adds them in rank order in float32, rounds the sum to bf16 (the value an
+// all-reduce would have delivered) and goes on as add_rmsnorm does: no separate collective, no
+// reduced tensor written and read back.
+//
+// Hand-shake, per CTA and bounded: CTA b of every rank raises flag [b][rank] in every peer's
+// flag array to its own launch count (release, system scope) and waits until the flags of its
+// peers reach that count.  A rank's CTA b runs only after that rank's GEMM has finished (stream
+// order), so a raised flag means "my partial is complete".  Callers alternate two partial
+// buffers: a buffer is rewritten only after a later hand-shake that every reader has passed.
+constexpr int kMaxPeers = 8;
+constexpr long long kPeerWaitCycles = 4000000000ll;
+
+struct PeerArgs {
+  const uint4* partial[kMaxPeers];   // every rank's partial buffer, as mapped here
+  int* flags[kMaxPeers];             // every rank's flag array [ctas][world]
+  int* launches;                     // this rank: [ctas] launch counts
+  int world, rank;
+  int32_t* error_flag;
+};
+
+__global__ void __launch_bounds__(kDThreads)
+add_rmsnorm_peer_kernel(const uint4* __restrict__ x, const PeerArgs pa,
+                        const uint4* __restrict__ weight, float eps, int64_t rows, int nvec,
+                        uint4* __restrict__ x_out, uint4* __restrict__ y_out, uint2* __restrict__ q,
+                        __nv_bfloat16* __restrict__ scale) {
+  __shared__ float red_f[kDThreads / 32];
+  __shared__ uint32_t red_u[kDThreads / 32];
+  __shared__ int s_count, s_ok;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    s_count = ++pa.launches[blockIdx.x];
+    s_ok = 1;
+  }
+  __syncthreads();
+  const int count = s_count;
+  if (tid < pa.world && tid != pa.rank) {
+    __threadfence_system();
+    int* theirs = pa.flags[tid] + (size_t)blockIdx.x * pa.world + pa.rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(count) : "memory");
+    const int* mine = pa.flags[pa.rank] + (size_t)blockIdx.x * pa.world + tid;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (v >= count) break;
+      if ((it & 255u) == 0 && clock64() - t0 > kPeerWaitCycles) {
+        s_ok = 0;
+        if (pa.error_flag) atomicExch(pa.error_flag, QWX_ERR_DEVICE_WAIT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;   // a peer never arrived: reported, nothing is read
+
+  const float inv_d = 1.0f / (float)(nvec * 8);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    uint4 cur[kDVec];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < kDVec; ++it) {
+      const int vi = tid + it * kDThreads;
+      if (vi >= nvec) continue;
+      // sum of the ranks' partials in rank order, float32, rounded once to bf16
+      float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < pa.world; ++r) {
+        float b[8];
+        unpack_bf16x8(__ldcg(pa.partial[r] + row * nvec + vi), b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d[j] = __fadd_rn(d[j], b[j]);
+      }
+      float a[8];
+      unpack_bf16x8(x[row * nvec + vi], a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) d[j] = round_to<BF16>(d[j]);
+      const uint4 u = make_uint4(pack_bf16(a[0] + d[0], a[1] + d[1]), pack_bf16(a[2] + d[2], a[3] + d[3]),
+                                 pack_bf16(a[4] + d[4], a[5] + d[5]), pack_bf16(a[6] + d[6], a[7] + d[7]));
+      x_out[row * nvec + vi] = u;
+      cur[it] = u;
+      float v[8];
+      unpack_bf16x8(u, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = __fmaf_rn(v[j], v[j], ss);
+    }
+    ss = block_sum(ss, red_f, tid);
+    const float rs = rsqrtf(__fadd_rn(__fmul_rn(ss, inv_d), eps));
+
+    uint32_t bits = 0;
+#pragma unroll
+    for (int it = 0; it < kDVec; ++it) {
+      const int vi = tid + it * kDThreads;
+      if (vi >= nvec) continue;
+      float v[8], w[8];
+      unpack_bf16x8(cur[it], v);
+      unpack_bf16x8(__ldg(weight + vi), w);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[j] = pack_bf16(__fmul_rn(__fmul_rn(v[2 * j], rs), w[2 * j]),
+                         __fmul_rn(__fmul_rn(v[2 * j + 1], rs), w[2 * j + 1]));
+        bits = max(bits, abs_bits2(o[j]));
+      }
+      cur[it] = make_uint4(o[0], o[1], o[2], o[3]);
+      if (y_out) y_out[row * nvec + vi] = cur[it];
+    }
+    if (q == nullptr) continue;
+    bits = block_max_bits(bits, red_u, tid);
+    const RowQuantizer rq(bits);
+    if (tid == 0) scale[row] = __float2bfloat16_rn(rq.s);
+#pragma unroll
+    for (int it = 0; it < kDVec; ++it) {
+      const int vi = tid + it * kDThreads;
+      if (vi >= nvec) continue;
+      const uint32_t w[4] = {cur[it].x, cur[it].y, cur[it].z, cur[it].w};
+      q[row * nvec + vi] = rq.codes(w);
+    }
+  }
+}
+
 // One CTA per row of [gate | up]; the product row is staged in shared memory (f * 2 bytes)
 // between the absmax pass and the quantizing pass.
 __global__ void __launch_bounds__(kDThreads)
@@ -306,6 +430,39 @@ int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weigh
   add_rmsnorm_kernel<<<grid, kDThreads, 0, (cudaStream_t)stream>>>(
       (const uint4*)x, (const uint4*)delta, (const uint4*)weight, (float)eps, rows, (int)(d / 8),
       (uint4*)x_out, (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, void* const* flags,
+                                  int world, int rank, int* launches, int max_ctas,
+                                  const void* weight, double eps, int64_t rows, int64_t d,
+                                  void* x_out, void* y_out, void* q, void* scale,
+                                  int32_t* error_flag, qwx_stream_t stream) {
+  if (!x || !partials || !flags || !launches || !weight || !x_out || (!y_out && !q) || (q && !scale))
+    return QWX_ERR_NULL;
+  if (world < 2 || world > kMaxPeers || rank < 0 || rank >= world || max_ctas <= 0) return QWX_ERR_SHAPE;
+  if (rows <= 0 || d <= 0 || d % 8) return QWX_ERR_SHAPE;
+  if (d > (int64_t)kDThreads * kDVec * 8) return QWX_ERR_UNSUPPORTED;
+  PeerArgs pa;
+  uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
+                  reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(y_out);
+  for (int r = 0; r < world; ++r) {
+    if (!partials[r] || !flags[r]) return QWX_ERR_NULL;
+    pa.partial[r] = (const uint4*)partials[r];
+    pa.flags[r] = (int*)flags[r];
+    all |= reinterpret_cast<uintptr_t>(partials[r]);
+  }
+  if ((all & 15) || (reinterpret_cast<uintptr_t>(q) & 7)) return QWX_ERR_ALIGN;
+  pa.launches = launches;
+  pa.world = world; pa.rank = rank;
+  pa.error_flag = error_flag;
+  // every rank must launch the same number of CTAs: the hand-shake is per CTA
+  const int64_t cap = max_ctas < 148 * 8 ? max_ctas : 148 * 8;
+  const unsigned grid = (unsigned)(rows < cap ? rows : cap);
+  add_rmsnorm_peer_kernel<<<grid, kDThreads, 0, (cudaStream_t)stream>>>(
+      (const uint4*)x, pa, (const uint4*)weight, (float)eps, rows, (int)(d / 8), (uint4*)x_out,
+      (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale);
   QWX_CHECK_LAUNCH();
   return QWX_OK;
 }

@@ -65,6 +65,18 @@ class _Comm:
     self.group = group
     self.size = self.dist.get_world_size(group) if self.dist else 1
     self.rank = self.dist.get_rank(group) if self.dist else 0
+    self.exchange = None      # fused.PeerExchange once opened
+    self.peer_active = False  # set while the fused layer loop runs
+
+  def open_exchange(self, capacity: int, device):
+    """Collective: maps every rank's partial-sum buffers into every other rank (symmetric
+    memory over NVLink), so that the consumer of a row-parallel projection can add the ranks'
+    partials itself.  Leaves `exchange` None where that is not possible."""
+    if self.size > 1 and self.exchange is None and torch.device(device).type == 'cuda':
+      group = self.group if self.group is not None else self.dist.group.WORLD
+      self.exchange = fused.PeerExchange.open(group, self.rank, self.size, capacity, device)
+    elif self.exchange is not None and self.exchange.capacity < capacity:
+      raise ValueError('exchange buffers are smaller than this call needs')
 
   def all_reduce_sum(self, x: torch.Tensor) -> torch.Tensor:
     if self.size > 1:
@@ -136,6 +148,11 @@ class RowParallelDense(nn.Dense):
       y = dg.dot_general(xq, kernel.array, dn, preferred_element_type=torch.float32)
       return self.comm.all_reduce_sum(y).to(x.dtype)
     y = ops.dot_general(x, kernel, dn)
+    ex = self.comm.exchange
+    if (self.comm.peer_active and ex is not None and y.dtype == torch.bfloat16
+        and y.numel() <= ex.capacity):
+      # leave the partial where the peers can read it: the next add + norm kernel sums the ranks
+      return ex.publish(y)
     return self.comm.all_reduce_sum(y)
 
 
@@ -268,6 +285,10 @@ class Decoder(torch.nn.Module):
     self._init_weights(seed, t, r)
     self.cache = None
     self.fuse = True   # fused element-wise kernels on CUDA bf16 tensors (same arithmetic)
+    # Under tensor parallelism, fold the all-reduce of the row-parallel projections into the
+    # add + norm kernel that consumes them (peer loads over NVLink) instead of calling NCCL.
+    self.peer_exchange = not exact_act_scale
+    self.prefill_rows = 4 * 2048   # tokens per prefill chunk the exchange buffers are sized for
 
   # -- weights ---------------------------------------------------------------------------
 
@@ -337,6 +358,9 @@ class Decoder(torch.nn.Module):
                                                  dtype=torch.float32) / cfg.head_dim))
     ang = pos[:, None] * inv[None, :]
     self.cos, self.sin = ang.cos(), ang.sin()
+    if self.peer_exchange and self.comm.size > 1:
+      # room for the partial sums of one prefill chunk (prefill_rows tokens) or one decode step
+      self.comm.open_exchange(max(self.prefill_rows, batch) * cfg.d_model, self.device)
 
   def forward(self, tokens: torch.Tensor, pos=0, batch_offset: int = 0,
               last_only: bool = True) -> torch.Tensor:
@@ -352,10 +376,16 @@ class Decoder(torch.nn.Module):
       cos, sin = self.cos[pos:pos + T], self.sin[pos:pos + T]
     if self.fuse and x.is_cuda and x.dtype == torch.bfloat16:
       delta = None
-      for i, blk in enumerate(self.layers):
-        ck = self.cache[i, 0, batch_offset:batch_offset + B]
-        cv = self.cache[i, 1, batch_offset:batch_offset + B]
-        x, delta = blk.forward_fused(x, delta, self.cos, self.sin, ck, cv, pos)
+      self.comm.peer_active = self.comm.exchange is not None
+      try:
+        for i, blk in enumerate(self.layers):
+          ck = self.cache[i, 0, batch_offset:batch_offset + B]
+          cv = self.cache[i, 1, batch_offset:batch_offset + B]
+          x, delta = blk.forward_fused(x, delta, self.cos, self.sin, ck, cv, pos)
+      finally:
+        self.comm.peer_active = False
+      if isinstance(delta, fused.PeerPartial):   # the last layer's MLP output: plain all-reduce
+        delta = delta.all_reduce(self.comm)
       if last_only:
         x, delta = x[:, -1:], delta[:, -1:]
       x = fused.AddRmsNorm(x, delta, self.final_norm.scale, self.final_norm.eps)

@@ -54,12 +54,77 @@ class LazyAct:
     raise NotImplementedError
 
 
+class PeerExchange:
+  """Buffers through which the ranks of a tensor-parallel group read each other's partial
+  sums with peer loads (symmetric memory over NVLink): two alternating partial buffers, a flag
+  array per rank and this rank's launch counts.  Built by `open`, which is collective."""
+
+  MAX_CTAS = 148 * 8
+
+  def __init__(self, group, rank: int, world: int, capacity: int, device):
+    import ctypes
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm
+    self.rank, self.world, self.capacity, self.device = rank, world, capacity, device
+    self.partials = [symm.empty((capacity,), dtype=torch.bfloat16, device=device) for _ in range(2)]
+    self.flags = symm.empty((self.MAX_CTAS * world,), dtype=torch.int32, device=device)
+    self.flags.zero_()
+    handles = [symm.rendezvous(t, group) for t in self.partials]
+    fh = symm.rendezvous(self.flags, group)
+    self._keep = handles + [fh]
+    arr = ctypes.c_void_p * world
+    self.partial_ptrs = [arr(*[int(p) for p in h.buffer_ptrs]) for h in handles]
+    self.flag_ptrs = arr(*[int(p) for p in fh.buffer_ptrs])
+    self.launches = torch.zeros(self.MAX_CTAS, dtype=torch.int32, device=device)
+    self.turn = 0
+    torch.cuda.synchronize(device)
+    dist.barrier(group=group)      # every rank's flags are zero before anyone raises one
+
+  @classmethod
+  def open(cls, group, rank, world, capacity, device):
+    """Returns the exchange, or None where symmetric memory cannot be set up (the caller then
+    keeps the NCCL all-reduce)."""
+    try:
+      return cls(group, rank, world, capacity, device)
+    except Exception as e:   # noqa: BLE001 -- any failure here means: no peer path
+      import warnings
+      warnings.warn(f'peer-memory exchange unavailable, using NCCL all-reduce: {e!r}')
+      return None
+
+  def publish(self, y: torch.Tensor) -> 'PeerPartial':
+    """Copies this rank's partial output into the buffer whose turn it is."""
+    if y.dtype != torch.bfloat16 or y.numel() > self.capacity:
+      raise ValueError('partial does not fit the exchange buffers')
+    which = self.turn
+    self.turn ^= 1
+    view = self.partials[which][:y.numel()].view(y.shape)
+    view.copy_(y)
+    return PeerPartial(self, which, view)
+
+
+class PeerPartial:
+  """This rank's partial output of a row-parallel projection, published for its peers; the
+  sum over ranks is formed by whoever consumes it (AddRmsNorm, or `all_reduce`)."""
+
+  def __init__(self, exchange: PeerExchange, which: int, local: torch.Tensor):
+    self.exchange, self.which, self.local = exchange, which, local
+    self.shape = tuple(local.shape)
+
+  def all_reduce(self, comm) -> torch.Tensor:
+    """The plain tensor, through the group's NCCL all-reduce (a collective all ranks make)."""
+    return comm.all_reduce_sum(self.local.clone())
+
+
 class AddRmsNorm(LazyAct):
   """RMSNorm(x + delta) * weight; after it has been consumed, `.residual` is bf16(x + delta)
   (x itself when delta is None)."""
 
-  def __init__(self, x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
-               eps: float):
+  def __init__(self, x: torch.Tensor, delta, weight: torch.Tensor, eps: float):
+    self.peer = delta if isinstance(delta, PeerPartial) else None
+    if self.peer is not None:
+      if tuple(delta.shape) != tuple(x.shape):
+        raise ValueError('partial and residual shapes differ')
+      delta = delta.local
     _lib.require_cuda(x, delta, weight)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
       raise ValueError('AddRmsNorm takes bfloat16 tensors.')
@@ -75,6 +140,18 @@ class AddRmsNorm(LazyAct):
     x_out = None
     if self.delta is not None:
       x_out = torch.empty_like(self.x) if self.residual is None else self.residual
+    if self.peer is not None:
+      if self.residual is not None:
+        raise RuntimeError('a peer partial is consumed once: every rank makes the same calls')
+      ex = self.peer.exchange
+      _lib.check(_lib.lib().qwx_add_rmsnorm_quantize_peer(
+          _lib.ptr(self.x), ex.partial_ptrs[self.peer.which], ex.flag_ptrs, ex.world, ex.rank,
+          _lib.ptr(ex.launches), ex.MAX_CTAS, _lib.ptr(self.weight), self.eps, rows, d,
+          _lib.ptr(x_out), _lib.ptr(y), _lib.ptr(q), _lib.ptr(scale),
+          _lib.ptr(_lib.error_flag(self.device)), _lib.stream_ptr(self.device)),
+          'add_rmsnorm_quantize_peer')
+      self.residual = x_out
+      return
     _lib.check(_lib.lib().qwx_add_rmsnorm_quantize(
         _lib.ptr(self.x), _lib.ptr(self.delta), _lib.ptr(self.weight), self.eps, rows, d,
         _lib.ptr(x_out), _lib.ptr(y), _lib.ptr(q), _lib.ptr(scale),
