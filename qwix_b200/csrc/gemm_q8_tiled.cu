@@ -14,8 +14,9 @@
 // correction and the scales, and keep the running float32 sums in registers.  That bounds the
 // tile to 128 x 128 (128 running sums per thread).
 //
-// Warp roles are those of the untiled kernel: warp 0 TMA producer, warp 1 MMA issuer, warp 2
-// owns the tensor-memory allocation, warps 4-7 epilogue.  Every wait is bounded.
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warp 2 owns the tensor-memory allocation,
+// warps 4-11 epilogue (two per tensor-memory lane quarter, 64 columns each: with 128-wide K
+// tiles the epilogue, not the MMA, sets the pace).  Every wait is bounded.
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -38,7 +39,7 @@ constexpr int TK = 128;        // bytes == elements for 8-bit codes
 constexpr int UMMA_K8 = 32;
 constexpr int kStagesT = 6;
 constexpr int kStageBytesT = (TM + TN) * TK;
-constexpr int kThreadsT = 256;
+constexpr int kThreadsT = 384;      // 4 control warps + 8 epilogue warps
 constexpr int kEpiWarpT = 4;
 
 struct ControlT {
@@ -48,8 +49,8 @@ struct ControlT {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort;
-  float sb[4][2][TN];      // per epilogue warp, double-buffered per K tile
-  int32_t zc[4][2][TN];
+  float sb[8][2][TN / 2];  // per epilogue warp (64 columns each), double-buffered per K tile
+  int32_t zc[8][2][TN / 2];
 };
 
 constexpr size_t kSmemBytesT = 1024 + (size_t)kStagesT * kStageBytesT + sizeof(ControlT);
@@ -104,7 +105,7 @@ gemm_q8_tiled_kernel(const __grid_constant__ CUtensorMap tma_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
-      mbar_init(smem_u32(&ctl->acc_empty[a]), 4);
+      mbar_init(smem_u32(&ctl->acc_empty[a]), 8);
     }
     ctl->abort = 0;
     fence_barrier_init();
@@ -202,7 +203,9 @@ gemm_q8_tiled_kernel(const __grid_constant__ CUtensorMap tma_a,
     }
   } else if (warp >= kEpiWarpT) {
     // ---------------- epilogue: drain one accumulator per K tile, keep running sums ----------------
-    const int q = warp - kEpiWarpT;           // tensor-memory lane quarter of this warp
+    const int ew = warp - kEpiWarpT;          // epilogue warp 0..7
+    const int q = ew & 3;                     // tensor-memory lane quarter of this warp
+    const int ch = ew >> 2;                   // which 64 columns of the tile
     const bool reference = p.epilogue == QWX_EPI_REFERENCE;
     const bool has_corr = p.corr_row != nullptr && p.corr_col != nullptr;
     const bool fast_i2f = p.fast_i2f != 0;
@@ -213,8 +216,8 @@ gemm_q8_tiled_kernel(const __grid_constant__ CUtensorMap tma_a,
     // Scales and correction factors of one (output tile, K tile): four columns per lane for
     // the warp's shared copy, one row value per lane.
     struct Prefetch {
-      float sb[4];
-      int32_t zc[4];
+      float sb[2];
+      int32_t zc[2];
       float sa;
       int32_t zr;
     };
@@ -224,8 +227,8 @@ gemm_q8_tiled_kernel(const __grid_constant__ CUtensorMap tma_a,
       const int n0 = (tile / p.tiles_m) * TN;
       const int64_t m = (int64_t)m0 + q * 32 + lane;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int64_t n = (int64_t)n0 + lane + 32 * i;
+      for (int i = 0; i < 2; ++i) {
+        const int64_t n = (int64_t)n0 + ch * 64 + lane + 32 * i;
         const bool in = n < p.N;
         f.sb[i] = (p.sb && in) ? load_scale_t(p.sb, p.scale_dtype, (p.sb_tiled ? (int64_t)t * p.N : 0) + n)
                                : 1.0f;
@@ -241,14 +244,14 @@ gemm_q8_tiled_kernel(const __grid_constant__ CUtensorMap tma_a,
     bool have = tile < num_tiles;
     Prefetch pf;
     if (have) pf = fetch(tile, t);
-    float v[TN];
+    float v[TN / 2];
 
     while (have && ok) {
       const int buf = it & 1;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        ctl->sb[q][buf][lane + 32 * i] = pf.sb[i];
-        ctl->zc[q][buf][lane + 32 * i] = pf.zc[i];
+      for (int i = 0; i < 2; ++i) {
+        ctl->sb[ew][buf][lane + 32 * i] = pf.sb[i];
+        ctl->zc[ew][buf][lane + 32 * i] = pf.zc[i];
       }
       const float sa = pf.sa;
       const int32_t zr = pf.zr;
@@ -265,14 +268,14 @@ gemm_q8_tiled_kernel(const __grid_constant__ CUtensorMap tma_a,
 
       if (t == 0) {
 #pragma unroll
-        for (int j = 0; j < TN; ++j) v[j] = 0.0f;
+        for (int j = 0; j < TN / 2; ++j) v[j] = 0.0f;
       }
-      const float* sbv = ctl->sb[q][buf];
-      const int32_t* zcv = ctl->zc[q][buf];
+      const float* sbv = ctl->sb[ew][buf];
+      const int32_t* zcv = ctl->zc[ew][buf];
 #pragma unroll
-      for (int c = 0; c < TN / 32; ++c) {
+      for (int c = 0; c < TN / 64; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * TN + c * 32, r);
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * TN + ch * 64 + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -305,8 +308,8 @@ gemm_q8_tiled_kernel(const __grid_constant__ CUtensorMap tma_a,
         const int64_t m = (int64_t)m0 + q * 32 + lane;
         if (m < p.M) {
 #pragma unroll
-          for (int c = 0; c < TN / 32; ++c) {
-            const int64_t ncol = (int64_t)n0 + c * 32;
+          for (int c = 0; c < TN / 64; ++c) {
+            const int64_t ncol = (int64_t)n0 + ch * 64 + c * 32;
             if (ncol >= p.N) break;
             const float* vc = v + c * 32;
             if (p.out_dtype == QWX_F32) {
