@@ -173,6 +173,21 @@ int qwx_gemm_q8_ws(const void* a, const void* b, int code_dtype, int b_layout,
                    void* workspace, size_t workspace_bytes, int workspace_is_zero,
                    int32_t* error_flag, qwx_stream_t stream);
 
+/* An activation quantized on the fly and contracted with a quantized weight: what
+ * BoxedParamProvider.dot_general does for a rule with act_qtype set (boxed_param.py:109-171:
+ * quantize_act :416-455 with per-token absmax scales, then dot_general.py:135-261), as one
+ * call.  a: bf16 [M, K]; wq: int8 or e4m3 codes ([K, N] or [N, K]) with scales sw: bf16 [N];
+ * code_dtype is the qtype of both operands.  The codes and scales of a are written to the
+ * workspace (scales: bf16 [M] at offset 0; codes: [M, K] at the next multiple of 256 bytes)
+ * and are bit-identical to qwx_quantize with one tile per row; the product is bit-identical
+ * to qwx_gemm_q8 on them.  workspace: qwx_quant_gemm_q8_workspace_bytes(M, K) bytes,
+ * 256-byte aligned. */
+size_t qwx_quant_gemm_q8_workspace_bytes(int64_t M, int64_t K);
+int qwx_quant_gemm_q8(const void* a, int64_t M, int64_t K, const void* wq, const void* sw,
+                      int64_t N, int code_dtype, int b_layout, int rounding, void* out,
+                      int out_dtype, int epilogue, void* workspace, size_t workspace_bytes,
+                      int32_t* error_flag, qwx_stream_t stream);
+
 /* The same product for at most 32 rows of int8 activations against an int8 weight held
  * [N, K] (the decode step of a served model): a warp-level kernel that streams the weight
  * once with no per-tile set-up.  K a multiple of 256, N of 16.  out_dtype as qwx_gemm_q8

@@ -53,6 +53,9 @@ _SIGNATURES = {
     'qwx_hadamard_gemm_workspace_bytes': (_sz, [_i64, _i64]),
     'qwx_hadamard_gemm': (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _vp, _int,
                                  _int, _vp, _sz, _vp, _vp]),
+    'qwx_quant_gemm_q8_workspace_bytes': (_sz, [_i64, _i64]),
+    'qwx_quant_gemm_q8': (_int, [_vp, _i64, _i64, _vp, _vp, _i64, _int, _int, _int, _vp, _int, _int,
+                                 _vp, _sz, _vp, _vp]),
     'qwx_gemm_q8': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,
                            _int, _vp, _int, _int, _vp, _vp]),
     'qwx_gemm_q8_tiled': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,

@@ -660,3 +660,33 @@ extern "C" int qwx_gemm_q8_ws(const void* a, const void* b, int code_dtype, int 
                       scale_dtype, out, out_dtype, epilogue, workspace, workspace_bytes,
                       workspace_is_zero, error_flag, stream);
 }
+
+extern "C" size_t qwx_quant_gemm_q8_workspace_bytes(int64_t M, int64_t K) {
+  if (M <= 0 || K <= 0) return 0;
+  return (size_t)(M * K) + (size_t)((M * 2 + 255) / 256 * 256);
+}
+
+// Per-token quantization of the bf16 activations followed by the GEMM, as one call.  The two
+// kernels run back to back on `stream`; the codes ([M, K], 1 byte each) are written once and
+// read by the GEMM while most of them are still in the 126 MB L2.  Quantizing inside the
+// GEMM's producer instead would repeat the division and rounding of every activation once per
+// column of output tiles (N / 256 times) and needs the row's absmax first, i.e. a second read
+// of the bf16 rows, so the separate pass is the cheaper form on this part.
+extern "C" int qwx_quant_gemm_q8(const void* a, int64_t M, int64_t K, const void* wq,
+                                 const void* sw, int64_t N, int code_dtype, int b_layout,
+                                 int rounding, void* out, int out_dtype, int epilogue,
+                                 void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                                 qwx_stream_t stream) {
+  if (!a || !wq || !sw || !out || !workspace) return QWX_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0) return QWX_ERR_SHAPE;
+  if (code_dtype != QWX_S8 && code_dtype != QWX_E4M3) return QWX_ERR_DTYPE;
+  if (workspace_bytes < qwx_quant_gemm_q8_workspace_bytes(M, K)) return QWX_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return QWX_ERR_ALIGN;
+  void* sa = workspace;                                     // [M] bf16 row scales
+  void* aq = (char*)workspace + (M * 2 + 255) / 256 * 256;  // [M, K] codes
+  int rc = qwx_quantize(a, QWX_BF16, 1, M, K, 1, 1, K, QWX_ABSMAX, 0, 0.0, code_dtype, rounding,
+                        aq, sa, nullptr, nullptr, 0, stream);
+  if (rc) return rc;
+  return gemm_q8_impl(aq, wq, code_dtype, b_layout, M, N, K, 0, sa, 0, sw, 0, QWX_BF16, out,
+                      out_dtype, epilogue, nullptr, 0, 0, error_flag, stream);
+}

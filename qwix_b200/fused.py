@@ -200,3 +200,51 @@ def rope_cache(qkv: torch.Tensor, hq: int, hkv: int, hd: int, cos: torch.Tensor,
       _lib.ptr(cache_v), cache_k.stride(0), cache_k.stride(1), _lib.stream_ptr(qkv.device)),
       'rope_cache')
   return q.transpose(1, 2)
+
+
+def quantized_matmul(x: torch.Tensor, w: QArray, out_dtype=torch.bfloat16,
+                     return_act: bool = False):
+  """x [M, K] bf16 times a quantized weight [K, N]: the activation is quantized per token
+  (absmax, the weight's qtype; boxed_param.py:416-455) and contracted on the tensor cores with
+  the scales in the epilogue (dot_general.py:135-261), as one library call.  Bit-identical to
+  `dot_general(quantize(x, per token), w)`.  With `return_act` the QArray of x is returned
+  too (views of the call's workspace)."""
+  from qwix_b200.core import dot_general as _dg
+  from qwix_b200.core import numerics
+  if x.ndim != 2 or x.dtype != torch.bfloat16:
+    raise ValueError('quantized_matmul expects a 2-D bfloat16 activation.')
+  store, code = numerics.storage(w.qtype)
+  if code not in (_lib.S8, _lib.E4M3):
+    raise NotImplementedError(f'quantized_matmul takes int8 or float8_e4m3fn weights, got {w.qtype}.')
+  k, n = w.shape
+  if x.shape[1] != k:
+    raise ValueError(f'contracting sizes differ: {x.shape[1]} and {k}.')
+  if tuple(w.scale.shape) != (1, n) or w.zero_point is not None:
+    raise NotImplementedError('the weight must be quantized per output channel, symmetric.')
+  _lib.require_cuda(x, w.qvalue)
+  x = x.contiguous()
+  m = x.shape[0]
+  wq = w.qvalue
+  if wq.t().is_contiguous() and not wq.is_contiguous():
+    codes, layout = wq.t(), _lib.B_NK
+  else:
+    codes, layout = wq.contiguous(), _lib.B_KN
+  if layout == _lib.B_KN and n % 16:
+    codes, layout = wq.t().contiguous(), _lib.B_NK
+  L = _lib.lib()
+  ws = torch.empty(L.qwx_quant_gemm_q8_workspace_bytes(m, k), dtype=torch.uint8, device=x.device)
+  out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+  err = _lib.error_flag(x.device)
+  oc = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}[out_dtype]
+  epi = _lib.EPI_REFERENCE if _dg.EPILOGUE == 'reference' else _lib.EPI_F32
+  _lib.check(L.qwx_quant_gemm_q8(
+      _lib.ptr(x), m, k, _lib.ptr(codes), _lib.ptr(w.scale.to(torch.bfloat16).contiguous()), n,
+      code, layout, qarray._rounding_code(), _lib.ptr(out), oc, epi, _lib.ptr(ws), ws.numel(),
+      _lib.ptr(err), _lib.stream_ptr(x.device)), 'quantized_matmul')
+  if not return_act:
+    return out
+  off = (m * 2 + 255) // 256 * 256
+  act = QArray(qvalue=ws[off:off + m * k].view(store).view(m, k),
+               scale=ws[:m * 2].view(torch.bfloat16).view(m, 1), zero_point=None,
+               qtype=numerics.qtype_name(w.qtype))
+  return out, act

@@ -407,3 +407,65 @@ def test_code_sums(k_axis, t_major):
                                       t_major, _lib.ptr(out), _lib.stream_ptr()), 'code_sums')
   torch.cuda.synchronize()
   assert np.array_equal(out.cpu().numpy(), want)
+
+
+# ---------------------------------------------------------------------------------------------
+# Activation quantization + GEMM as one call (qwx_quant_gemm_q8).
+
+QUANT_GEMM_CASES = [('int8', 192, 1024, 512, False), ('int8', 640, 2048, 768, True),
+                    ('int8', 5, 512, 264, False), ('float8_e4m3fn', 320, 1024, 512, False),
+                    ('float8_e4m3fn', 48, 768, 256, True)]
+
+
+@pytest.mark.parametrize('case', QUANT_GEMM_CASES,
+                         ids=[f'{q}-{m}x{k}x{n}-{"nk" if t else "kn"}'
+                              for q, m, k, n, t in QUANT_GEMM_CASES])
+def test_quantized_matmul_one_call_matches_oracle_and_two_calls(case):
+  from qwix_b200 import fused
+  qtype, M, K, N, nk = case
+  rng = np.random.default_rng(11)
+  x = rng.standard_normal((M, K)).astype(np.float32)
+  x[:, rng.choice(K, 8, replace=False)] *= 20
+  x[M // 2] = 0                       # an all-zero token: scale 1, codes 0
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32)
+  x, w = x.astype(h.np_dtype('bfloat16')), w.astype(h.np_dtype('bfloat16'))
+  kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=None, qtype=qtype)
+  xo = oq.quantize(x, odg.get_how_to_quantize(for_lhs=True, **kw))
+  wo = oq.quantize(w, odg.get_how_to_quantize(for_lhs=False, **kw))
+  want = odg.dot_general(xo, wo, DN).astype(np.float32)
+
+  xt = h.to_torch(x)
+  wq = bq.quantize(h.to_torch(w), bdg.get_how_to_quantize(for_lhs=False, **kw))
+  if nk:    # codes held [N, K], seen as [K, N]
+    wq = dataclasses.replace(wq, qvalue=wq.qvalue.t().contiguous().t())
+  out, act = fused.quantized_matmul(xt, wq, return_act=True)
+  assert h.codes_equal(act.qvalue, xo.qvalue)
+  assert np.array_equal(h.to_numpy(act.scale).view(np.uint16), xo.scale.view(np.uint16))
+  g = h.to_numpy(out).astype(np.float32)
+  assert np.all(np.abs(g - want) <= 1e-2 + 2e-2 * np.abs(want))
+  two = bdg.dot_general(bq.quantize(xt, bdg.get_how_to_quantize(for_lhs=True, **kw)), wq, DN)
+  if qtype == 'int8':   # exact int32 sums: any split of K gives the same bits
+    assert torch.equal(out.view(torch.int16), two.view(torch.int16))
+  else:                 # float32 sums may be added in another order when K is split
+    assert torch.allclose(out.float(), two.float(), rtol=2 ** -7, atol=1e-3)
+  _lib.raise_on_device_error()
+
+
+def test_quantized_matmul_rejects_bad_arguments():
+  from qwix_b200 import fused
+  x = torch.zeros((4, 256), dtype=torch.bfloat16, device='cuda')
+  w = bq.quantize(torch.ones((256, 32), dtype=torch.bfloat16, device='cuda'),
+                  bq.HowToQuantize(qtype='int8', channelwise_axes=[1]))
+  with pytest.raises(ValueError):
+    fused.quantized_matmul(x.float(), w)
+  with pytest.raises(ValueError):
+    fused.quantized_matmul(x[:, :128], w)
+  L = _lib.lib()
+  out = torch.empty((4, 32), dtype=torch.bfloat16, device='cuda')
+  ws = torch.empty(L.qwx_quant_gemm_q8_workspace_bytes(4, 256), dtype=torch.uint8, device='cuda')
+  args = lambda nbytes: (_lib.ptr(x), 4, 256, _lib.ptr(w.qvalue), _lib.ptr(w.scale), 32, _lib.S8,
+                         _lib.B_KN, 0, _lib.ptr(out), _lib.BF16, 0, _lib.ptr(ws), nbytes, None,
+                         _lib.stream_ptr())
+  assert L.qwx_quant_gemm_q8(*args(ws.numel() - 1)) == 6      # QWX_ERR_WORKSPACE
+  assert L.qwx_quant_gemm_q8(*args(ws.numel())) == 0
+  torch.cuda.synchronize()
