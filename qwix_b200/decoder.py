@@ -172,7 +172,7 @@ class Attention(torch.nn.Module):
                               comm=comm, exact_act_scale=exact)
     self.layer = layer
 
-  def forward(self, x, cos, sin, cache_k, cache_v, pos):
+  def forward(self, x, cos, sin, cache_k, cache_v, pos, mask=None):
     B, T, _ = x.shape
     hd = self.cfg.head_dim
     qkv = self.qkv(x)
@@ -181,7 +181,8 @@ class Attention(torch.nn.Module):
       # and k and writes k and v straight into the cache
       q = fused.rope_cache(qkv, self.hq, self.hkv, hd, cos, sin, pos, cache_k, cache_v)
       if isinstance(pos, torch.Tensor):
-        mask = (torch.arange(cache_k.shape[2], device=qkv.device) <= pos).view(1, 1, 1, -1)
+        if mask is None:
+          mask = _key_mask(cache_k.shape[2], pos)
         out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
       else:
         out = F.scaled_dot_product_attention(q, cache_k[:, :, :pos + T], cache_v[:, :, :pos + T],
@@ -197,7 +198,8 @@ class Attention(torch.nn.Module):
       # write it into the cache by index and mask the keys that lie beyond it.
       cache_k.index_copy_(2, pos, k)
       cache_v.index_copy_(2, pos, v)
-      mask = (torch.arange(cache_k.shape[2], device=x.device) <= pos).view(1, 1, 1, -1)
+      if mask is None:
+        mask = _key_mask(cache_k.shape[2], pos)
       out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
       out = out.transpose(1, 2).reshape(B, T, self.hq * hd)
       return self.o(out)
@@ -210,6 +212,11 @@ class Attention(torch.nn.Module):
                                            is_causal=False, enable_gqa=True)
     out = out.transpose(1, 2).reshape(B, T, self.hq * hd)
     return self.o(out)
+
+
+def _key_mask(length: int, pos: torch.Tensor) -> torch.Tensor:
+  """Keys a single-token step at device-held position `pos` may attend to: [1, 1, 1, length]."""
+  return (torch.arange(length, device=pos.device) <= pos).view(1, 1, 1, -1)
 
 
 def _rope(x, cos, sin):
@@ -246,16 +253,16 @@ class Block(torch.nn.Module):
     self.ffn_norm = RMSNorm(cfg.d_model, cfg.norm_eps, cfg.dtype, device)
     self.ffn = FeedForward(cfg, comm, device, exact)
 
-  def forward(self, x, cos, sin, ck, cv, pos):
-    x = x + self.attn(self.attn_norm(x), cos, sin, ck, cv, pos)
+  def forward(self, x, cos, sin, ck, cv, pos, mask=None):
+    x = x + self.attn(self.attn_norm(x), cos, sin, ck, cv, pos, mask)
     return x + self.ffn(self.ffn_norm(x))
 
-  def forward_fused(self, x, delta, cos, sin, ck, cv, pos):
+  def forward_fused(self, x, delta, cos, sin, ck, cv, pos, mask=None):
     """The same layer with the residual add, the norm and the activation quantization of the
     next projection in one kernel each.  Takes the residual stream x and the not yet added
     output `delta` of the previous layer's MLP; returns the new pair."""
     a = fused.AddRmsNorm(x, delta, self.attn_norm.scale, self.attn_norm.eps)
-    attn_out = self.attn(a, cos, sin, ck, cv, pos)
+    attn_out = self.attn(a, cos, sin, ck, cv, pos, mask)
     f = fused.AddRmsNorm(a.residual, attn_out, self.ffn_norm.scale, self.ffn_norm.eps)
     ffn_out = self.ffn(f)
     return f.residual, ffn_out
@@ -369,9 +376,11 @@ class Decoder(torch.nn.Module):
     Returns full-vocabulary logits [B, 1 or T, vocab] (float32)."""
     B, T = tokens.shape
     x = self.embed[tokens]
+    mask = None
     if isinstance(pos, torch.Tensor):
       assert T == 1
       cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
+      mask = _key_mask(self.cache.shape[4], pos)   # one mask per step, shared by the layers
     else:
       cos, sin = self.cos[pos:pos + T], self.sin[pos:pos + T]
     if self.fuse and x.is_cuda and x.dtype == torch.bfloat16:
@@ -381,7 +390,7 @@ class Decoder(torch.nn.Module):
         for i, blk in enumerate(self.layers):
           ck = self.cache[i, 0, batch_offset:batch_offset + B]
           cv = self.cache[i, 1, batch_offset:batch_offset + B]
-          x, delta = blk.forward_fused(x, delta, self.cos, self.sin, ck, cv, pos)
+          x, delta = blk.forward_fused(x, delta, self.cos, self.sin, ck, cv, pos, mask)
       finally:
         self.comm.peer_active = False
       if isinstance(delta, fused.PeerPartial):   # the last layer's MLP output: plain all-reduce
@@ -393,7 +402,7 @@ class Decoder(torch.nn.Module):
       for i, blk in enumerate(self.layers):
         ck = self.cache[i, 0, batch_offset:batch_offset + B]
         cv = self.cache[i, 1, batch_offset:batch_offset + B]
-        x = blk(x, cos, sin, ck, cv, pos)
+        x = blk(x, cos, sin, ck, cv, pos, mask)
       x = self.final_norm(x[:, -1:] if last_only else x)
     logits = self.lm_head(x)
     return self.comm.all_gather_last(logits).float()
