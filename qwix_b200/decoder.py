@@ -182,7 +182,7 @@ class Attention(torch.nn.Module):
       q = fused.rope_cache(qkv, self.hq, self.hkv, hd, cos, sin, pos, cache_k, cache_v)
       if isinstance(pos, torch.Tensor):
         if mask is None:
-          mask = _key_mask(cache_k.shape[2], pos)
+          mask = _key_mask(cache_k.shape[2], pos, q.dtype)
         out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
       else:
         out = F.scaled_dot_product_attention(q, cache_k[:, :, :pos + T], cache_v[:, :, :pos + T],
@@ -199,7 +199,7 @@ class Attention(torch.nn.Module):
       cache_k.index_copy_(2, pos, k)
       cache_v.index_copy_(2, pos, v)
       if mask is None:
-        mask = _key_mask(cache_k.shape[2], pos)
+        mask = _key_mask(cache_k.shape[2], pos, q.dtype)
       out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
       out = out.transpose(1, 2).reshape(B, T, self.hq * hd)
       return self.o(out)
@@ -214,9 +214,13 @@ class Attention(torch.nn.Module):
     return self.o(out)
 
 
-def _key_mask(length: int, pos: torch.Tensor) -> torch.Tensor:
-  """Keys a single-token step at device-held position `pos` may attend to: [1, 1, 1, length]."""
-  return (torch.arange(length, device=pos.device) <= pos).view(1, 1, 1, -1)
+def _key_mask(length: int, pos: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+  """Keys a single-token step at device-held position `pos` may attend to, [1, 1, 1, length],
+  as the additive mask (0 / -inf, in the dtype of the queries) that the attention call would
+  otherwise derive from a boolean one at every layer."""
+  beyond = (torch.arange(length, device=pos.device) > pos).view(1, 1, 1, -1)
+  return torch.zeros(beyond.shape, dtype=dtype, device=pos.device).masked_fill_(
+      beyond, float('-inf'))
 
 
 def _rope(x, cos, sin):
@@ -380,7 +384,7 @@ class Decoder(torch.nn.Module):
     if isinstance(pos, torch.Tensor):
       assert T == 1
       cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
-      mask = _key_mask(self.cache.shape[4], pos)   # one mask per step, shared by the layers
+      mask = _key_mask(self.cache.shape[4], pos, x.dtype)   # one per step, shared by the layers
     else:
       cos, sin = self.cos[pos:pos + T], self.sin[pos:pos + T]
     if self.fuse and x.is_cuda and x.dtype == torch.bfloat16:
