@@ -257,14 +257,17 @@ int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weigh
  * call on every rank; launches: this rank's int32 [max_ctas], zero before the first call.
  * Every rank must make the same sequence of calls with the same rows, and a partial buffer
  * may be rewritten only after one further call of this function (callers alternate two
- * buffers).  The hand-shake between ranks is bounded; if a peer never arrives the call
- * reports QWX_ERR_DEVICE_WAIT through error_flag and writes nothing.  No counterpart in the
+ * buffers).  The grid is min(rows, max_ctas, CTAs the device keeps resident), so that every
+ * hand-shaking CTA is running while it waits; ranks must sit on identical GPUs.  The hand-shake
+ * is bounded by wait_cycles SM clocks (<= 0: the default of 4e9, about two seconds): ranks must
+ * enter the call within that budget of each other.  If a peer never arrives the call reports
+ * QWX_ERR_DEVICE_WAIT through error_flag and writes none of its outputs.  No counterpart in the
  * reference (GSPMD inserts the all-reduce there, flax_util.py:354-357). */
 int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, void* const* flags,
                                   int world, int rank, int* launches, int max_ctas,
                                   const void* weight, double eps, int64_t rows, int64_t d,
                                   void* x_out, void* y_out, void* q, void* scale,
-                                  int32_t* error_flag, qwx_stream_t stream);
+                                  int32_t* error_flag, int64_t wait_cycles, qwx_stream_t stream);
 int qwx_silu_mul_quantize(const void* gu, int64_t rows, int64_t f, void* y_out, void* q,
                           void* scale, qwx_stream_t stream);
 int qwx_rope_cache(const void* qkv, int64_t B, int64_t T, int hq, int hkv, int hd,

@@ -63,7 +63,7 @@ _SIGNATURES = {
     'qwx_code_sums': (_int, [_vp, _i64, _i64, _int, _i64, _int, _vp, _vp]),
     'qwx_add_rmsnorm_quantize': (_int, [_vp, _vp, _vp, _dbl, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     'qwx_add_rmsnorm_quantize_peer': (_int, [_vp, _vp, _vp, _int, _int, _vp, _int, _vp, _dbl, _i64, _i64,
-                                             _vp, _vp, _vp, _vp, _vp, _vp]),
+                                             _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     'qwx_silu_mul_quantize': (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     'qwx_rope_cache': (_int, [_vp, _i64, _i64, _int, _int, _int, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                               _i64, _i64, _vp]),
@@ -131,6 +131,16 @@ def error_flag(device) -> torch.Tensor:
   return flag
 
 
+_error_hooks: list = []
+
+
+def on_device_error(hook):
+  """Registers a callable that runs when a device-side failure is reported or cleared: the
+  owners of scratch buffers that kernels are supposed to leave zeroed drop them, because a
+  kernel that gave up on a wait leaves its counters as they were."""
+  _error_hooks.append(hook)
+
+
 def raise_on_device_error(device=None):
   """Synchronises and raises if any kernel of this process reported a wait that ran out."""
   for key, flag in list(_error_flags.items()):
@@ -138,8 +148,20 @@ def raise_on_device_error(device=None):
       continue
     code = int(flag.item())
     if code:
+      for hook in _error_hooks:
+        hook()
       raise RuntimeError(f'a device-side wait ran out on cuda:{key[1]} (status {code}: '
                          f'{lib().qwx_status_string(code).decode()})')
+
+
+def clear_device_error(device=None):
+  """Forgets a reported failure (after the caller has dealt with it) and drops the cached
+  scratch buffers, so that the next call starts from zeroed counters."""
+  for key, flag in list(_error_flags.items()):
+    if device is None or torch.device(device).index in (None, key[1]):
+      flag.zero_()
+  for hook in _error_hooks:
+    hook()
 
 
 def require_cuda(*tensors):

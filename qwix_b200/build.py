@@ -21,15 +21,28 @@ def _newest_source_mtime() -> float:
 
 
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
-  """Compiles every kernel for sm_100a; returns the path of the shared library."""
+  """Compiles every kernel for sm_100a; returns the path of the shared library.  Translation
+  units are compiled side by side (objects under csrc/build/, which is not tracked) and linked
+  into one library."""
   if not force and LIB.exists() and LIB.stat().st_mtime >= _newest_source_mtime():
     return LIB
+  from concurrent.futures import ThreadPoolExecutor
   nvcc = os.environ.get('NVCC', 'nvcc')
-  cmd = [nvcc, *FLAGS, '-o', str(LIB), *[str(CSRC / s) for s in SOURCES]]
-  if verbose:
-    cmd.insert(1, '-Xptxas')
-    cmd.insert(2, '-v')
-  subprocess.run(cmd, check=True, cwd=str(CSRC))
+  objdir = CSRC / 'build'
+  objdir.mkdir(exist_ok=True)
+  compile_flags = [f for f in FLAGS if f != '-shared']
+
+  def compile_one(src: str) -> str:
+    obj = objdir / (src.rsplit('.', 1)[0] + '.o')
+    cmd = [nvcc, *compile_flags, '-c', '-o', str(obj), str(CSRC / src)]
+    if verbose:
+      cmd[1:1] = ['-Xptxas', '-v']
+    subprocess.run(cmd, check=True, cwd=str(CSRC))
+    return str(obj)
+
+  with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+    objects = list(pool.map(compile_one, SOURCES))
+  subprocess.run([nvcc, '-gencode', 'arch=compute_100a,code=sm_100a', '-shared', '-o', str(LIB), *objects], check=True, cwd=str(CSRC))
   return LIB
 
 

@@ -264,6 +264,15 @@ _ws_lock = threading.Lock()
 _ws_cache: dict = {}
 
 
+def _drop_workspaces():
+  with _ws_lock:
+    _ws_cache.clear()
+
+
+# a kernel that gave up on a wait skips the reset of its tile counters: start from new buffers
+_lib.on_device_error(_drop_workspaces)
+
+
 def _splitk_workspace(device, nbytes: int, kind: str = 'split') -> torch.Tensor:
   """Zero-filled scratch for the split-K and the decode-shaped form of the GEMM, one per
   (device, stream, kind).  The kernels leave what they need zero and calls on one stream run

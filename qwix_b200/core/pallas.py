@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import dataclasses
 import itertools
+import threading
 from typing import Any, Callable, Sequence
 
 import torch
@@ -74,12 +75,34 @@ def _block_of(arg, spec, grid_idx):
   return _take_block(arg, spec, grid_idx)
 
 
+_grid_state = threading.local()
+
+
+def program_id(axis: int) -> int:
+  """Index of the running kernel instance along grid axis `axis` (the role of
+  jax.experimental.pallas.program_id inside a kernel body)."""
+  idx = getattr(_grid_state, 'idx', None)
+  if idx is None:
+    raise RuntimeError('program_id is only defined inside a pallas_call kernel body.')
+  return idx[axis]
+
+
+def num_programs(axis: int) -> int:
+  grid = getattr(_grid_state, 'grid', None)
+  if grid is None:
+    raise RuntimeError('num_programs is only defined inside a pallas_call kernel body.')
+  return grid[axis]
+
+
 def pallas_call(kernel: Callable[..., None], out_shape: Any, *, grid: Sequence[int] = (),
                 in_specs: Sequence[BlockSpec] | None = None,
-                out_specs: BlockSpec | Sequence[BlockSpec] | None = None, **kwargs):
+                out_specs: BlockSpec | Sequence[BlockSpec] | None = None,
+                scratch_shapes: Sequence[tuple] = (), **kwargs):
   """pallas.py:27-87 -- returns a function of the operands; `out_shape` is a
   (shape, dtype) pair (or a sequence of them).  The kernel receives input blocks followed
-  by output blocks and writes the outputs in place."""
+  by output blocks and then one tensor per `scratch_shapes` entry (a (shape, dtype) pair:
+  memory that lives across the grid, like the reference's VMEM scratch) and writes the
+  outputs in place.  Grid points run in row-major order, the last axis fastest."""
   del kwargs
   single = isinstance(out_shape, tuple) and len(out_shape) == 2 and \
       isinstance(out_shape[1], torch.dtype)
@@ -91,10 +114,16 @@ def pallas_call(kernel: Callable[..., None], out_shape: Any, *, grid: Sequence[i
         if in_specs is not None else [None] * len(args)
     device = next(a.device for a in args if hasattr(a, 'device'))
     outs = [torch.empty(shape, dtype=dtype, device=device) for shape, dtype in out_shapes]
-    for grid_idx in itertools.product(*[range(g) for g in grid]):
-      ins = [_block_of(a, s, grid_idx) if s is not None else a for a, s in zip(args, specs)]
-      blocks = [_take_block(o, s, grid_idx) for o, s in zip(outs, out_spec_list)]
-      kernel(*ins, *blocks)
+    scratch = [torch.empty(shape, dtype=dtype, device=device) for shape, dtype in scratch_shapes]
+    _grid_state.grid = tuple(grid)
+    try:
+      for grid_idx in itertools.product(*[range(g) for g in grid]):
+        _grid_state.idx = grid_idx
+        ins = [_block_of(a, s, grid_idx) if s is not None else a for a, s in zip(args, specs)]
+        blocks = [_take_block(o, s, grid_idx) for o, s in zip(outs, out_spec_list)]
+        kernel(*ins, *blocks, *scratch)
+    finally:
+      _grid_state.idx = _grid_state.grid = None
     return outs[0] if single else tuple(outs)
 
   return run

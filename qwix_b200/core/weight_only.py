@@ -26,6 +26,14 @@ _ws_lock = threading.Lock()
 _ws_cache: dict = {}
 
 
+def _drop_workspaces():
+  with _ws_lock:
+    _ws_cache.clear()
+
+
+_lib.on_device_error(_drop_workspaces)
+
+
 def eligible(lhs, rhs, dimension_numbers) -> bool:
   """True when (lhs, rhs) is [.., K] bf16 x int4 [K, N] with K-tiled symmetric scales that
   the fused kernel supports."""

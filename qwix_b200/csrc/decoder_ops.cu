@@ -15,6 +15,8 @@
 // code = sat_int8(round_half_even(bf16(y / scale))) per row -- the strict recipe of
 // quantize.cu.  Every rounding of the unfused PyTorch composition is kept, so results differ
 // from it only through the order of the float32 sum of squares.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace qwx {
@@ -206,6 +208,7 @@ struct PeerArgs {
   int* launches;                     // this rank: [ctas] launch counts
   int world, rank;
   int32_t* error_flag;
+  long long wait_cycles;             // budget of the hand-shake, SM clocks
 };
 
 __global__ void __launch_bounds__(kDThreads)
@@ -233,7 +236,7 @@ add_rmsnorm_peer_kernel(const uint4* __restrict__ x, const PeerArgs pa,
       int v;
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
       if (v >= count) break;
-      if ((it & 255u) == 0 && clock64() - t0 > kPeerWaitCycles) {
+      if ((it & 255u) == 0 && clock64() - t0 > pa.wait_cycles) {
         s_ok = 0;
         if (pa.error_flag) atomicExch(pa.error_flag, QWX_ERR_DEVICE_WAIT);
         break;
@@ -434,11 +437,32 @@ int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weigh
   return QWX_OK;
 }
 
+// CTAs of the hand-shaking kernel that can be resident at once on the current device.  The
+// hand-shake pairs CTA b of every rank, so every launched CTA must be running while it waits:
+// the grid never exceeds this number (ranks on identical GPUs compute the same value).
+static int peer_resident_ctas() {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int cached[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int per_sm = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, add_rmsnorm_peer_kernel, kDThreads, 0) !=
+            cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      return 0;
+    cached[dev] = per_sm * sms;
+  }
+  return cached[dev];
+}
+
 int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, void* const* flags,
                                   int world, int rank, int* launches, int max_ctas,
                                   const void* weight, double eps, int64_t rows, int64_t d,
                                   void* x_out, void* y_out, void* q, void* scale,
-                                  int32_t* error_flag, qwx_stream_t stream) {
+                                  int32_t* error_flag, int64_t wait_cycles, qwx_stream_t stream) {
   if (!x || !partials || !flags || !launches || !weight || !x_out || (!y_out && !q) || (q && !scale))
     return QWX_ERR_NULL;
   if (world < 2 || world > kMaxPeers || rank < 0 || rank >= world || max_ctas <= 0) return QWX_ERR_SHAPE;
@@ -457,8 +481,12 @@ int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, vo
   pa.launches = launches;
   pa.world = world; pa.rank = rank;
   pa.error_flag = error_flag;
-  // every rank must launch the same number of CTAs: the hand-shake is per CTA
-  const int64_t cap = max_ctas < 148 * 8 ? max_ctas : 148 * 8;
+  pa.wait_cycles = wait_cycles > 0 ? wait_cycles : kPeerWaitCycles;
+  // Every rank must launch the same number of CTAs (the hand-shake is per CTA), all of them
+  // resident: rows, the caller's flag capacity and the device's occupancy bound the grid.
+  const int resident = peer_resident_ctas();
+  if (resident <= 0) return QWX_ERR_NO_DEVICE;
+  int64_t cap = max_ctas < resident ? max_ctas : resident;
   const unsigned grid = (unsigned)(rows < cap ? rows : cap);
   add_rmsnorm_peer_kernel<<<grid, kDThreads, 0, (cudaStream_t)stream>>>(
       (const uint4*)x, pa, (const uint4*)weight, (float)eps, rows, (int)(d / 8), (uint4*)x_out,

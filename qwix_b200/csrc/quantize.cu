@@ -727,6 +727,12 @@ int dispatch_out(int qtype, Fn&& fn) {
   }
 }
 
+// Tiles that are contiguous row segments of whole 16-byte vectors are quantized in one pass
+// over x with no scratch memory at all.
+bool row_segment_view(const void* x, const void* q, int64_t tp, int64_t tr, int64_t tc) {
+  return tp == 1 && tr == 1 && tc % 8 == 0 && aligned16(x) && aligned16(q);
+}
+
 int check_method(int method, int has_arg, int qtype) {
   if (method != QWX_ABSMAX && method != QWX_MINMAX && method != QWX_RMS) return QWX_ERR_UNSUPPORTED;
   if (method == QWX_RMS && !has_arg) return QWX_ERR_SHAPE;
@@ -738,10 +744,11 @@ int run_calibrate_tiles(const void* x, int x_dtype, const View& vw, const CalibA
                         void* out_a, void* out_b, void* ws, size_t ws_bytes, cudaStream_t st) {
   const size_t need = (size_t)vw.groups() * 2 * sizeof(int);
   if (ws == nullptr || ws_bytes < need) return QWX_ERR_WORKSPACE;
-  if (cudaMemsetAsync(ws, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
+  // every refusal comes before the first thing put on the stream
   const int64_t chunks = (vw.tr + kChunkRows - 1) / kChunkRows;
   const int64_t gy = vw.GR * chunks;
   if (gy > 65535 || vw.P > 65535) return QWX_ERR_UNSUPPORTED;
+  if (cudaMemsetAsync(ws, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
   dim3 grid((unsigned)((vw.C + kChunkCols - 1) / kChunkCols), (unsigned)gy, (unsigned)vw.P);
   const int vec_ok = (vw.C % 8 == 0) && aligned16(x);
   return dispatch_float(x_dtype, [&](auto t) {
@@ -856,7 +863,7 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
   CalibArgs cal{method, has_arg, (float)arg};
 
   // One pass when every tile is a contiguous row segment of whole 16-byte vectors.
-  if (tp == 1 && tr == 1 && tc % 8 == 0 && aligned16(x) && aligned16(q)) {
+  if (row_segment_view(x, q, tp, tr, tc)) {
     const int64_t segments = P * R * (C / tc);
     if (x_dtype == QWX_BF16 && qtype == QWX_S8 && method == QWX_ABSMAX && !has_arg &&
         rounding == QWX_STRICT && tc > 32 * 8 * kCache && tc <= kThreads * 8 * 8) {
@@ -965,7 +972,10 @@ int qwx_quantize_noalloc(const void* x, int x_dtype, int64_t P, int64_t R, int64
   int rc = make_view(P, R, C, tp, tr, tc, &vw);
   if (rc) return rc;
   // Refuse, before touching anything, a view whose statistics do not fit the built-in array.
-  if (qwx_quantize_workspace_bytes(P, R, C, tp, tr, tc) > kBuiltinScratchBytes)
+  // Row-segment views take the one-pass kernels, which use no scratch: they are never refused,
+  // whatever their tile count.
+  if (!row_segment_view(x, q, tp, tr, tc) &&
+      qwx_quantize_workspace_bytes(P, R, C, tp, tr, tc) > kBuiltinScratchBytes)
     return QWX_ERR_WORKSPACE;
   void* scratch = nullptr;
   rc = builtin_scratch_address(&scratch);

@@ -25,6 +25,7 @@ import torch
 import torch.nn.functional as F
 
 import qwix_b200 as qwix
+from qwix_b200 import _lib
 from qwix_b200 import fused
 from qwix_b200 import nn
 from qwix_b200 import ops
@@ -480,4 +481,7 @@ def generate(model, tokens: torch.Tensor, steps: int, prefill_batch: int = 4,
     torch.cuda.synchronize()
     timings['prefill_ms'] = ev[0].elapsed_time(ev[1])
     timings['decode_ms'] = ev[1].elapsed_time(ev[2])
+  # A bounded wait inside a kernel (tensor-core pipeline, peer hand-shake) that ran out leaves
+  # its outputs unwritten: the ids would be garbage, so fail loudly instead.
+  _lib.raise_on_device_error(tokens.device)
   return out

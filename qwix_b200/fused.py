@@ -77,6 +77,7 @@ class PeerExchange:
     self.flag_ptrs = arr(*[int(p) for p in fh.buffer_ptrs])
     self.launches = torch.zeros(self.MAX_CTAS, dtype=torch.int32, device=device)
     self.turn = 0
+    self.wait_cycles = 0           # 0: the library's default budget for the hand-shake
     torch.cuda.synchronize(device)
     dist.barrier(group=group)      # every rank's flags are zero before anyone raises one
 
@@ -84,12 +85,23 @@ class PeerExchange:
   def open(cls, group, rank, world, capacity, device):
     """Returns the exchange, or None where symmetric memory cannot be set up (the caller then
     keeps the NCCL all-reduce)."""
+    import torch.distributed as dist
+    import warnings
+    ex, why = None, None
     try:
-      return cls(group, rank, world, capacity, device)
+      ex = cls(group, rank, world, capacity, device)
     except Exception as e:   # noqa: BLE001 -- any failure here means: no peer path
-      import warnings
-      warnings.warn(f'peer-memory exchange unavailable, using NCCL all-reduce: {e!r}')
+      why = repr(e)
+    # The ranks must agree on the path: one rank on NCCL while the others spin in the peer
+    # hand-shake would stall all of them.  Every rank reaches this reduction.
+    ok = torch.tensor([1 if ex is not None else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if int(ok.item()) == 0:
+      if ex is not None:
+        why = 'another rank could not set it up'
+      warnings.warn(f'peer-memory exchange unavailable, using NCCL all-reduce: {why}')
       return None
+    return ex
 
   def publish(self, y: torch.Tensor) -> 'PeerPartial':
     """Copies this rank's partial output into the buffer whose turn it is."""
@@ -148,7 +160,7 @@ class AddRmsNorm(LazyAct):
           _lib.ptr(self.x), ex.partial_ptrs[self.peer.which], ex.flag_ptrs, ex.world, ex.rank,
           _lib.ptr(ex.launches), ex.MAX_CTAS, _lib.ptr(self.weight), self.eps, rows, d,
           _lib.ptr(x_out), _lib.ptr(y), _lib.ptr(q), _lib.ptr(scale),
-          _lib.ptr(_lib.error_flag(self.device)), _lib.stream_ptr(self.device)),
+          _lib.ptr(_lib.error_flag(self.device)), ex.wait_cycles, _lib.stream_ptr(self.device)),
           'add_rmsnorm_quantize_peer')
       self.residual = x_out
       return

@@ -10,7 +10,7 @@ from qwix_b200.core import pallas as _pallas
 from qwix_b200.core import qarray as _qarray
 
 __all__ = ['QArray', 'quantize', 'dequantize', 'get_current_rule', 'pallas_call', 'BlockSpec',
-           'dot_general', 'dot', 'einsum']
+           'program_id', 'num_programs', 'dot_general', 'dot', 'einsum']
 
 QArray = _qarray.QArray
 quantize = _qarray.quantize_api
@@ -19,6 +19,8 @@ dequantize = _qarray.dequantize
 get_current_rule = qconfig.get_current_rule
 pallas_call = _pallas.pallas_call
 BlockSpec = _pallas.BlockSpec
+program_id = _pallas.program_id
+num_programs = _pallas.num_programs
 
 # The reference binds these to its per-K-tile loop implementation; here that loop is inside
 # the GEMM kernel.

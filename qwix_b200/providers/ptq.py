@@ -163,6 +163,15 @@ def _plain(x):
   return qarray.dequantize(x) if isinstance(x, qarray.QArray) else x
 
 
+def calibration_from_quant_stat(quant_stat: Mapping[str, Any]) -> dict:
+  """averaging.py:67-98 (SimpleMovingAverage.get_calibration without a default): every
+  `sum_of_<key>` divided by `count`, in the float32 the sums are kept in."""
+  count = quant_stat['count']
+  if int(count) == 0:
+    raise ValueError('quant_stats is not initialized.')
+  return {k[len('sum_of_'):]: v / count for k, v in quant_stat.items() if k.startswith('sum_of_')}
+
+
 def quantize_act(array: torch.Tensor, how: qarray.HowToQuantize,
                  rule: qconfig.QuantizationRule, act_name: str, *,
                  _qarray_module=qarray) -> qarray.QArray:
@@ -179,10 +188,17 @@ def quantize_act(array: torch.Tensor, how: qarray.HowToQuantize,
   scale_name, zp_name = act_name + '_scale', act_name + '_zero_point'
   box = getattr(module, scale_name, None) if module is not None else None
   if box is None:
-    calibration = _qarray_module.calibrate(array, how)
-    axes = [a for a in rule.act_batch_axes if a < array.ndim]
-    calibration = {k: v.float().mean(dim=axes, keepdim=True).to(v.dtype)
-                   for k, v in calibration.items()}
+    # Statistics gathered by a calibration or QAT run, kept on the module as
+    # `quant_stats[act_name]`, are used once and removed (boxed_param.py:428-434).
+    stats = getattr(module, 'quant_stats', None) if module is not None else None
+    quant_stat = stats.pop(act_name, None) if isinstance(stats, dict) else None
+    if quant_stat is not None:
+      calibration = calibration_from_quant_stat(quant_stat)
+    else:
+      calibration = _qarray_module.calibrate(array, how)
+      axes = [a for a in rule.act_batch_axes if a < array.ndim]
+      calibration = {k: v.float().mean(dim=axes, keepdim=True).to(v.dtype)
+                     for k, v in calibration.items()}
     scale, zp = _qarray_module.compute_scale_zero_point(calibration, how.qtype)
     box = WithAux(scale, how)
     if module is not None:
@@ -243,11 +259,14 @@ def quantize_params(params: Any, abstract_quantized_params: Any, quant_stats: An
 
   `abstract_quantized_params` is the param tree of the PTQ model (nested dict or the model
   itself); its WithAux leaves say how each weight is quantized and in which shape it is
-  used.  Leaves without a WithAux template pass through.  Static-range statistics
-  (`quant_stats`) belong to quantized training and are not built.
+  used.  Leaves without a WithAux template pass through.
+
+  `quant_stats` (static-range quantization, ptq.py:106-129): a nested dict whose leaves are
+  `{'count': n, 'sum_of_absmax': ...}` (or `sum_of_min` / `sum_of_max`) under the name of an
+  activation, e.g. `{'Dense_0': {'dot_general0_lhs': {...}}}`.  Each becomes the static
+  `<name>_scale` (and `<name>_zero_point`) of that activation; the qtype comes from the
+  `<name>_scale` WithAux of the abstract tree.
   """
-  if quant_stats:
-    raise NotImplementedError('quant_stats (static-range calibration from a QAT run) is not built.')
   out = {}
   for path, param in _flatten(params):
     if not isinstance(param, torch.Tensor):
@@ -261,4 +280,19 @@ def quantize_params(params: Any, abstract_quantized_params: Any, quant_stats: An
       param = param.reshape(template.shape)
       param = template.replace(array=_qarray_module.quantize(param, template.how))
     out[path] = param
+
+  stat_paths = {path[:-1] for path, _ in _flatten(quant_stats or {})}
+  for path in stat_paths:
+    quant_stat = _lookup(quant_stats, path)
+    if int(quant_stat['count']) == 0:
+      raise ValueError(f'quant_stats is not initialized for {path}.')
+    scale_path = (*path[:-1], path[-1] + '_scale')
+    abs_scale = _lookup(abstract_quantized_params, scale_path)
+    if not isinstance(abs_scale, WithAux):
+      raise ValueError(f'{scale_path} is not a static scale of the abstract_quantized_params.')
+    scale, zero_point = _qarray_module.compute_scale_zero_point(
+        calibration_from_quant_stat(quant_stat), abs_scale.how.qtype)
+    out[scale_path] = abs_scale.replace(array=scale)
+    if zero_point is not None:
+      out[(*path[:-1], path[-1] + '_zero_point')] = zero_point
   return _unflatten(out)

@@ -80,13 +80,19 @@ import qwix_b200 as qwix
 from qwix_b200 import decoder as D
 cfg = D.DecoderConfig.tiny()
 tokens = torch.randint(0, cfg.vocab, (2, 24), generator=torch.Generator().manual_seed(0)).cuda()
+from qwix_b200 import _lib
 def run(group, exact):
   m = D.Decoder(cfg, device="cuda", group=group, exact_act_scale=exact)
   m.quantize_weights()
   m.alloc_cache(2, 32)
+  if group is None and not exact:
+    # the default mode must really take the peer-memory path, not the NCCL fall-back
+    assert m.comm.exchange is not None, "peer exchange was not set up"
   q = qwix.quantize_model(m, qwix.PtqProvider(D.w8a8_rules()))
   with torch.no_grad():
-    return q(tokens, 0, 0, last_only=False)
+    out = q(tokens, 0, 0, last_only=False)
+  _lib.raise_on_device_error()     # no hand-shake between the ranks ran out
+  return out
 solo = dist.new_group([rank]) if False else None
 # TP=1 reference on every rank: a one-rank group
 groups = [dist.new_group([r]) for r in range(dist.get_world_size())]

@@ -103,3 +103,91 @@ def test_rope_cache_matches_unfused(tensor_pos):
   assert torch.equal(cv[:, :, pos:pos + T], vv)
   # nothing else in the cache was touched
   assert int(cache.count_nonzero()) == int(ck[:, :, pos:pos + T].count_nonzero() + cv[:, :, pos:pos + T].count_nonzero())
+
+
+# ---- the all-reduce folded into add + norm + quantize, on ONE GPU ------------------------------
+#
+# Both "ranks'" partial buffers and flag arrays live on this device.  Only rank 0's kernel is
+# launched; the flags its peer would have raised are written from the host beforehand, so no
+# kernel ever waits for another one.
+
+def _peer_setup(rows, d, world=2, max_ctas=148 * 8, seed=0):
+  import ctypes
+  g = torch.Generator(device='cuda').manual_seed(seed)
+  x = torch.randn((rows, d), device='cuda', generator=g).to(torch.bfloat16)
+  parts = [(0.5 * torch.randn((rows, d), device='cuda', generator=g)).to(torch.bfloat16)
+           for _ in range(world)]
+  w = (1 + 0.1 * torch.randn(d, device='cuda', generator=g)).to(torch.bfloat16)
+  flags = [torch.zeros(max_ctas * world, dtype=torch.int32, device='cuda') for _ in range(world)]
+  launches = torch.zeros(max_ctas, dtype=torch.int32, device='cuda')
+  arr = ctypes.c_void_p * world
+  return dict(x=x, parts=parts, w=w, flags=flags, launches=launches, max_ctas=max_ctas, world=world,
+              part_ptrs=arr(*[p.data_ptr() for p in parts]), flag_ptrs=arr(*[f.data_ptr() for f in flags]))
+
+
+def _peer_call(s, err, wait_cycles=0, quantize=True):
+  from qwix_b200 import _lib
+  rows, d = s['x'].shape
+  out = dict(x_out=torch.full_like(s['x'], 7.0),
+             q=torch.full((rows, d), 7, dtype=torch.int8, device='cuda') if quantize else None,
+             scale=torch.full((rows,), 7.0, dtype=torch.bfloat16, device='cuda') if quantize else None,
+             y=None if quantize else torch.full_like(s['x'], 7.0))
+  _lib.check(_lib.lib().qwx_add_rmsnorm_quantize_peer(
+      _lib.ptr(s['x']), s['part_ptrs'], s['flag_ptrs'], s['world'], 0, _lib.ptr(s['launches']),
+      s['max_ctas'], _lib.ptr(s['w']), 1e-5, rows, d, _lib.ptr(out['x_out']), _lib.ptr(out['y']),
+      _lib.ptr(out['q']), _lib.ptr(out['scale']), _lib.ptr(err), wait_cycles, _lib.stream_ptr()),
+      'add_rmsnorm_quantize_peer')
+  torch.cuda.synchronize()
+  return out
+
+
+@pytest.mark.parametrize('rows,d,world', [(32, 4096, 2), (3000, 1024, 2), (70, 4096, 4), (8192, 512, 8)])
+def test_peer_add_rmsnorm_equals_local_on_summed_partials(rows, d, world):
+  from qwix_b200 import _lib
+  s = _peer_setup(rows, d, world)
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  # what an all-reduce would deliver: the float32 sum in rank order, rounded once to bf16
+  total = s['parts'][0].float()
+  for p in s['parts'][1:]:
+    total = total + p.float()
+  delta = total.to(torch.bfloat16)
+  want = dict(x_out=torch.empty_like(s['x']), q=torch.empty((rows, d), dtype=torch.int8, device='cuda'),
+              scale=torch.empty((rows,), dtype=torch.bfloat16, device='cuda'))
+  _lib.check(_lib.lib().qwx_add_rmsnorm_quantize(
+      _lib.ptr(s['x']), _lib.ptr(delta), _lib.ptr(s['w']), 1e-5, rows, d, _lib.ptr(want['x_out']),
+      None, _lib.ptr(want['q']), _lib.ptr(want['scale']), _lib.stream_ptr()), 'add_rmsnorm_quantize')
+  for call in (1, 2):                       # the second call waits for launch count 2
+    s['flags'][0].fill_(call)               # "every peer has finished its GEMM `call` times"
+    got = _peer_call(s, err)
+    assert int(err.item()) == 0
+    assert torch.equal(got['x_out'], want['x_out'])
+    assert torch.equal(got['q'], want['q'])
+    assert torch.equal(got['scale'].view(torch.int16), want['scale'].view(torch.int16))
+    # rank 0 told every peer, in that peer's flag array, that its own partial is complete
+    ctas = int((s['launches'] == call).sum().item())
+    assert 0 < ctas <= min(rows, s['max_ctas'])
+    for r in range(1, world):
+      mine = s['flags'][r].view(-1, world)[:, 0]
+      assert int((mine == call).sum().item()) == ctas
+
+
+def test_peer_wait_runs_out_and_reports():
+  """The peer never raises its flags: the bounded hand-shake gives up after its budget, the
+  call reports QWX_ERR_DEVICE_WAIT, writes nothing, and the context stays usable."""
+  from qwix_b200 import _lib
+  s = _peer_setup(64, 2048)
+  err = _lib.error_flag(torch.device('cuda'))
+  assert int(err.item()) == 0
+  got = _peer_call(s, err, wait_cycles=2_000_000)        # about a millisecond
+  assert int(err.item()) == 8                             # QWX_ERR_DEVICE_WAIT
+  assert bool((got['x_out'] == 7.0).all()) and bool((got['q'] == 7).all())
+  assert bool((got['scale'] == 7.0).all())
+  with pytest.raises(RuntimeError, match='wait ran out'):
+    _lib.raise_on_device_error()
+  _lib.clear_device_error()
+  _lib.raise_on_device_error()                            # cleared: no longer raises
+  # a healthy call afterwards (launch counts went on to 1, so the peer's flags say 2 next)
+  s['flags'][0].fill_(2)
+  got = _peer_call(s, err)
+  assert int(err.item()) == 0
+  assert not bool((got['q'] == 7).all())

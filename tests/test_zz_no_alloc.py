@@ -78,3 +78,19 @@ def test_noalloc_entry_refuses_views_beyond_its_scratch():
   assert rc == 6  # QWX_ERR_WORKSPACE
   with pytest.raises(RuntimeError, match='workspace'):
     _lib.check(rc, 'quantize_noalloc')
+
+
+def test_noalloc_entry_never_refuses_row_segment_views():
+  """Per-token scales of 70,000 rows: 70,000 tiles would not fit the built-in array, but tiles
+  that are row segments are quantized in one pass without scratch, so the call must go through
+  and equal qwx_quantize bit for bit (the shape of a long prefill in a warm serving loop)."""
+  L = _lib.lib()
+  R, C = 70000, 64
+  g = torch.Generator(device='cpu').manual_seed(11)
+  x = torch.randn(R, C, generator=g).to(torch.bfloat16).cuda()
+  assert L.qwx_quantize_workspace_bytes(1, R, C, 1, 1, C) > L.qwx_quantize_builtin_scratch_bytes()
+  ws = torch.empty(1, dtype=torch.uint8, device='cuda')   # the one-pass path ignores it
+  want = _quantize('workspace', x, (1, C), _lib.ABSMAX, _lib.S8, workspace=ws)
+  got = _quantize('noalloc', x, (1, C), _lib.ABSMAX, _lib.S8)
+  assert torch.equal(got[0], want[0])
+  assert torch.equal(got[1].view(torch.int16), want[1].view(torch.int16))
