@@ -1,24 +1,49 @@
-"""Benchmark of the w8a8 quantized dot_general hot path (BASELINE.json configs[1]).
-
-One step = what PtqProvider.dot_general does for one Dense layer at inference time:
-  quantize the bf16 activations A[4096, 8192] per token to int8 (absmax), then
-  int8 x int8 -> int32 GEMM against the pre-quantized weight W[8192, 8192] (int8, one
-  scale per output channel) with both scales applied in the epilogue, bf16 output.
+"""Benchmark of the quantized-inference hot path.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Under torchrun every rank runs the same step on its own token shard (weak scaling, no
-collective on the data path).  Rank 0 prints one JSON line.
+Rank 0 prints ONE JSON line.  Its headline fields (`metric`, `value`, `roofline`, `e2e`,
+`cpu_baseline`) are the w8a8 dot_general step, prefill-shaped -- what PtqProvider.dot_general
+does for one Dense layer at inference time:
+
+  quantize the bf16 activations A[4096, 8192] per token to int8 (absmax), then the
+  int8 x int8 -> int32 GEMM against the pre-quantized weight W[8192, 8192] (int8, one scale
+  per output channel) with both scales applied in the epilogue, bf16 output.
+
+Under torchrun every rank runs that step on its own token shard (weak scaling, no collective
+on the data path).  The same line carries one record per further workload:
+
+  "decoder"   Llama-3-8B-shaped w8a8 decoder, 32 x 2048-token prefill + 128 greedy steps,
+              tensor-parallel over the launched ranks (strong scaling): every N
+  "w4"        int4 weight-only GEMM, W[8192, 28672] with 128-wide scale tiles, 1/16/128 tokens: N = 1
+  "hadamard"  128-point Hadamard rotation + e4m3 quantization + fp8 GEMM [8192,4096]x[4096,14336]: N = 1
+
+each with its own roofline, end-to-end (host buffers) figure, a check of the timed output
+against the CPU oracle, and (N = 1) the CPU oracle timed on a bounded sample.
 """
 
 from __future__ import annotations
 
-import argparse
-import json
 import os
+import sys
+
+
+def _claim_host_threads():
+  """The CPU arm uses every host core: torchrun exports OMP_NUM_THREADS=1, which would leave
+  the BLAS behind NumPy single-threaded.  Must run before NumPy is imported."""
+  n = str(os.cpu_count() or 1)
+  for key in ('OMP_NUM_THREADS', 'OPENBLAS_NUM_THREADS', 'MKL_NUM_THREADS'):
+    os.environ[key] = n
+
+
+if any('reference' in a for a in sys.argv[1:]) or 'WORLD_SIZE' not in os.environ:
+  _claim_host_threads()
+
+import argparse
+import hashlib
+import json
 import statistics
 import subprocess
-import sys
 import threading
 import time
 
@@ -31,10 +56,34 @@ if ROOT not in sys.path:
 
 M, K, N = 4096, 8192, 8192
 OPS_PER_STEP = 2 * M * N * K
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_q8_pair_kernel launch at this size,
-# from the ncu capture summarised in profiles/gemm_q8_pair_w8a8_prefill.md (mean of two launches).
-GEMM_DRAM_TRAFFIC_BYTES = 159_363_000
 NSETS = 3  # buffer sets cycled through so that no step finds its inputs in the 126 MB L2
+DN = (((1,), (0,)), ((), ()))
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of the named kernel
+# (the summaries under profiles/ give the commands).  A figure is reported only while the
+# kernel's source is the one that was profiled (sha1 of the listed files, first 12 hex digits).
+NCU_DRAM_TRAFFIC = {
+    'gemm_q8_pair_kernel<i8>': {
+        'bytes_per_launch': 159_363_000, 'shape': [4096, 8192, 8192],
+        'sources': ['qwix_b200/csrc/gemm_q8_pair.cu'], 'sha1': '371052c7a394'},
+}
+
+
+def _source_tag(files) -> str:
+  h = hashlib.sha1()
+  for f in files:
+    with open(os.path.join(ROOT, f), 'rb') as fh:
+      h.update(fh.read())
+  return h.hexdigest()[:12]
+
+
+def measured_traffic(kernel: str):
+  rec = NCU_DRAM_TRAFFIC.get(kernel)
+  if rec is None:
+    return None, 'no ncu capture of this kernel'
+  if _source_tag(rec['sources']) != rec['sha1']:
+    return None, 'kernel source changed since its ncu capture'
+  return rec['bytes_per_launch'], 'ncu dram__bytes_read.sum + dram__bytes_write.sum per launch'
 
 
 def _peaks():
@@ -74,8 +123,7 @@ class ClockSampler:
       self.rows.append([c.strip() for c in line.split(',')])
 
   def wait_first(self, timeout_s: float = 4.0):
-    """Blocks until nvidia-smi has printed its first row (its start-up takes longer than a
-    short timed region)."""
+    """Blocks until nvidia-smi has printed its first row (its start-up takes a while)."""
     t0 = time.time()
     while self.proc is not None and not self.rows and time.time() - t0 < timeout_s:
       time.sleep(0.02)
@@ -83,7 +131,7 @@ class ClockSampler:
   def mark(self) -> int:
     return len(self.rows)
 
-  def stop(self, first: int = 0) -> dict:
+  def stop(self, first: int = 0, last: int | None = None) -> dict:
     if self.proc is None:
       return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
     self.proc.terminate()
@@ -94,7 +142,7 @@ class ClockSampler:
     self.thread.join(timeout=2)
     sm, mx, reasons = [], [], set()
     names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
-    for r in self.rows[first:]:
+    for r in self.rows[first:last]:
       if len(r) < 6:
         continue
       try:
@@ -107,7 +155,7 @@ class ClockSampler:
           reasons.add(n)
     return {'sm_mhz': statistics.median(sm) if sm else None,
             'sm_max_mhz': max(mx) if mx else None, 'reasons': sorted(reasons),
-            'samples': len(sm)}
+            'samples': len(sm), 'sm_mhz_min': min(sm) if sm else None}
 
 
 def token_shard(rank: int, world: int, tokens_per_rank: int):
@@ -129,8 +177,8 @@ def whole_job_tops(ms_per_step: float, world: int) -> float:
   return world * OPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
 
 
-def _inputs(seed_base: int, device):
-  """BASELINE configs[1]: A ~ N(0,1) with 1% of the K columns scaled x20, W ~ N(0, 0.02)."""
+def _inputs(seed_base: int):
+  """A ~ N(0,1) with a seeded 1 % of the K columns scaled x20, W ~ N(0, 0.02), bf16."""
   sets = []
   for s in range(NSETS):
     g = torch.Generator(device='cpu').manual_seed(seed_base + s)
@@ -142,68 +190,48 @@ def _inputs(seed_base: int, device):
   return sets
 
 
-# ---------------------------------------------------------------------------------------------
-# CPU arm: the oracle's restatement of the reference path, timed on the host cores.
-# ---------------------------------------------------------------------------------------------
-
-def cpu_step_factory(rows: int):
-  """Returns (fn, ops): one w8a8 step on `rows` of the workload's tokens, full K and N."""
+def _np(t: torch.Tensor):
   import ml_dtypes
-  from oracle import dot_general as odg
-  from oracle import qarray as oq
-  rng = np.random.default_rng(0)
-  a = rng.standard_normal((rows, K)).astype(np.float32)
-  a[:, rng.choice(K, K // 100, replace=False)] *= 20.0
-  a = a.astype(ml_dtypes.bfloat16)
-  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32).astype(ml_dtypes.bfloat16)
-  dn = (((1,), (0,)), ((), ()))
-  kw = dict(dimension_numbers=dn, ndims=(2, 2), tile_size=None, qtype='int8')
-  wq = oq.quantize(w, odg.get_how_to_quantize(for_lhs=False, **kw))  # offline, untimed
-  how_a = odg.get_how_to_quantize(for_lhs=True, **kw)
-
-  def step():
-    return odg.dot_general(oq.quantize(a, how_a), wq, dn)
-
-  return step, 2 * rows * N * K
+  t = t.detach().cpu().contiguous()
+  if t.dtype == torch.bfloat16:
+    return t.view(torch.int16).numpy().view(ml_dtypes.bfloat16)
+  if t.dtype == torch.float8_e4m3fn:
+    return t.view(torch.uint8).numpy().view(ml_dtypes.float8_e4m3fn)
+  return t.numpy()
 
 
-def run_cpu(steps: int, warmup: int, rows: int):
-  threads = os.cpu_count() or 1
-  torch.set_num_threads(threads)
-  step, ops = cpu_step_factory(rows)
-  for _ in range(warmup):
-    step()
-  t0 = time.perf_counter()
-  for _ in range(steps):
-    step()
-  dt = (time.perf_counter() - t0) / steps
-  return ops / dt / 1e12, dt, threads
+def _tolerance_report(got: np.ndarray, want: np.ndarray) -> dict:
+  g, w = got.astype(np.float32), want.astype(np.float32)
+  err = np.abs(g - w)
+  return {'max_abs': float(err.max()),
+          'within_1e-2_abs_or_2e-2_rel': bool(np.all(err <= 1e-2 + 2e-2 * np.abs(w))),
+          'rel_l2': float(np.linalg.norm(g - w) / max(np.linalg.norm(w), 1e-30))}
 
 
-def reference_arm(args, rank: int):
-  if rank != 0:
-    return
-  rows = 256
-  tops, dt, threads = run_cpu(max(1, args.steps), max(1, args.warmup), rows)
-  line = {
-      'impl': 'reference', 'metric': 'quantized GEMM TOPS', 'value': tops, 'unit': 'TOPS',
-      'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
-      'ms_per_step': dt * 1e3, 'higher_is_better': True, 'scaling': 'weak',
-      'vs_baseline': None, 'dtype': 'int8', 'data': 'synthetic',
-      'config': {'workload': 'w8a8 dot_general prefill, BASELINE configs[1]', 'M': M, 'N': N,
-                 'K': K, 'sample': f'{rows} of {M} token rows per step, full K and N'},
-      'cpu_baseline': {'value': tops, 'unit': 'TOPS', 'cores': threads, 'kind': 'port',
-                       'sample': f'{rows} of {M} token rows per step (NumPy/ml_dtypes oracle; '
-                                 'the reference needs jax, which is not installed)'},
-      'e2e': {'value': tops, 'unit': 'TOPS', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
-      'gpu_launches': 0,
-  }
-  print(json.dumps(line), flush=True)
+def _host_threads() -> int:
+  n = os.cpu_count() or 1
+  torch.set_num_threads(n)
+  try:
+    import threadpoolctl
+    threadpoolctl.threadpool_limits(limits=n)
+  except Exception:  # noqa: BLE001 -- the environment variables above already asked for it
+    pass
+  return n
 
 
-# ---------------------------------------------------------------------------------------------
-# BASELINE configs[4]: Llama-3-8B-shaped w8a8 decoder, tensor-parallel over the ranks
-# ---------------------------------------------------------------------------------------------
+def _timed_cpu(fn, budget_s: float = 6.0, max_runs: int = 3):
+  """Median wall time of fn() over up to max_runs runs (after one warm-up) within a budget."""
+  fn()
+  times = []
+  t_all = time.perf_counter()
+  for _ in range(max_runs):
+    t0 = time.perf_counter()
+    fn()
+    times.append(time.perf_counter() - t0)
+    if time.perf_counter() - t_all > budget_s:
+      break
+  return statistics.median(times), len(times)
+
 
 def _time_calls(fn, steps, warmup):
   for i in range(warmup):
@@ -218,84 +246,307 @@ def _time_calls(fn, steps, warmup):
   return e0.elapsed_time(e1) / steps
 
 
-def w4_workload(args):
-  """BASELINE configs[2]: int4 weight-only decode GEMM, W [8192, 28672] with 128-wide scale
-  tiles, bf16 activations of 1 / 16 / 128 tokens (--m).  One extra bench line, HBM-bound."""
+# ---------------------------------------------------------------------------------------------
+# Library ceilings measured in this run: the vendor GEMMs the roofline is stated against
+# ---------------------------------------------------------------------------------------------
+
+def library_peaks(device, sustain_s: float = 4.0) -> dict:
+  """torch._int_mm (int8) and torch._scaled_mm (e4m3) at 8192^3, best of 10 (burst) and back
+  to back for `sustain_s` seconds under the power cap (sustained), in TOP/s."""
+  n = 8192
+  ops = 2.0 * n * n * n
+  out = {}
+
+  def run(tag, fn):
+    try:
+      for _ in range(3):
+        fn()
+      best = None
+      for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        best = ms if best is None else min(best, ms)
+      out[tag + '_burst'] = ops / (best * 1e-3) / 1e12
+      if sustain_s > 0:
+        reps = max(10, int(sustain_s * 1e3 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+          fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[tag + '_sustained'] = ops * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    except Exception as e:  # noqa: BLE001 -- the library figure is context, not a requirement
+      out[tag + '_error'] = repr(e)[:200]
+
+  a8 = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device)
+  b8 = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device).t()   # column-major
+  run('int8', lambda: torch._int_mm(a8, b8))
+  del a8, b8
+  af = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+  bf = torch.randn(n, n, device=device).to(torch.float8_e4m3fn).t()
+  one = torch.ones((), device=device)
+  run('fp8', lambda: torch._scaled_mm(af, bf, scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+  out['how'] = (f'torch._int_mm / torch._scaled_mm at 8192^3: best of 10 (burst), back to back for '
+                f'{sustain_s:g} s (sustained)')
+  return out
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference path, timed on the host cores
+# ---------------------------------------------------------------------------------------------
+
+def cpu_step_factory(rows: int):
+  """Returns (fn, ops): one w8a8 step on `rows` of the workload's tokens, full K and N."""
+  import ml_dtypes
+  from oracle import dot_general as odg
+  from oracle import qarray as oq
+  rng = np.random.default_rng(0)
+  a = rng.standard_normal((rows, K)).astype(np.float32)
+  a[:, rng.choice(K, K // 100, replace=False)] *= 20.0
+  a = a.astype(ml_dtypes.bfloat16)
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32).astype(ml_dtypes.bfloat16)
+  kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=None, qtype='int8')
+  wq = oq.quantize(w, odg.get_how_to_quantize(for_lhs=False, **kw))  # offline, untimed
+  how_a = odg.get_how_to_quantize(for_lhs=True, **kw)
+
+  def step():
+    return odg.dot_general(oq.quantize(a, how_a), wq, DN)
+
+  return step, 2 * rows * N * K
+
+
+def run_cpu(steps: int, warmup: int, rows: int):
+  threads = _host_threads()
+  step, ops = cpu_step_factory(rows)
+  for _ in range(warmup):
+    step()
+  t0 = time.perf_counter()
+  for _ in range(steps):
+    step()
+  dt = (time.perf_counter() - t0) / steps
+  return ops / dt / 1e12, dt, threads
+
+
+def reference_arm(args, rank: int):
+  """The reference's path on the host cores: its NumPy restatement (the reference itself is
+  Python on JAX, which is not installed), all host threads, a bounded sample per step."""
+  if rank != 0:
+    return
+  rows = 256
+  tops, dt, threads = run_cpu(max(1, min(args.steps, 10)), max(1, min(args.warmup, 2)), rows)
+  line = {
+      'impl': 'reference', 'metric': 'quantized GEMM TOPS', 'value': tops, 'unit': 'TOPS',
+      'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
+      'ms_per_step': dt * 1e3, 'higher_is_better': True, 'scaling': 'weak',
+      'vs_baseline': None, 'dtype': 'int8', 'data': 'synthetic',
+      'config': {'workload': 'w8a8 dot_general, prefill-shaped: per-token int8 absmax quantize of '
+                             'A + int8 GEMM with per-token/per-channel dequant',
+                 'M': M, 'N': N, 'K': K,
+                 'sample': f'{rows} of {M} token rows per step, full K and N'},
+      'cpu_baseline': {'value': tops, 'unit': 'TOPS', 'cores': threads, 'kind': 'port',
+                       'sample': f'{rows} of {M} token rows per step (NumPy/ml_dtypes oracle; '
+                                 'the reference needs jax, which is not installed)'},
+      'e2e': {'value': tops, 'unit': 'TOPS', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+      'gpu_launches': 0,
+  }
+  print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# int4 weight-only GEMM (decode-shaped): W [8192, 28672], 128-wide scale tiles along K
+# ---------------------------------------------------------------------------------------------
+
+def w4_records(args, device, with_cpu: bool):
   from qwix_b200 import _lib
-  from qwix_b200.core import qarray as bq, weight_only
-  torch.cuda.set_device(0)
-  Kw, Nw, Mw = 8192, 28672, args.m or 16
+  from qwix_b200.core import dot_general as bdg
+  from qwix_b200.core import qarray as bq
+  from qwix_b200.core import weight_only
+  Kw, Nw = 8192, 28672
   L = _lib.lib()
+  peaks = _peaks()
   sets = []
   for i in range(3):   # 3 x 125 MB of weights cycled: no step finds its weight in L2
-    w = torch.randn(Kw, Nw, device='cuda', dtype=torch.bfloat16, generator=torch.Generator('cuda').manual_seed(3 + i)) * 0.02
+    w = torch.randn(Kw, Nw, device=device, dtype=torch.bfloat16,
+                    generator=torch.Generator(device).manual_seed(3 + i)) * 0.02
+    if i == 0:
+      w0_host = w.cpu()
     wq = bq.quantize_api(w, 'int4', channelwise_axes=[1], tiled_axes={0: 128}, scale_dtype=torch.float32)
     weight_only.prepare(wq)
     sets.append(wq)
     del w
-  a = torch.randn(Mw, Kw, device='cuda', dtype=torch.bfloat16, generator=torch.Generator('cuda').manual_seed(4))
-  out = torch.empty(Mw, Nw, device='cuda', dtype=torch.bfloat16)
-  ws = torch.zeros(L.qwx_gemm_a16w4_workspace_bytes(Mw, Nw), dtype=torch.uint8, device='cuda')
-  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  err = _lib.error_flag(device)
+  steps = max(20, min(args.steps, 100))
+  records = []
+  cols = np.unique(np.concatenate([np.arange(0, Nw, 112), [Nw - 1]]))       # sample for the checks
+  cpu = None
+  for Mw in ([args.m] if args.m else [1, 16, 128]):
+    a = torch.randn(Mw, Kw, device=device, dtype=torch.bfloat16,
+                    generator=torch.Generator(device).manual_seed(4))
+    out = torch.empty(Mw, Nw, device=device, dtype=torch.bfloat16)
+    ws = torch.zeros(L.qwx_gemm_a16w4_workspace_bytes(Mw, Nw), dtype=torch.uint8, device=device)
+    fused_path = weight_only.eligible(a, sets[0], DN)
 
-  from qwix_b200.core import dot_general as bdg
-  dn = (((1,), (0,)), ((), ()))
-  fused_path = weight_only.eligible(a, sets[0], dn)
+    def call(i):
+      wq = sets[i % len(sets)]
+      if not fused_path:
+        return bdg.dot_general(a, wq, DN, preferred_element_type=torch.bfloat16)
+      _lib.check(L.qwx_gemm_a16w4(_lib.ptr(a), _lib.ptr(wq._w4_packed), _lib.ptr(wq._w4_scale), _lib.F32,
+                                  Mw, Nw, Kw, 128, _lib.ptr(out), _lib.BF16, _lib.ptr(ws), ws.numel(), 1,
+                                  _lib.ptr(err), _lib.stream_ptr(device)), 'gemm_a16w4')
+    ms = _time_calls(call, steps, max(args.warmup, 3))
+    nbytes = Kw * Nw // 2 + (Kw // 128) * Nw * 4 + Mw * Kw * 2 + Mw * Nw * 2
+
+    # end to end through the public dot_general: activations from pinned host memory, result back
+    a_pin = a.cpu().pin_memory()
+    o_pin = torch.empty((Mw, Nw), dtype=torch.bfloat16).pin_memory()
+
+    def e2e(i):
+      x = a_pin.to(device, non_blocking=True)
+      o_pin.copy_(bdg.dot_general(x, sets[i % len(sets)], DN, preferred_element_type=torch.bfloat16),
+                  non_blocking=True)
+    e2e_ms = _time_calls(e2e, max(10, steps // 2), 3)
+
+    # the timed kernel's last output against the oracle on a sample of columns
+    call(0)
+    torch.cuda.synchronize()
+    from oracle import dot_general as odg
+    from oracle import qarray as oq
+    import ml_dtypes
+    w_o = oq.quantize_api(_np(w0_host[:, cols]), 'int4', channelwise_axes=[1], tiled_axes={0: 128},
+                          scale_dtype=np.float32)
+    want = odg.dot_general(_np(a), w_o, DN, preferred_element_type=ml_dtypes.bfloat16)
+    ci = torch.as_tensor(cols, device=device)
+    got_codes = _np(sets[0].qvalue[:, ci])
+    verified = _tolerance_report(_np((out if fused_path else call(0))[:, ci]), want)
+    verified.update({'columns': int(cols.size), 'tokens': Mw,
+                     'codes_bit_exact': bool(np.array_equal(got_codes, w_o.qvalue.astype(np.int8)))})
+    rec = {
+        'M': Mw, 'K': Kw, 'N': Nw, 'scale_tile': 128, 'ms_per_step': ms, 'steps': steps,
+        'value': nbytes / ms / 1e6, 'unit': 'GB/s',
+        'l2': '3 weight sets (375 MB) cycled',
+        'roofline': {'bound': 'hbm', 'achieved': nbytes / ms / 1e6, 'peak': peaks['hbm_gbs'],
+                     'unit': 'GB/s', 'frac': nbytes / ms / 1e6 / peaks['hbm_gbs'], 'traffic': None,
+                     'algorithmic_bytes': nbytes,
+                     'kernel': 'gemm_w4_kernel' if fused_path else 'dequantize_kernel + library bf16 GEMM',
+                     'peak_source': f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})"},
+        'e2e': {'value': nbytes / e2e_ms / 1e6, 'unit': 'GB/s', 'ms_per_step': e2e_ms,
+                'h2d_bytes_per_step': Mw * Kw * 2, 'd2h_bytes_per_step': Mw * Nw * 2},
+        'verified': verified, 'gpu_launches': steps,
+    }
+    if with_cpu:
+      if cpu is None:
+        # the reference's weight-only path on the host: dequantize, then a floating-point dot
+        # (dot_general.py:264-275), on a column sample of the weight
+        threads = _host_threads()
+        sample_cols = 1024
+        w_s = oq.quantize_api(_np(w0_host[:, :sample_cols]), 'int4', channelwise_axes=[1],
+                              tiled_axes={0: 128}, scale_dtype=np.float32)
+        cpu = (threads, sample_cols, w_s)
+      threads, sample_cols, w_s = cpu
+      a_np = _np(a)
+      dt, runs = _timed_cpu(lambda: odg.dot_general(a_np, w_s, DN, preferred_element_type=ml_dtypes.bfloat16),
+                            budget_s=4.0)
+      sample_bytes = Kw * sample_cols // 2 + (Kw // 128) * sample_cols * 4 + Mw * Kw * 2 + Mw * sample_cols * 2
+      rec['cpu_baseline'] = {'value': sample_bytes / dt / 1e9, 'unit': 'GB/s', 'cores': threads,
+                             'kind': 'port',
+                             'sample': f'{sample_cols} of {Nw} weight columns, {runs} timed runs '
+                                       f'({dt * 1e3:.0f} ms each): oracle dequantize + float dot'}
+    records.append(rec)
+  return records
+
+
+# ---------------------------------------------------------------------------------------------
+# Hadamard-quantized fp8 matmul: A [8192, 4096] x W [4096, 14336], 128-point blocks along K
+# ---------------------------------------------------------------------------------------------
+
+def hadamard_record(args, device, with_cpu: bool, lib_peaks: dict):
+  from qwix_b200.contrib import hadamard as bhd
+  Mh, Kh, Nh = 8192, 4096, 14336
+  steps = max(10, min(args.steps, 50))
+  acts_host = [(0.5 * torch.distributions.StudentT(3.0).sample((Mh, Kh))).to(torch.bfloat16)
+               for _ in range(3)]
+  acts = [a.to(device) for a in acts_host]
+  w_host = (torch.randn(Kh, Nh, generator=torch.Generator().manual_seed(6)) * 0.02).to(torch.bfloat16)
+  wq = bhd.quantize_rotated_weight(w_host.to(device))
+  last = {}
 
   def call(i):
-    wq = sets[i % len(sets)]
-    if not fused_path:   # more tokens than the fused kernel serves: dequantize + library GEMM
-      return bdg.dot_general(a, wq, dn, preferred_element_type=torch.bfloat16)
-    _lib.check(L.qwx_gemm_a16w4(_lib.ptr(a), _lib.ptr(wq._w4_packed), _lib.ptr(wq._w4_scale), _lib.F32,
-                                Mw, Nw, Kw, 128, _lib.ptr(out), _lib.BF16, _lib.ptr(ws), ws.numel(), 1,
-                                _lib.ptr(err), _lib.stream_ptr()), 'gemm_a16w4')
-  ms = _time_calls(call, args.steps, max(args.warmup, 3))
-  nbytes = Kw * Nw // 2 + (Kw // 128) * Nw * 4 + Mw * Kw * 2 + Mw * Nw * 2
-  peaks = _peaks()
-  print(json.dumps({
-      'metric': 'int4 weight-only GEMM GB/s', 'value': nbytes / ms / 1e6, 'unit': 'GB/s', 'n_gpus': 1,
-      'steps': args.steps, 'ms_per_step': ms, 'higher_is_better': True, 'dtype': 'bf16 x int4',
-      'data': 'synthetic',
-      'config': {'workload': 'a16w4 decode GEMM, BASELINE configs[2]', 'M': Mw, 'K': Kw, 'N': Nw,
-                 'scale_tile': 128, 'l2': '3 weight sets (375 MB) cycled'},
-      'roofline': {'bound': 'hbm', 'achieved': nbytes / ms / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
-                   'frac': nbytes / ms / 1e6 / peaks['hbm_gbs'], 'traffic': None,
-                   'kernel': 'gemm_w4_kernel' if fused_path else 'dequantize_kernel + library bf16 GEMM',
-                   'peak_source': peaks['source']}}))
-
-
-def hadamard_workload(args):
-  """BASELINE configs[3]: A [8192, 4096] bf16 rotated by 128-point Hadamard blocks, quantized
-  to e4m3 per row, times the offline-rotated e4m3 weight [4096, 14336]."""
-  from qwix_b200.contrib import hadamard as bhd
-  torch.cuda.set_device(0)
-  Mh, Kh, Nh = 8192, 4096, 14336
-  acts = [(0.5 * torch.distributions.StudentT(3.0).sample((Mh, Kh))).to(torch.bfloat16).cuda()
-          for _ in range(3)]
-  w = (torch.randn(Kh, Nh, generator=torch.Generator().manual_seed(6)) * 0.02).to(torch.bfloat16).cuda()
-  wq = bhd.quantize_rotated_weight(w)
-  ms = _time_calls(lambda i: bhd.hadamard_quantize_multiply(acts[i % 3], wq), args.steps, max(args.warmup, 3))
-  ms_q = _time_calls(lambda i: bhd.hadamard_quantize(acts[i % 3]), args.steps, max(args.warmup, 3))
+    last['out'], last['i'] = bhd.hadamard_quantize_multiply(acts[i % 3], wq), i % 3
+  ms = _time_calls(call, steps, max(args.warmup, 3))
+  ms_q = _time_calls(lambda i: bhd.hadamard_quantize(acts[i % 3]), steps, max(args.warmup, 3))
   flops = 2.0 * Mh * Nh * Kh
   peaks = _peaks()
-  peak = 2 * peaks['bf16_burst']
-  print(json.dumps({
-      'metric': 'Hadamard-quantized fp8 GEMM TFLOP/s', 'value': flops / ms / 1e9, 'unit': 'TFLOP/s',
-      'n_gpus': 1, 'steps': args.steps, 'ms_per_step': ms, 'higher_is_better': True, 'dtype': 'e4m3',
-      'data': 'synthetic',
-      'config': {'workload': 'rotate + e4m3 quantize + GEMM, BASELINE configs[3]', 'M': Mh, 'K': Kh,
-                 'N': Nh, 'block': 128, 'l2': '3 activation sets (201 MB) cycled'},
+  peak = lib_peaks.get('fp8_burst') or 2 * peaks['bf16_burst']
+  peak_src = ('torch._scaled_mm e4m3 at 8192^3, best of 10, measured in this run'
+              if lib_peaks.get('fp8_burst') else '2 x bf16_tflops (burst) of MEASURED_PEAKS.json')
+
+  # end to end: activations from pinned host memory, bf16 result back to pinned host memory
+  a_pin = [a.pin_memory() for a in acts_host]
+  o_pin = torch.empty((Mh, Nh), dtype=torch.bfloat16).pin_memory()
+
+  def e2e(i):
+    o_pin.copy_(bhd.hadamard_quantize_multiply(a_pin[i % 3].to(device, non_blocking=True), wq),
+                non_blocking=True)
+  e2e_ms = _time_calls(e2e, 5, 2)
+
+  # the last timed output against the oracle on a sample of rows and columns
+  from oracle import hadamard as ohd
+  torch.cuda.synchronize()
+  rows = np.array([t * 256 + b * 64 + (5 * t + 11 * b) % 64 for t in range(32) for b in range(4)])
+  cols = np.random.default_rng(7).choice(Nh, 512, replace=False)
+  a_np, w_np = _np(acts_host[last['i']][rows]), _np(w_host[:, cols])
+  want, _, _ = ohd.hadamard_quantized_matmul(a_np, w_np)
+  got = _np(last['out'][torch.as_tensor(rows, device=device)][:, torch.as_tensor(cols, device=device)])
+  verified = _tolerance_report(got, want)
+  verified.update({'rows': int(rows.size), 'columns': int(cols.size),
+                   'rel_l2_within_1e-2': verified['rel_l2'] <= 1e-2})
+  rec = {
+      'M': Mh, 'K': Kh, 'N': Nh, 'block': 128, 'qtype': 'float8_e4m3fn', 'ms_per_step': ms, 'steps': steps,
+      'value': flops / ms / 1e9, 'unit': 'TFLOP/s', 'l2': '3 activation sets (201 MB) cycled',
       'roofline': {'bound': 'tensor', 'achieved': flops / ms / 1e9, 'peak': peak, 'unit': 'TFLOP/s',
                    'frac': flops / ms / 1e9 / peak, 'traffic': None,
                    'kernel': 'hadamard_quantize_blocks_kernel + gemm_q8_pair_kernel<f8f6f4>',
                    'rotate_quantize_ms': ms_q, 'rotate_quantize_gbs': Mh * Kh * 3 / ms_q / 1e6,
-                   'hbm_peak_gbs': peaks['hbm_gbs'],
-                   'peak_source': '2 x bf16_tflops (burst), ' + peaks['source']}}))
+                   'hbm_peak_gbs': peaks['hbm_gbs'], 'peak_source': peak_src,
+                   'peak_sustained': lib_peaks.get('fp8_sustained')},
+      'e2e': {'value': flops / e2e_ms / 1e9, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms,
+              'h2d_bytes_per_step': Mh * Kh * 2, 'd2h_bytes_per_step': Mh * Nh * 2},
+      'verified': verified, 'gpu_launches': 2 * steps,
+  }
+  if with_cpu:
+    threads = _host_threads()
+    from oracle import qarray as oq
+    srows, scols = 256, 2048
+    a_s, w_s = _np(acts_host[0][:srows]), _np(w_host[:, :scols])
+    wq_s = oq.quantize(ohd.rotate_rhs(w_s, 128), oq.HowToQuantize(qtype='float8_e4m3fn', channelwise_axes=[1]))
+    wf = wq_s.qvalue.astype(np.float32)   # offline half, untimed
+
+    def cpu_step():
+      aq = oq.quantize(ohd.rotate_lhs(a_s, 128), oq.HowToQuantize(qtype='float8_e4m3fn', channelwise_axes=[0]))
+      acc = aq.qvalue.astype(np.float32) @ wf
+      return (acc * aq.scale.astype(np.float32) * wq_s.scale.astype(np.float32)).astype(a_s.dtype)
+    dt, runs = _timed_cpu(cpu_step, budget_s=6.0)
+    rec['cpu_baseline'] = {'value': 2.0 * srows * scols * Kh / dt / 1e12, 'unit': 'TFLOP/s', 'cores': threads,
+                           'kind': 'port',
+                           'sample': f'{srows} of {Mh} rows x {scols} of {Nh} columns, {runs} timed runs '
+                                     f'({dt * 1e3:.0f} ms each): oracle rotate + e4m3 quantize + f32 GEMM'}
+  return rec
+
+
+# ---------------------------------------------------------------------------------------------
+# Llama-3-8B-shaped w8a8 decoder, tensor-parallel over the ranks
+# ---------------------------------------------------------------------------------------------
+
+GOLDEN_DECODER = os.path.join(ROOT, 'tests', 'golden', 'decoder_prefill_logits_sample.json')
+GOLDEN_STRIDE = 501   # every 501st vocabulary entry: 256 logits per sequence
 
 
 def _decoder_kernel_breakdown(ptq_model, tokens, batch, layers):
   """Device time per kernel of one eager decode step and of one prefill chunk (PyTorch
-  profiler); prints two tables.  For profiles/, not a timed result."""
+  profiler); prints two tables.  A profiling aid, not a timed result."""
   from torch.profiler import profile, ProfilerActivity
   dec = ptq_model.model
 
@@ -323,21 +574,45 @@ def _decoder_kernel_breakdown(ptq_model, tokens, batch, layers):
   table(prof, 1, f'one prefill chunk of 4 x {tokens.shape[1]} tokens')
 
 
-def decoder_workload(args):
-  """batch x prompt-token prefill plus `decode` greedy tokens per sequence; tokens/s of the
-  whole job.  Not the line the round-end driver reads (that is the GEMM workload)."""
+def _decoder_cpu_baseline(cfg):
+  """The oracle decoder on a cut-down of the same architecture (2 layers of the real widths,
+  one 64-token prompt, small vocabulary), timed on the host; tokens/s extrapolated to the
+  model's layer count.  Weights are random codes: the time does not depend on their values."""
   import dataclasses
-  rank = int(os.environ.get('RANK', '0'))
-  world = int(os.environ.get('WORLD_SIZE', '1'))
-  local_rank = int(os.environ.get('LOCAL_RANK', '0'))
-  torch.cuda.set_device(local_rank)
-  device = torch.device('cuda', local_rank)
-  dist = None
-  if world > 1:
-    import torch.distributed as dist
-    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
-    dist.init_process_group('nccl', device_id=device)
+  import ml_dtypes
+  from oracle import decoder as odec
+  from oracle import qarray as oq
+  threads = _host_threads()
+  cut = dataclasses.replace(cfg, layers=2, vocab=1024)
+  rng = np.random.default_rng(0)
+  hd = cut.head_dim
+
+  def qw(k, n):
+    return oq.QArray(rng.integers(-127, 128, (k, n), dtype=np.int8),
+                     np.full((1, n), 1e-3, ml_dtypes.bfloat16), None, 'int8')
+  weights = {'embed': rng.standard_normal((cut.vocab, cut.d_model), dtype=np.float32).astype(ml_dtypes.bfloat16),
+             'layers': [{'qkv': qw(cut.d_model, (cut.q_heads + 2 * cut.kv_heads) * hd),
+                         'o': qw(cut.q_heads * hd, cut.d_model),
+                         'gate_up': qw(cut.d_model, 2 * cut.ffn), 'down': qw(cut.ffn, cut.d_model)}
+                        for _ in range(cut.layers)],
+             'lm_head': qw(cut.d_model, cut.vocab)}
+  tokens = rng.integers(0, cut.vocab, (1, 64))
+  t0 = time.perf_counter()
+  odec.forward(cut, weights, tokens)
+  dt = time.perf_counter() - t0
+  per_token_layer = dt / (cut.layers * tokens.size)
+  return {'value': 1.0 / (per_token_layer * cfg.layers), 'unit': 'tokens/s', 'cores': threads,
+          'kind': 'port', 'extrapolated': True,
+          'sample': f'oracle decoder, {cut.layers} layers of the real widths, one 64-token prompt, '
+                    f'{dt:.1f} s; per-token-layer time x {cfg.layers} layers (prefill only, lm_head ignored)'}
+
+
+def decoder_record(args, dist, device, rank, world, lib_peaks, with_cpu: bool):
+  """batch x prompt-token prefill plus `decode` greedy tokens per sequence; tokens/s of the
+  whole job (strong scaling over the tensor-parallel ranks)."""
+  import dataclasses
   import qwix_b200 as qwix
+  from qwix_b200 import _lib
   from qwix_b200 import decoder as D
 
   cfg = dataclasses.replace(D.DecoderConfig.llama3_8b(), layers=args.layers)
@@ -345,7 +620,8 @@ def decoder_workload(args):
   model.quantize_weights()
   ptq_model = qwix.quantize_model(model, qwix.PtqProvider(D.w8a8_rules()))
   g = torch.Generator().manual_seed(0)
-  tokens = torch.randint(0, cfg.vocab, (args.batch, args.prompt), generator=g).to(device)
+  tokens_host = torch.randint(0, cfg.vocab, (args.batch, args.prompt), generator=g).pin_memory()
+  ids_host = torch.empty((args.batch, args.decode), dtype=torch.long).pin_memory()
   model.alloc_cache(args.batch, args.prompt + args.decode)
 
   def sync():
@@ -354,111 +630,114 @@ def decoder_workload(args):
     torch.cuda.synchronize()
 
   # warm-up: every kernel shape of the real run, and the one-time capture of the decode step
+  tokens = tokens_host.to(device)
   D.generate(ptq_model, tokens, steps=3, prefill_batch=4)
   if args.kernel_breakdown:
     _decoder_kernel_breakdown(ptq_model, tokens, args.batch, cfg.layers)
-    return
+    return None
   runs, phases = [], {}
-  for _ in range(max(1, min(args.steps, 3))):
+  for _ in range(max(1, min(args.decoder_runs, 3))):
     sync()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     e[0].record()
+    # end to end: the prompt ids come from pinned host memory, the generated ids go back to it
+    tokens = tokens_host.to(device, non_blocking=True)
     ids = D.generate(ptq_model, tokens, steps=args.decode, prefill_batch=4, timings=phases)
+    ids_host.copy_(ids, non_blocking=True)
     e[1].record()
     sync()
     runs.append(max_over_ranks(e[0].elapsed_time(e[1]), dist, device))
-  from qwix_b200 import _lib
   _lib.raise_on_device_error()   # no bounded wait inside a kernel ran out
   ms = min(runs)
   total_tokens = args.batch * (args.prompt + args.decode)
-  if rank == 0:
-    print(json.dumps({
-        'metric': 'w8a8 decoder tokens/s', 'value': total_tokens / (ms * 1e-3), 'unit': 'tokens/s',
-        'n_gpus': world, 'ms_total': ms, 'runs_ms': runs, 'phases_last_run_ms': phases,
-        'higher_is_better': True,
-        'scaling': 'strong', 'dtype': 'int8', 'data': 'synthetic',
-        'config': {'workload': 'Llama-3-8B-shaped w8a8 decoder, BASELINE configs[4]',
-                   'layers': cfg.layers, 'batch': args.batch, 'prompt': args.prompt,
-                   'decode': args.decode, 'parallelism': f'tp{world}',
-                   'act_scale': 'global row absmax' if args.exact_act_scale else 'per shard'},
-        'checksum': int(ids.sum().item()),
-    }), flush=True)
-  if dist is not None:
-    # Tearing an NCCL communicator down while CUDA graphs that contain its kernels are alive
-    # was seen to hang: drop the graphs, drain the device, meet the other ranks, then leave
-    # without the communicator's destructor.
-    model.__dict__.pop('_step_graphs', None)
-    torch.cuda.synchronize()
-    dist.barrier()
-    sys.stdout.flush()
-    os._exit(0)
+
+  # last-position prefill logits of the first chunk against the committed single-GPU sample
+  with torch.no_grad():
+    logits = ptq_model(tokens[:4], 0, 0)[:, -1].float()
+  sample = logits[:, ::GOLDEN_STRIDE].cpu().numpy()
+  verified = None
+  if args.write_golden and rank == 0 and world == 1:
+    with open(GOLDEN_DECODER, 'w') as f:
+      json.dump({'what': 'last-position prefill logits of sequences 0..3 at every '
+                         f'{GOLDEN_STRIDE}th vocabulary entry, w8a8 decoder on one GPU',
+                 'made_by': 'python bench.py --workload decoder --write-golden',
+                 'layers': cfg.layers, 'prompt': args.prompt, 'argmax': logits.argmax(-1).tolist(),
+                 'logits': [[round(float(v), 5) for v in row] for row in sample]}, f)
+  if os.path.exists(GOLDEN_DECODER):
+    with open(GOLDEN_DECODER) as f:
+      gold = json.load(f)
+    if gold['layers'] == cfg.layers and gold['prompt'] == args.prompt:
+      want = np.asarray(gold['logits'], np.float32)
+      rel = float(np.linalg.norm(sample - want) / np.linalg.norm(want))
+      bound = 1e-2 if world == 1 or args.exact_act_scale else 4e-2
+      verified = {'against': 'committed single-GPU logits sample', 'sequences': 4,
+                  'logits_per_sequence': int(want.shape[1]), 'rel_l2': rel, 'bound': bound,
+                  'within_bound': rel <= bound,
+                  'argmax_agree': int(sum(int(a == b) for a, b in zip(logits.argmax(-1).tolist(), gold['argmax'])))}
+
+  # roofline: prefill against the int8 tensor ceiling, the decode step against HBM
+  hd = cfg.head_dim
+  layer_params = cfg.d_model * (cfg.q_heads + 2 * cfg.kv_heads) * hd + cfg.q_heads * hd * cfg.d_model \
+      + 3 * cfg.d_model * cfg.ffn
+  prefill_ops = 2.0 * layer_params * cfg.layers * args.batch * args.prompt
+  weight_bytes = layer_params * cfg.layers + cfg.d_model * cfg.vocab
+  kv_per_pos = 2 * cfg.kv_heads * hd * 2 * cfg.layers
+  avg_len = args.prompt + (args.decode + 1) / 2.0
+  step_bytes = weight_bytes + kv_per_pos * args.batch * avg_len
+  peaks = _peaks()
+  int8_peak = lib_peaks.get('int8_burst') or 2 * peaks['bf16_burst']
+  prefill_ms, decode_ms = phases.get('prefill_ms'), phases.get('decode_ms')
+  rec = {
+      'tp': world, 'tokens_per_s': total_tokens / (ms * 1e-3), 'unit': 'tokens/s', 'ms_total': ms,
+      'runs_ms': runs, 'prefill_ms': prefill_ms, 'decode_ms': decode_ms,
+      'decode_ms_per_step': decode_ms / max(1, args.decode - 1) if decode_ms else None,
+      'scaling': 'strong', 'dtype': 'int8',
+      'config': {'workload': 'Llama-3-8B-shaped decoder under a w8a8 rule: int8 per-channel weights, '
+                             'per-token int8 activations on every projection',
+                 'layers': cfg.layers, 'batch': args.batch, 'prompt': args.prompt, 'decode': args.decode,
+                 'parallelism': f'tp{world}',
+                 'act_scale': 'global row absmax' if args.exact_act_scale else 'per shard',
+                 'reduce': ('peer-memory sum inside the add+norm kernel' if model.comm.exchange is not None
+                            else ('nccl all-reduce' if world > 1 else 'none'))},
+      'checksum': int(ids.sum().item()),
+      'e2e': {'value': total_tokens / (ms * 1e-3), 'unit': 'tokens/s',
+              'h2d_bytes_per_step': tokens_host.numel() * 8, 'd2h_bytes_per_step': ids_host.numel() * 8,
+              'note': 'the timed region of every run includes both copies'},
+      'roofline': {
+          'prefill': {'bound': 'tensor', 'achieved': prefill_ops / (prefill_ms * 1e-3) / 1e12 if prefill_ms else None,
+                      'peak': int8_peak * world, 'unit': 'TOP/s',
+                      'frac': prefill_ops / (prefill_ms * 1e-3) / 1e12 / (int8_peak * world) if prefill_ms else None,
+                      'algorithmic_ops': prefill_ops, 'note': 'projection GEMMs only (attention not counted)'},
+          'decode': {'bound': 'hbm', 'achieved': step_bytes * (args.decode - 1) / (decode_ms * 1e-3) / 1e9 if decode_ms else None,
+                     'peak': peaks['hbm_gbs'] * world, 'unit': 'GB/s',
+                     'frac': step_bytes * (args.decode - 1) / (decode_ms * 1e-3) / 1e9 / (peaks['hbm_gbs'] * world) if decode_ms else None,
+                     'algorithmic_bytes_per_step': step_bytes,
+                     'note': 'int8 weights once + bf16 KV cache up to the current position, summed over ranks'}},
+      'verified': verified,
+  }
+  if with_cpu:
+    rec['cpu_baseline'] = _decoder_cpu_baseline(cfg)
+  # Graphs that hold NCCL kernels must not outlive the communicator's users: drop them here.
+  model.__dict__.pop('_step_graphs', None)
+  del ptq_model, model
+  torch.cuda.empty_cache()
+  return rec
 
 
 # ---------------------------------------------------------------------------------------------
-# GPU arm
+# The headline workload: w8a8 dot_general, prefill-shaped
 # ---------------------------------------------------------------------------------------------
 
-def main():
-  ap = argparse.ArgumentParser()
-  ap.add_argument('--gpus', type=int, default=1)
-  ap.add_argument('--steps', type=int, default=200)
-  ap.add_argument('--warmup', type=int, default=20)
-  ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-  ap.add_argument('--no-cpu-baseline', action='store_true')
-  ap.add_argument('--m', type=int, default=None,
-                  help='token rows per step (profiling aid; the benchmark uses 4096)')
-  ap.add_argument('--workload', default='gemm', choices=['gemm', 'decoder', 'w4', 'hadamard'],
-                  help="'decoder': BASELINE configs[4], tensor-parallel over the launched ranks")
-  ap.add_argument('--layers', type=int, default=32)
-  ap.add_argument('--batch', type=int, default=32)
-  ap.add_argument('--prompt', type=int, default=2048)
-  ap.add_argument('--decode', type=int, default=128)
-  ap.add_argument('--exact-act-scale', action='store_true')
-  ap.add_argument('--kernel-breakdown', action='store_true',
-                  help='decoder workload: print device time per kernel of a decode step and a '
-                       'prefill chunk instead of timing the run')
-  args = ap.parse_args()
-  if args.workload == 'decoder':
-    return decoder_workload(args)
-  if args.workload == 'w4':
-    return w4_workload(args)
-  if args.workload == 'hadamard':
-    return hadamard_workload(args)
-  args.warmup = max(args.warmup, 3)
-  if args.m is not None:
-    global M, OPS_PER_STEP
-    M = args.m
-    OPS_PER_STEP = 2 * M * N * K
-
-  rank = int(os.environ.get('RANK', '0'))
-  world = int(os.environ.get('WORLD_SIZE', '1'))
-  local_rank = int(os.environ.get('LOCAL_RANK', '0'))
-
-  if args.impl == 'reference':
-    reference_arm(args, rank)
-    return
-
-  if not torch.cuda.is_available():
-    raise SystemExit('bench.py needs a CUDA device: the quantized path has no CPU fallback.')
-  torch.cuda.set_device(local_rank)
-  device = torch.device('cuda', local_rank)
-  dist = None
-  if world > 1:
-    import torch.distributed as dist
-    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
-    dist.init_process_group('nccl', device_id=device)
-
+def gemm_workload(args, dist, device, rank, world, local_rank, lib_peaks):
   from qwix_b200 import _lib
   from qwix_b200.core import dot_general as bdg
   from qwix_b200.core import qarray as bq
   import qwix_b200 as qwix
 
-  dn = (((1,), (0,)), ((), ()))
-  kw = dict(dimension_numbers=dn, ndims=(2, 2), tile_size=None, qtype='int8')
-  how_a = bdg.get_how_to_quantize(for_lhs=True, **kw)
+  kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=None, qtype='int8')
   how_w = bdg.get_how_to_quantize(for_lhs=False, **kw)
 
-  host_sets = _inputs(1000 * rank, device)
+  host_sets = _inputs(1000 * rank)
   dev = []
   for a_h, w_h in host_sets:
     a = a_h.to(device)
@@ -495,46 +774,64 @@ def main():
     torch.cuda.synchronize()
 
   # ---- device-resident throughput (`value`) + per-kernel durations for the roofline ----
+  # The block of `steps` steps is repeated back to back until at least a second lies between
+  # the first and the last event, so that the clocks settle under the power cap and nvidia-smi
+  # (100 ms sampling) sees the timed region itself; the reported step time is the median block.
   sampler = ClockSampler(local_rank)
   sampler.start()
   sampler.wait_first()
   for i in range(args.warmup):
     step(i)
   barrier()
-  ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
+  probe = _time_calls(step, min(args.steps, 10), 0)            # ms per step, to size the repeats
+  repeats = max(1, min(2000, int(np.ceil(1000.0 / (probe * args.steps)))))
+  nev = repeats * args.steps
+  ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * nev + 1)]
   barrier()
   mark0 = sampler.mark()
   ev[0].record()
-  for i in range(args.steps):
+  for i in range(nev):
     d = dev[i % NSETS]
     quantize_act(d)
-    ev[3 * i + 1].record()
+    ev[2 * i + 1].record()
     gemm(d)
-    ev[3 * i + 2].record()
-    ev[3 * i + 3].record()
+    ev[2 * i + 2].record()
   barrier()
   mark1 = sampler.mark()
-  # nvidia-smi samples every 100 ms and the timed region may be shorter than that: the same
-  # steps keep running, untimed, until a few samples under this load exist.
-  t_load = time.time()
-  i = args.steps
-  while sampler.mark() - mark0 < 6 and time.time() - t_load < 1.5:
-    for _ in range(50):
-      step(i)
-      i += 1
-    torch.cuda.synchronize()
-  clocks = sampler.stop(mark0)
-  clocks['samples_in_timed_region'] = mark1 - mark0
-  clocks['window'] = 'timed region plus an untimed continuation of the same steps (100 ms sampling)'
-  total_ms = ev[0].elapsed_time(ev[3 * args.steps])
-  quant_ms = sum(ev[3 * i].elapsed_time(ev[3 * i + 1]) for i in range(args.steps)) / args.steps
-  gemm_ms = sum(ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(args.steps)) / args.steps
+  time.sleep(0.12)   # let the sample that covers the end of the region arrive
+  clocks = sampler.stop(mark0, max(mark1, mark0 + 1))
+  clocks['window'] = f'the timed region ({repeats} blocks of {args.steps} steps), 100 ms sampling'
+  blocks = [ev[2 * b * args.steps].elapsed_time(ev[2 * (b + 1) * args.steps]) for b in range(repeats)]
+  quant = [ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(nev)]
+  gemms = [ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(nev)]
+  quant_ms, gemm_ms = statistics.median(quant), statistics.median(gemms)
   if int(err.item()) != 0:
     raise SystemExit(f'device-side wait ran out inside the GEMM (code {int(err.item())})')
-
-  total_ms = max_over_ranks(total_ms, dist, device)
-  ms_per_step = total_ms / args.steps
+  block_ms = max_over_ranks(statistics.median(blocks), dist, device)
+  first_block_ms = max_over_ranks(blocks[0], dist, device)
+  ms_per_step = block_ms / args.steps
   value = whole_job_tops(ms_per_step, world)
+  last_set = dev[(nev - 1) % NSETS]
+
+  # ---- the last timed step's output against the oracle on a sample of its token rows ----
+  verified = None
+  if rank == 0:
+    from oracle import dot_general as odg
+    from oracle import qarray as oq
+    rows = np.array([t * 256 + b * 64 + (7 * t + 13 * b) % 64 for t in range(16) for b in range(4)])
+    ri = torch.as_tensor(rows, device=device)
+    a_o = oq.quantize(_np(host_sets[(nev - 1) % NSETS][0][rows]), odg.get_how_to_quantize(for_lhs=True, **kw))
+    codes_ok = bool(np.array_equal(_np(last_set['aq'][ri]), a_o.qvalue)) and \
+        bool(np.array_equal(_np(last_set['sa'][ri]).view(np.uint16), a_o.scale.view(np.uint16)))
+    w_codes = _np(last_set['wq'].qvalue)
+    want_acc = (a_o.qvalue.astype(np.float64) @ w_codes.astype(np.float64)).astype(np.int64)
+    acc = bdg.dot_general(last_set['aq'], last_set['wq'].qvalue, DN)      # raw int32 accumulator
+    acc_ok = bool(np.array_equal(acc[ri].cpu().numpy().astype(np.int64), want_acc))
+    del acc
+    want = odg.dot_general(a_o, oq.QArray(w_codes, _np(last_set['wq'].scale), None, 'int8'), DN)
+    verified = _tolerance_report(_np(last_set['out'][ri]), want)
+    verified.update({'rows': int(rows.size), 'row_tiles_covered': 16, 'codes_bit_exact': codes_ok,
+                     'acc_bit_exact': acc_ok})
 
   # ---- end to end through the public plugin API, host buffers in, host buffers out ----
   provider_rule = qwix.QuantizationRule(module_path='.*', weight_qtype='int8', act_qtype='int8')
@@ -542,99 +839,96 @@ def main():
   pinned_in = [a_h.pin_memory() for a_h, _ in host_sets]
   pinned_out = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(NSETS)]
   boxed = [qwix.WithAux(d['wq'], how_w) for d in dev]
-
   # Each buffer set has its own stream, so the host->device copy of one step, the kernels of
   # another and the device->host copy of a third overlap (PCIe is full duplex); all of it is
   # inside the timed region.
   streams = [torch.cuda.Stream(device) for _ in range(NSETS)]
 
-  def e2e_step(i):
+  def e2e_step(i, compute=True):
     s = i % NSETS
     with torch.cuda.stream(streams[s]):
       x = pinned_in[s].to(device, non_blocking=True)
-      y = provider.dot_general(x, boxed[s], dn)
+      y = provider.dot_general(x, boxed[s], DN) if compute else dev[s]['out']
       pinned_out[s].copy_(y, non_blocking=True)
 
   def join_streams():
     for st in streams:
       torch.cuda.current_stream(device).wait_stream(st)
 
+  def timed_e2e(n, compute):
+    for st in streams:
+      st.wait_stream(torch.cuda.current_stream(device))
+    for i in range(3):
+      e2e_step(i, compute)
+    join_streams()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for st in streams:
+      st.wait_stream(torch.cuda.current_stream(device))
+    for i in range(n):
+      e2e_step(i, compute)
+    join_streams()
+    e1.record()
+    barrier()
+    return max_over_ranks(e0.elapsed_time(e1), dist, device) / n
+
   e2e_steps = max(3, min(args.steps, 30))
-  for st in streams:
-    st.wait_stream(torch.cuda.current_stream(device))
-  for i in range(3):
-    e2e_step(i)
-  join_streams()
-  barrier()
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  e0.record()
-  for st in streams:
-    st.wait_stream(torch.cuda.current_stream(device))
-  for i in range(e2e_steps):
-    e2e_step(i)
-  join_streams()
-  e1.record()
-  barrier()
-  e2e_ms = max_over_ranks(e0.elapsed_time(e1), dist, device) / e2e_steps
+  e2e_ms = timed_e2e(e2e_steps, True)
+  copy_ms = timed_e2e(e2e_steps, False)    # the same copies without the kernels: the host's ceiling
   e2e_value = whole_job_tops(e2e_ms, world)
 
   if rank != 0:
-    if dist is not None:
-      dist.destroy_process_group()
-    return
+    return None
 
   peaks = _peaks()
-  # int8 tcgen05 issues at twice the bf16 rate, so the int8 ceiling is taken as 2 x the
-  # driver-measured bf16 GEMM figure: the burst one while the timed region is shorter than
-  # two seconds (the power cap has not pulled the clocks down yet), else the sustained one.
-  burst = total_ms < 2000.0
-  peak_tops = 2.0 * (peaks['bf16_burst'] if burst else peaks['bf16_sustained'])
   achieved = OPS_PER_STEP / (gemm_ms * 1e-3) / 1e12
-
-  # The vendor library on the same GEMM, same buffers, timed the same way (context only).
-  library_tops = None
-  try:
-    d = dev[0]
-    w_cm = d['wq'].qvalue.t().contiguous().t()  # _int_mm wants a column-major right operand
-    for _ in range(3):
-      torch._int_mm(d['aq'], w_cm)
-    l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    l0.record()
-    for _ in range(20):
-      torch._int_mm(d['aq'], w_cm)
-    l1.record()
-    torch.cuda.synchronize()
-    library_tops = OPS_PER_STEP / (l0.elapsed_time(l1) / 20 * 1e-3) / 1e12
-  except Exception:  # the comparison is optional
-    library_tops = None
+  derived = 2.0 * peaks['bf16_burst']
+  peak = lib_peaks.get('int8_burst') or derived
+  traffic, traffic_note = measured_traffic('gemm_q8_pair_kernel<i8>')
+  # time x clock: the same work at another SM clock shows the same product when compute-bound
+  mhz = clocks.get('sm_mhz')
   line = {
       'metric': 'quantized GEMM TOPS', 'value': value, 'unit': 'TOPS', 'n_gpus': world,
       'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step,
+      'repeats': repeats, 'first_block_ms_per_step': first_block_ms / args.steps,
       'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'int8',
       'data': 'synthetic',
       'config': {
-          'workload': 'w8a8 dot_general prefill, BASELINE configs[1]: per-token int8 absmax '
-                      'quantize of A + int8 GEMM with fused per-token/per-channel dequant',
+          'workload': 'w8a8 dot_general, prefill-shaped: per-token int8 absmax quantize of A + '
+                      'int8 GEMM with fused per-token/per-channel dequant',
           'M': M, 'N': N, 'K': K, 'per_gpu': 'every rank runs the full [M,K]x[K,N] step on '
           'its own tokens',
           'l2': f'{NSETS} input/weight/output sets ({NSETS * 224} MB) cycled; one set (224 MB) '
                 'exceeds the 126 MB L2',
+          'timing': f'{repeats} back-to-back blocks of {args.steps} steps (>= 1 s inside CUDA '
+                    'events); ms_per_step is the median block / steps',
       },
       'roofline': {
-          'bound': 'tensor', 'achieved': achieved, 'peak': peak_tops, 'unit': 'TOP/s',
-          'frac': achieved / peak_tops, 'traffic': GEMM_DRAM_TRAFFIC_BYTES,
+          'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TOP/s',
+          'frac': achieved / peak, 'traffic': traffic, 'traffic_source': traffic_note,
           'kernel': 'gemm_q8_pair_kernel<i8>', 'kernel_ms': gemm_ms,
-          'peak_source': f"2 x bf16_tflops{'' if burst else '_sustained'} of MEASURED_PEAKS.json "
-                         f"({peaks['source']}; int8 issues at twice the bf16 rate)",
-          'library_int8_gemm_tops': library_tops,
+          'peak_source': ('torch._int_mm at 8192^3, best of 10, measured in this run (burst)'
+                          if lib_peaks.get('int8_burst') else
+                          f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})"),
+          'peak_measured_burst': lib_peaks.get('int8_burst'),
+          'peak_measured_sustained': lib_peaks.get('int8_sustained'),
+          'frac_of_sustained': (achieved / lib_peaks['int8_sustained']) if lib_peaks.get('int8_sustained') else None,
+          'peak_2x_bf16_burst': derived, 'frac_of_2x_bf16_burst': achieved / derived,
+          'kernel_ms_x_sm_mhz': gemm_ms * mhz if mhz else None,
+          'step_frac': (OPS_PER_STEP / (ms_per_step * 1e-3) / 1e12) / peak,
           'quantize_kernel_ms': quant_ms,
           'quantize_gbs': (M * K * 3 + M * 2) / (quant_ms * 1e-3) / 1e9,
+          'quantize_frac_of_hbm': (M * K * 3 + M * 2) / (quant_ms * 1e-3) / 1e9 / peaks['hbm_gbs'],
           'hbm_peak_gbs': peaks['hbm_gbs'],
       },
+      'library_peaks': lib_peaks,
       'e2e': {'value': e2e_value, 'unit': 'TOPS', 'h2d_bytes_per_step': M * K * 2,
-              'd2h_bytes_per_step': M * N * 2, 'ms_per_step': e2e_ms, 'steps': e2e_steps},
-      'gpu_launches': 2 * args.steps,
+              'd2h_bytes_per_step': M * N * 2, 'ms_per_step': e2e_ms, 'steps': e2e_steps,
+              'copy_only_ms_per_step': copy_ms,
+              'note': 'copy_only = the same pinned H2D + D2H copies without the kernels'},
+      'verified': verified,
+      'gpu_launches': 2 * nev,
       'clocks': clocks,
   }
   if world == 1 and not args.no_cpu_baseline:
@@ -644,9 +938,99 @@ def main():
         'value': tops, 'unit': 'TOPS', 'cores': threads, 'kind': 'port',
         'sample': f'{rows} of {M} token rows per step, full K and N, 3 timed steps '
                   f'({dt * 1e3:.0f} ms each)'}
-  print(json.dumps(line), flush=True)
+  return line
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument('--gpus', type=int, default=1)
+  ap.add_argument('--steps', type=int, default=200)
+  ap.add_argument('--warmup', type=int, default=20)
+  ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+  ap.add_argument('--no-cpu-baseline', action='store_true')
+  ap.add_argument('--m', type=int, default=None,
+                  help='token rows per step (profiling aid; the benchmark uses its own sizes)')
+  ap.add_argument('--workload', default='all', choices=['all', 'gemm', 'decoder', 'w4', 'hadamard'],
+                  help="'all' (default): the headline GEMM step plus the decoder / w4 / hadamard "
+                       'records in one line; the others run one workload alone')
+  ap.add_argument('--layers', type=int, default=32)
+  ap.add_argument('--batch', type=int, default=32)
+  ap.add_argument('--prompt', type=int, default=2048)
+  ap.add_argument('--decode', type=int, default=128)
+  ap.add_argument('--decoder-runs', type=int, default=3)
+  ap.add_argument('--exact-act-scale', action='store_true')
+  ap.add_argument('--write-golden', action='store_true',
+                  help='decoder workload on one GPU: (re)write the logits sample under tests/golden/')
+  ap.add_argument('--kernel-breakdown', action='store_true',
+                  help='decoder workload: print device time per kernel of a decode step and a '
+                       'prefill chunk instead of timing the run')
+  args = ap.parse_args()
+  args.warmup = max(args.warmup, 3)
+  if args.m is not None and args.workload in ('gemm',):
+    global M, OPS_PER_STEP
+    M = args.m
+    OPS_PER_STEP = 2 * M * N * K
+
+  rank = int(os.environ.get('RANK', '0'))
+  world = int(os.environ.get('WORLD_SIZE', '1'))
+  local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+
+  if args.impl == 'reference':
+    reference_arm(args, rank)
+    return
+
+  if not torch.cuda.is_available():
+    raise SystemExit('bench.py needs a CUDA device: the quantized path has no CPU fallback.')
+  torch.cuda.set_device(local_rank)
+  device = torch.device('cuda', local_rank)
+  dist = None
+  if world > 1:
+    import torch.distributed as dist
+    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+    dist.init_process_group('nccl', device_id=device)
+
+  with_cpu = world == 1 and not args.no_cpu_baseline
+  lib_peaks = {}
+  if rank == 0 and args.workload in ('all', 'gemm', 'hadamard', 'decoder'):
+    lib_peaks = library_peaks(device, sustain_s=4.0 if args.workload in ('all', 'gemm') else 0.0)
   if dist is not None:
-    dist.destroy_process_group()
+    dist.barrier()
+
+  line = None
+  if args.workload in ('all', 'gemm'):
+    line = gemm_workload(args, dist, device, rank, world, local_rank, lib_peaks)
+    torch.cuda.empty_cache()
+  if args.workload in ('all', 'decoder'):
+    rec = decoder_record(args, dist, device, rank, world, lib_peaks, with_cpu)
+    if line is not None:
+      line['decoder'] = rec
+    elif rank == 0 and rec is not None:
+      line = {'metric': 'w8a8 decoder tokens/s', 'value': rec['tokens_per_s'], 'unit': 'tokens/s',
+              'n_gpus': world, 'higher_is_better': True, 'data': 'synthetic', **rec}
+  if world == 1 and args.workload in ('all', 'w4'):
+    recs = w4_records(args, device, with_cpu)
+    if line is not None and args.workload == 'all':
+      line['w4'] = recs
+    else:
+      line = {'metric': 'int4 weight-only GEMM GB/s', 'n_gpus': 1, 'data': 'synthetic', 'w4': recs}
+    torch.cuda.empty_cache()
+  if world == 1 and args.workload in ('all', 'hadamard'):
+    rec = hadamard_record(args, device, with_cpu, lib_peaks)
+    if line is not None and args.workload == 'all':
+      line['hadamard'] = rec
+    else:
+      line = {'metric': 'Hadamard-quantized fp8 GEMM TFLOP/s', 'n_gpus': 1, 'data': 'synthetic', **rec}
+
+  if rank == 0 and line is not None:
+    print(json.dumps(line), flush=True)
+  if dist is not None:
+    # The decode-step graphs (which hold NCCL kernels) were dropped with the model; drain the
+    # device, meet the other ranks, then leave without running the communicator's destructor
+    # (tearing it down after graph capture was seen to stall).
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == '__main__':

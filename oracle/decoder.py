@@ -1,6 +1,11 @@
-"""NumPy restatement of qwix_b200.decoder for parity tests: same architecture, every projection
-through the oracle's quantize + dot_general (w8a8), everything else in float32 rounded to bf16
-where the model holds bf16 tensors."""
+"""Oracle decoder: a NumPy restatement of a Llama-shaped decoder under a w8a8 PTQ rule.
+
+Test infrastructure only (parity tests and the timed CPU baseline).  Every projection goes
+through the oracle's per-token quantize + dot_general, i.e. what BoxedParamProvider.dot_general
+does for a rule with act_qtype set (qwix/_src/providers/boxed_param.py:109-171, 416-455;
+qwix/_src/core/dot_general.py:135-261); everything else (RMSNorm, RoPE, attention, SwiGLU) is
+model code outside qwix, computed in float32 and rounded to bf16 where the model holds bf16
+tensors."""
 
 import ml_dtypes
 import numpy as np

@@ -166,8 +166,10 @@ def test_static_scale_activation(method):
   y0, y1 = ptq(x0), ptq(x1)
 
   dn = (((1,), (0,)), ((), ()))
-  how_a = oq.HowToQuantize(qtype='int8', channelwise_axes=[], calibration_method=method)
-  cal = oq.calibrate(h.to_numpy(x0), how_a)                     # per tensor: the batch mean is itself
+  # per-token statistics of the first batch, averaged over the batch axis (act_batch_axes)
+  how_a = oq.HowToQuantize(qtype='int8', channelwise_axes=[0], calibration_method=method)
+  cal = {k: v.astype(np.float32).mean(axis=0, keepdims=True).astype(v.dtype)
+         for k, v in oq.calibrate(h.to_numpy(x0), how_a).items()}
   scale, zp = oq.compute_scale_zero_point(cal, 'int8')
   wq = oq.quantize(w, oq.HowToQuantize(qtype='int8', channelwise_axes=[1]))
   for x, y in ((x0, y0), (x1, y1)):

@@ -12,7 +12,7 @@ import torch
 
 import qwix_b200 as qwix
 from qwix_b200 import decoder as D
-from tests import decoder_oracle as DO
+from oracle import decoder as DO
 from tests import helpers as h
 
 pytestmark = pytest.mark.gpu
