@@ -201,6 +201,23 @@ int qwx_gemm_q8_skinny(const void* a, const void* w, int64_t M, int64_t N, int64
                        int epilogue, void* workspace, size_t workspace_bytes,
                        int workspace_is_zero, qwx_stream_t stream);
 
+/* The same product for the decode step of a served model: at most 128 rows of int8 activations
+ * against an int8 weight held [N, K], on the tensor cores with the operands swapped (128 output
+ * channels are the tcgen05.mma's M, the tokens its N), the (channel tile, K stage) units dealt
+ * to the SMs in equal contiguous runs so that every SM streams the same share of the weight.
+ * Tiles shared by several CTAs are summed with exact int32 atomics in the workspace; the CTA
+ * that adds last scales, stores and clears, and nobody waits for another CTA.  K a multiple of
+ * 16.  out_dtype as qwx_gemm_q8 (QWX_S32 with both scales NULL for the raw accumulator); the
+ * result is bit-identical to qwx_gemm_q8.  workspace: qwx_gemm_q8_decode_workspace_bytes bytes,
+ * 16-byte aligned, zero on entry (workspace_is_zero = 0 clears it first), left zero.  The
+ * reference has no counterpart: XLA picks its own kernel for the shape
+ * (dot_general.py:253-258 hands it one lax.dot_general). */
+size_t qwx_gemm_q8_decode_workspace_bytes(int64_t M, int64_t N);
+int qwx_gemm_q8_decode(const void* a, const void* w, int64_t M, int64_t N, int64_t K,
+                       const void* sa, const void* sb, int scale_dtype, void* out, int out_dtype,
+                       int epilogue, void* workspace, size_t workspace_bytes,
+                       int workspace_is_zero, int32_t* error_flag, qwx_stream_t stream);
+
 /* The general dequantize-on-output contraction of dot_general._fast_dot_general
  * (dot_general.py:135-261): scales that change along K (sub-channel quantization, the tiled
  * contracting axis of :187-203 and the tile sum of :259) and the zero-point correction of an

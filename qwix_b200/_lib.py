@@ -70,6 +70,9 @@ _SIGNATURES = {
     'qwx_gemm_q8_skinny_workspace_bytes': (_sz, [_i64, _i64]),
     'qwx_gemm_q8_skinny': (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _int, _vp, _int, _int, _vp, _sz,
                                   _int, _vp]),
+    'qwx_gemm_q8_decode_workspace_bytes': (_sz, [_i64, _i64]),
+    'qwx_gemm_q8_decode': (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _int, _vp, _int, _int, _vp, _sz,
+                                  _int, _vp, _vp]),
     'qwx_gemm_q8_workspace_bytes': (_sz, [_i64, _i64, _i64]),
     'qwx_gemm_q8_ws': (_int, [_vp, _vp, _int, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _int,
                               _int, _vp, _int, _int, _vp, _sz, _int, _vp, _vp]),

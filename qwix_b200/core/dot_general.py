@@ -27,6 +27,9 @@ MIN_TILE_SIZE_TO_DEQUANT_ON_OUTPUT = 128
 # split-K tcgen05 kernel it wins up to 8 rows (9-17 us against 15-23 us on 16-58 MB weights,
 # 6.0 against 5.0 TB/s on 525 MB) and loses from 32 rows on, where its MMAs crowd the loads.
 SKINNY_MAX_ROWS = 8
+# Rows up to which an [N, K] int8 weight takes the swapped-operand tensor-core kernel
+# (tokens are the MMA's N: 32, 64 or 128 of them).
+DECODE_MAX_ROWS = 128
 
 # 'f32': float(acc) * sa * sb in float32, rounded once (default).  'reference': every step
 # rounds to the result dtype in the reference's order (dot_general.py:255-261).
@@ -247,6 +250,17 @@ def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
           _lib.ptr(None if ls is None else ls[b]), _lib.ptr(None if rs is None else rs[b]),
           scale_code, _lib.ptr(out[b]), _out_code(out_t), epi, _lib.ptr(ws), ws.numel(), 1,
           stream), 'dot_general')
+  elif (code == _lib.S8 and layout == _lib.B_NK and M <= DECODE_MAX_ROWS and K % 16 == 0):
+    # a few token rows against an [N, K] weight: operands swapped on the tensor cores, the
+    # weight dealt to the SMs in equal shares
+    ws_bytes = L.qwx_gemm_q8_decode_workspace_bytes(M, N)
+    ws = _splitk_workspace(lq.device, ws_bytes, 'decode')
+    for b in range(B):
+      _lib.check(L.qwx_gemm_q8_decode(
+          _lib.ptr(a3[b]), _lib.ptr(b3[b]), M, N, K,
+          _lib.ptr(None if ls is None else ls[b]), _lib.ptr(None if rs is None else rs[b]),
+          scale_code, _lib.ptr(out[b]), _out_code(out_t), epi, _lib.ptr(ws), ws.numel(), 1,
+          _lib.ptr(err), stream), 'dot_general')
   else:
     ws_bytes = L.qwx_gemm_q8_workspace_bytes(M, N, K)
     ws = _splitk_workspace(lq.device, ws_bytes) if ws_bytes else None

@@ -469,3 +469,77 @@ def test_quantized_matmul_rejects_bad_arguments():
   assert L.qwx_quant_gemm_q8(*args(ws.numel() - 1)) == 6      # QWX_ERR_WORKSPACE
   assert L.qwx_quant_gemm_q8(*args(ws.numel())) == 0
   torch.cuda.synchronize()
+
+
+# ---- the swapped-operand decode kernel (tokens are the MMA's N) ---------------------------------
+
+def _decode_gemm(a, w, out_dtype=torch.int32, sa=None, sb=None, ws=None, epilogue=0):
+  M, K = a.shape
+  N = w.shape[0]
+  L = _lib.lib()
+  need = L.qwx_gemm_q8_decode_workspace_bytes(M, N)
+  if ws is None:
+    ws = torch.zeros(need, dtype=torch.uint8, device='cuda')
+  out = torch.empty((M, N), dtype=out_dtype, device='cuda')
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  oc = {torch.int32: _lib.S32, torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}[out_dtype]
+  _lib.check(L.qwx_gemm_q8_decode(_lib.ptr(a), _lib.ptr(w), M, N, K, _lib.ptr(sa), _lib.ptr(sb),
+                                  _lib.F32, _lib.ptr(out), oc, epilogue, _lib.ptr(ws), ws.numel(), 1,
+                                  _lib.ptr(err), _lib.stream_ptr()), 'gemm_q8_decode')
+  torch.cuda.synchronize()
+  assert int(err.item()) == 0
+  return out, ws
+
+
+DECODE_KERNEL_SHAPES = [
+    (32, 4096, 4096),     # 32 tiles x 16 stages on 148 CTAs: every tile shared by 4-5 CTAs
+    (32, 6144, 4096), (32, 28672, 4096), (32, 4096, 14336),
+    (32, 128256, 4096),   # 1002 tiles: most owned whole, one shared at every CTA boundary
+    (32, 768, 4096), (32, 4096, 512), (32, 3584, 4096), (32, 4096, 1792),   # 1/8 shards: units < SMs
+    (1, 1024, 14336), (7, 1000, 272), (33, 2048 + 48, 512 + 32), (64, 4096, 4096),
+    (100, 1536, 2048), (128, 8192, 2048), (5, 128, 256), (32, 128, 128),
+]
+
+
+@pytest.mark.parametrize('mnk', DECODE_KERNEL_SHAPES, ids=[f'{m}x{n}x{k}' for m, n, k in DECODE_KERNEL_SHAPES])
+def test_decode_kernel_bit_exact(mnk):
+  M, N, K = mnk
+  rng = np.random.default_rng(M + N + K)
+  a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+  w = rng.integers(-128, 128, (N, K), dtype=np.int8)
+  want = (a.astype(np.float64) @ w.astype(np.float64).T).astype(np.int64)   # exact: |sums| < 2^53
+  at, wt = h.to_torch(a), h.to_torch(w)
+  got, ws = _decode_gemm(at, wt)
+  assert np.array_equal(got.cpu().numpy().astype(np.int64), want)
+  assert int(ws.count_nonzero().item()) == 0          # scratch slots and counters are left zero
+  # second call on the same scratch; scaled outputs equal the ordinary kernel's bit for bit
+  sa = torch.rand(M, device='cuda') + 0.5
+  sb = torch.rand(N, device='cuda') * 1e-3
+  for epi in (0, 1):
+    got2, ws = _decode_gemm(at, wt, out_dtype=torch.bfloat16, sa=sa, sb=sb, ws=ws, epilogue=epi)
+    ref = torch.empty_like(got2)
+    err = torch.zeros(1, dtype=torch.int32, device='cuda')
+    _lib.check(_lib.lib().qwx_gemm_q8(_lib.ptr(at), _lib.ptr(wt), _lib.S8, _lib.B_NK, M, N, K, 0,
+                                      _lib.ptr(sa), 0, _lib.ptr(sb), 0, _lib.F32, _lib.ptr(ref),
+                                      _lib.BF16, epi, _lib.ptr(err), _lib.stream_ptr()), 'gemm')
+    torch.cuda.synchronize()
+    assert torch.equal(got2.view(torch.int16), ref.view(torch.int16))
+  assert int(ws.count_nonzero().item()) == 0
+
+
+def test_decode_kernel_through_dot_general_and_errors():
+  L = _lib.lib()
+  rng = np.random.default_rng(1)
+  a = rng.integers(-128, 128, (32, 1024), dtype=np.int8)
+  w = rng.integers(-128, 128, (1024, 512), dtype=np.int8)       # logical [K, N]
+  wt = h.to_torch(w).t().contiguous().t()                       # stored [N, K]
+  got = bdg.dot_general(h.to_torch(a), wt, DN)
+  assert np.array_equal(got.cpu().numpy(), a.astype(np.int32) @ w.astype(np.int32))
+  assert L.qwx_gemm_q8_decode_workspace_bytes(129, 512) == 0
+  x = torch.zeros(16, dtype=torch.uint8, device='cuda')
+  args = (_lib.ptr(x), _lib.ptr(x), 200, 512, 1024, None, None, _lib.F32, _lib.ptr(x), _lib.S32, 0,
+          _lib.ptr(x), 16, 1, None, _lib.stream_ptr())
+  assert L.qwx_gemm_q8_decode(*args) == 5                        # more than 128 rows: unsupported
+  args = (_lib.ptr(x), _lib.ptr(x), 32, 512, 1024, None, None, _lib.F32, _lib.ptr(x), _lib.S32, 0,
+          _lib.ptr(x), 16, 1, None, _lib.stream_ptr())
+  assert L.qwx_gemm_q8_decode(*args) == 6                        # workspace too small
