@@ -64,6 +64,16 @@ enum qwx_epilogue { QWX_EPI_F32 = 0, QWX_EPI_REFERENCE = 1 };
 int qwx_version(void);
 const char* qwx_status_string(int status);
 
+/* Process-wide option: launch the short kernels of a decode step (qwx_gemm_q8_decode, the
+ * fused decoder stages below, the one-pass row quantizers) with CUDA's programmatic stream
+ * serialization, so that a kernel's set-up and its weight fetches overlap the tail of the
+ * kernel before it on the same stream.  Each of these kernels waits (griddepcontrol.wait) for
+ * its predecessor before it reads an activation or writes anything, so results do not change.
+ * Off by default; safe to set at any time, affects launches made afterwards (stream capture
+ * included).  The reference has no counterpart (XLA schedules its own kernels). */
+void qwx_set_programmatic_launch(int enabled);
+int qwx_get_programmatic_launch(void);
+
 /* Bytes of scratch the quantizer calls below need for this view (zero is possible). */
 size_t qwx_quantize_workspace_bytes(int64_t P, int64_t R, int64_t C,
                                     int64_t tp, int64_t tr, int64_t tc);
@@ -287,6 +297,16 @@ int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, vo
                                   int32_t* error_flag, int64_t wait_cycles, qwx_stream_t stream);
 int qwx_silu_mul_quantize(const void* gu, int64_t rows, int64_t f, void* y_out, void* q,
                           void* scale, qwx_stream_t stream);
+/* Greedy sampling over the logits a (column-parallel) lm_head projection produced: for every
+ * row of x (bf16 [rows, cols]) the largest value (best_value, float32 [rows], may be NULL) and
+ * index_offset + its lowest index (best_index, int64 [rows]); a positive NaN counts as the
+ * largest value.  index_offset is the first vocabulary entry of this rank's shard.  Model code
+ * like the stages above (no counterpart in qwix).  workspace: qwx_argmax_rows_workspace_bytes
+ * bytes, 16-byte aligned, its first rows * 4 bytes zero on entry and left zero. */
+size_t qwx_argmax_rows_workspace_bytes(int64_t rows, int64_t cols);
+int qwx_argmax_rows(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t index_offset,
+                    float* best_value, int64_t* best_index, void* workspace,
+                    size_t workspace_bytes, qwx_stream_t stream);
 int qwx_rope_cache(const void* qkv, int64_t B, int64_t T, int hq, int hkv, int hd,
                    const float* cos_t, const float* sin_t, int64_t pos, const int64_t* pos_dev,
                    void* q_out, void* cache_k, void* cache_v, int64_t cache_batch_stride,

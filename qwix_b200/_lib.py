@@ -34,6 +34,8 @@ _i64, _int, _vp, _sz, _dbl = (ctypes.c_int64, ctypes.c_int, ctypes.c_void_p,
 _SIGNATURES = {
     'qwx_version': (_int, []),
     'qwx_status_string': (ctypes.c_char_p, [_int]),
+    'qwx_set_programmatic_launch': (None, [_int]),
+    'qwx_get_programmatic_launch': (_int, []),
     'qwx_quantize_workspace_bytes': (_sz, [_i64] * 6),
     'qwx_calibrate': (_int, [_vp, _int] + [_i64] * 6 + [_int, _int, _dbl, _vp, _vp, _vp, _sz, _vp]),
     'qwx_compute_scale_zero_point': (_int, [_vp, _vp, _int, _i64, _int, _vp, _vp, _vp]),
@@ -65,6 +67,8 @@ _SIGNATURES = {
     'qwx_add_rmsnorm_quantize_peer': (_int, [_vp, _vp, _vp, _int, _int, _vp, _int, _vp, _dbl, _i64, _i64,
                                              _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     'qwx_silu_mul_quantize': (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
+    'qwx_argmax_rows_workspace_bytes': (_sz, [_i64, _i64]),
+    'qwx_argmax_rows': (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
     'qwx_rope_cache': (_int, [_vp, _i64, _i64, _int, _int, _int, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                               _i64, _i64, _vp]),
     'qwx_gemm_q8_skinny_workspace_bytes': (_sz, [_i64, _i64]),

@@ -9,6 +9,7 @@ to XLA.
 
 from __future__ import annotations
 
+import contextlib
 import math
 import threading
 from typing import Any, Mapping, Sequence
@@ -28,8 +29,13 @@ MIN_TILE_SIZE_TO_DEQUANT_ON_OUTPUT = 128
 # 6.0 against 5.0 TB/s on 525 MB) and loses from 32 rows on, where its MMAs crowd the loads.
 SKINNY_MAX_ROWS = 8
 # Rows up to which an [N, K] int8 weight takes the swapped-operand tensor-core kernel
-# (tokens are the MMA's N: 32, 64 or 128 of them).
-DECODE_MAX_ROWS = 128
+# (qwx_gemm_q8_decode: tokens are the MMA's N).  0 = never: measured against the split-K kernel
+# on the decoder's shapes at 32 tokens it is level on 16-25 MB weights (14.7 against 13.6 us,
+# 16.5 against 15.4 us) and behind on the large ones (31 against 25.5 us at 117 MB), because
+# what bounds a launch of this size is not the MMA shape but launch gap, first-byte latency
+# and the reduction of shared tiles (the breakdown is in gemm_q8_decode.cu); a whole decode
+# step of the 32-layer model takes 5.2 ms with it and 4.7 ms without.
+DECODE_MAX_ROWS = 0
 
 # 'f32': float(acc) * sa * sb in float32, rounded once (default).  'reference': every step
 # rounds to the result dtype in the reference's order (dot_general.py:255-261).
@@ -141,6 +147,32 @@ def _refine(t: torch.Tensor | None, k_from: int, k_to: int) -> torch.Tensor | No
 _INT_CODES = ('int8', 'int4')
 
 
+_placement = threading.local()
+
+
+@contextlib.contextmanager
+def output_into(buffer: torch.Tensor):
+  """While active, the next tensor-core contraction of this thread whose result has the
+  dtype and element count of `buffer` (contiguous) is written straight into it instead of
+  into a fresh allocation -- for callers whose consumer reads a fixed buffer (a partial sum
+  that peers read over NVLink).  The caller checks `result.data_ptr()` to see whether the
+  offer was taken."""
+  _placement.buffer = buffer
+  try:
+    yield
+  finally:
+    _placement.buffer = None
+
+
+def _result_buffer(shape, dtype, device) -> torch.Tensor:
+  buf = getattr(_placement, 'buffer', None)
+  if (buf is not None and buf.dtype == dtype and buf.device == device and buf.is_contiguous()
+      and buf.numel() == math.prod(shape)):
+    _placement.buffer = None
+    return buf.view(shape)
+  return torch.empty(shape, dtype=dtype, device=device)
+
+
 def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
                       **kwargs) -> torch.Tensor:
   """dot_general.py:135-261 on the tensor cores."""
@@ -208,7 +240,7 @@ def _fast_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None,
   scale_code = numerics.code_of_float(scale_dt) if scale_dt is not None else _lib.F32
   raw = ls is None and rs is None and code == _lib.S8
   out_t = torch.int32 if raw else res_t
-  out = torch.empty((B, M, N), dtype=out_t, device=lq.device)
+  out = _result_buffer((B, M, N), out_t, lq.device)
   err = _lib.error_flag(lq.device)
   epi = _lib.EPI_REFERENCE if EPILOGUE == 'reference' else _lib.EPI_F32
   L = _lib.lib()

@@ -1,5 +1,19 @@
 // Version and status strings of the C ABI.
+#include <atomic>
+
 #include "common.cuh"
+
+namespace qwx {
+namespace {
+std::atomic<int> g_programmatic_launch{0};
+}
+bool programmatic_launch_enabled() { return g_programmatic_launch.load(std::memory_order_relaxed) != 0; }
+}  // namespace qwx
+
+extern "C" void qwx_set_programmatic_launch(int enabled) {
+  qwx::g_programmatic_launch.store(enabled ? 1 : 0, std::memory_order_relaxed);
+}
+extern "C" int qwx_get_programmatic_launch(void) { return qwx::programmatic_launch_enabled() ? 1 : 0; }
 
 extern "C" int qwx_version(void) { return 100; }
 

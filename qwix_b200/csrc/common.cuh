@@ -165,6 +165,40 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+//
+// The kernels of a decode step are short and run back to back on one stream, so a good part of
+// each one's time is launch latency, set-up and the first loads.  A kernel launched with the
+// programmatic-stream-serialization attribute may start while its predecessor is still
+// running; it does whatever does not depend on the predecessor (barrier set-up, tensor-memory
+// allocation, fetching WEIGHTS, which are static) and then executes griddepcontrol.wait, which
+// returns once the predecessor has completed and its writes are visible.  Everything that
+// reads activations or writes global memory comes after that wait.  Without the attribute both
+// instructions do nothing.  qwx_set_programmatic_launch() turns the attribute on for the
+// kernels that contain the wait.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+bool programmatic_launch_enabled();   // capi.cu
+
+template <typename... P, typename... A>
+inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 // Function attributes (the dynamic shared-memory limit) are per device: a launch site keeps
 // one of these and sets its attributes the first time it runs on each device.  The flags are
 // idempotent; a benign race sets an attribute twice.

@@ -126,6 +126,8 @@ add_rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ delta,
   __shared__ uint32_t red_u[kDThreads / 32];
   const int tid = threadIdx.x;
   const float inv_d = 1.0f / (float)(nvec * 8);
+  griddep_launch_dependents();
+  griddep_wait();
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     uint4 cur[kDVec];
     float ss = 0.f;
@@ -220,6 +222,8 @@ add_rmsnorm_peer_kernel(const uint4* __restrict__ x, const PeerArgs pa,
   __shared__ uint32_t red_u[kDThreads / 32];
   __shared__ int s_count, s_ok;
   const int tid = threadIdx.x;
+  griddep_launch_dependents();
+  griddep_wait();       // this rank's GEMM has finished: its partial is complete
   if (tid == 0) {
     s_count = ++pa.launches[blockIdx.x];
     s_ok = 1;
@@ -318,6 +322,8 @@ silu_mul_kernel(const uint4* __restrict__ gu, int64_t rows, int fvec, uint4* __r
   extern __shared__ uint4 yrow[];
   __shared__ uint32_t red_u[kDThreads / 32];
   const int tid = threadIdx.x;
+  griddep_launch_dependents();
+  griddep_wait();
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint4* g = gu + row * 2 * fvec;
     const uint4* u = g + fvec;
@@ -369,6 +375,8 @@ __global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t
   const int half = hd / 2, per_head = half / 8;
   const int heads = hq + 2 * hkv;
   const int64_t total = B * T * heads * per_head;
+  griddep_launch_dependents();
+  griddep_wait();
   const int64_t p0 = pos_dev ? *pos_dev : pos;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -411,12 +419,142 @@ __global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t
   }
 }
 
+// ---- greedy sampling: argmax of every row of the logits --------------------------------------
+//
+// grid = (segments, rows): a CTA reduces one segment of one row to (largest value, its lowest
+// index), leaves the pair in the workspace and counts itself; the CTA that counts last for a
+// row merges the row's pairs, writes the result and clears the counter.  Values are compared
+// through their order-preserving integer image, ties go to the lower index (what a whole-row
+// argmax returns), a positive NaN sorts above everything.
+constexpr int kArgThreads = 256;
+
+__device__ __forceinline__ uint32_t orderable(uint32_t f32_bits) {
+  return (f32_bits & 0x80000000u) ? ~f32_bits : (f32_bits | 0x80000000u);
+}
+__device__ __forceinline__ float from_orderable(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ void take_better(uint32_t& k, int& i, uint32_t k2, int i2) {
+  if (k2 > k || (k2 == k && i2 < i)) { k = k2; i = i2; }
+}
+
+__global__ void __launch_bounds__(kArgThreads)
+argmax_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t cols, int seg_cols,
+                   int64_t index_offset, float* __restrict__ best_value,
+                   int64_t* __restrict__ best_index, uint2* __restrict__ partial,
+                   int* __restrict__ counters) {
+  __shared__ uint32_t sk[kArgThreads / 32];
+  __shared__ int si[kArgThreads / 32];
+  __shared__ int s_last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seg = blockIdx.x, segs = gridDim.x;
+  const int64_t row = blockIdx.y;
+  griddep_launch_dependents();
+  griddep_wait();
+  const int64_t c0 = (int64_t)seg * seg_cols;
+  const int64_t c1 = c0 + seg_cols < cols ? c0 + seg_cols : cols;
+  const __nv_bfloat16* src = x + row * cols;
+  uint32_t k = 0;          // below every real value's image
+  int idx = 0x7fffffff;
+  // 16-byte loads where the row pitch allows them (cols % 8 == 0 keeps every row aligned)
+  if ((cols & 7) == 0 && (c0 & 7) == 0) {
+    const int64_t v0 = c0 >> 3, v1 = c1 >> 3;
+    const uint4* v = reinterpret_cast<const uint4*>(src);
+    for (int64_t vi = v0 + tid; vi < v1; vi += kArgThreads) {
+      const uint4 u = v[vi];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t klo = orderable(w[j] << 16), khi = orderable(w[j] & 0xffff0000u);
+        const int base = (int)(vi * 8 + 2 * j);
+        if (klo > k) { k = klo; idx = base; }
+        if (khi > k) { k = khi; idx = base + 1; }
+      }
+    }
+    for (int64_t c = (v1 << 3) + tid; c < c1; c += kArgThreads) {
+      const uint32_t kk = orderable(__float_as_uint(__bfloat162float(src[c])));
+      if (kk > k) { k = kk; idx = (int)c; }
+    }
+  } else {
+    for (int64_t c = c0 + tid; c < c1; c += kArgThreads) {
+      const uint32_t kk = orderable(__float_as_uint(__bfloat162float(src[c])));
+      if (kk > k) { k = kk; idx = (int)c; }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    take_better(k, idx, __shfl_xor_sync(0xffffffffu, k, o), __shfl_xor_sync(0xffffffffu, idx, o));
+  if (lane == 0) { sk[warp] = k; si[warp] = idx; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int i = 1; i < kArgThreads / 32; ++i) take_better(k, idx, sk[i], si[i]);
+    partial[row * segs + seg] = make_uint2(k, (uint32_t)idx);
+    __threadfence();
+    const int old = atomicAdd(counters + row, 1);
+    s_last = old == segs - 1;
+    if (s_last) counters[row] = 0;
+  }
+  __syncthreads();
+  if (!s_last || warp != 0) return;
+  __threadfence();
+  k = 0;
+  idx = 0x7fffffff;
+  for (int s = lane; s < segs; s += 32) {
+    const uint2 p = __ldcg(partial + row * segs + s);
+    take_better(k, idx, p.x, (int)p.y);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    take_better(k, idx, __shfl_xor_sync(0xffffffffu, k, o), __shfl_xor_sync(0xffffffffu, idx, o));
+  if (lane == 0) {
+    if (best_value) best_value[row] = from_orderable(k);
+    best_index[row] = (int64_t)idx + index_offset;
+  }
+}
+
 }  // namespace
 }  // namespace qwx
 
 using namespace qwx;
 
 extern "C" {
+
+static int argmax_segments(int64_t rows, int64_t cols) {
+  // enough CTAs to cover the SMs about twice, at least 2048 values each
+  int64_t s = (2 * 148 + rows - 1) / rows;
+  const int64_t most = (cols + 2047) / 2048;
+  if (s > most) s = most;
+  if (s > 64) s = 64;
+  return (int)(s < 1 ? 1 : s);
+}
+
+size_t qwx_argmax_rows_workspace_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return (size_t)rows * 4 + 256 + (size_t)rows * argmax_segments(rows, cols) * 8;
+}
+
+int qwx_argmax_rows(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t index_offset,
+                    float* best_value, int64_t* best_index, void* workspace,
+                    size_t workspace_bytes, qwx_stream_t stream) {
+  if (!x || !best_index || !workspace) return QWX_ERR_NULL;
+  if (rows <= 0 || cols <= 0 || rows > 65535 || cols > 0x7fffffff) return QWX_ERR_SHAPE;
+  if (x_dtype != QWX_BF16) return QWX_ERR_DTYPE;
+  if (workspace_bytes < qwx_argmax_rows_workspace_bytes(rows, cols)) return QWX_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15))
+    return QWX_ERR_ALIGN;
+  const int segs = argmax_segments(rows, cols);
+  int64_t seg_cols = (cols + segs - 1) / segs;
+  seg_cols = (seg_cols + 7) & ~(int64_t)7;
+  int* counters = (int*)workspace;
+  uint2* partial = (uint2*)((char*)workspace + (((size_t)rows * 4 + 255) & ~(size_t)255));
+  if (launch_dependent(argmax_rows_kernel, dim3((unsigned)segs, (unsigned)rows), dim3(kArgThreads), 0,
+                       (cudaStream_t)stream, (const __nv_bfloat16*)x, cols, (int)seg_cols,
+                       index_offset, best_value, best_index, partial, counters) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return QWX_ERR_LAUNCH;
+  }
+  return QWX_OK;
+}
 
 int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weight, double eps,
                              int64_t rows, int64_t d, void* x_out, void* y_out, void* q,
@@ -430,10 +568,13 @@ int qwx_add_rmsnorm_quantize(const void* x, const void* delta, const void* weigh
   if ((all & 15) || (reinterpret_cast<uintptr_t>(q) & 7)) return QWX_ERR_ALIGN;
   const int64_t cap = 148 * 8;
   const unsigned grid = (unsigned)(rows < cap ? rows : cap);
-  add_rmsnorm_kernel<<<grid, kDThreads, 0, (cudaStream_t)stream>>>(
-      (const uint4*)x, (const uint4*)delta, (const uint4*)weight, (float)eps, rows, (int)(d / 8),
-      (uint4*)x_out, (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale);
-  QWX_CHECK_LAUNCH();
+  if (launch_dependent(add_rmsnorm_kernel, dim3(grid), dim3(kDThreads), 0, (cudaStream_t)stream,
+                       (const uint4*)x, (const uint4*)delta, (const uint4*)weight, (float)eps, rows,
+                       (int)(d / 8), (uint4*)x_out, (uint4*)y_out, (uint2*)q,
+                       (__nv_bfloat16*)scale) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return QWX_ERR_LAUNCH;
+  }
   return QWX_OK;
 }
 
@@ -488,10 +629,12 @@ int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, vo
   if (resident <= 0) return QWX_ERR_NO_DEVICE;
   int64_t cap = max_ctas < resident ? max_ctas : resident;
   const unsigned grid = (unsigned)(rows < cap ? rows : cap);
-  add_rmsnorm_peer_kernel<<<grid, kDThreads, 0, (cudaStream_t)stream>>>(
-      (const uint4*)x, pa, (const uint4*)weight, (float)eps, rows, (int)(d / 8), (uint4*)x_out,
-      (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale);
-  QWX_CHECK_LAUNCH();
+  if (launch_dependent(add_rmsnorm_peer_kernel, dim3(grid), dim3(kDThreads), 0, (cudaStream_t)stream,
+                       (const uint4*)x, pa, (const uint4*)weight, (float)eps, rows, (int)(d / 8),
+                       (uint4*)x_out, (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return QWX_ERR_LAUNCH;
+  }
   return QWX_OK;
 }
 
@@ -513,9 +656,12 @@ int qwx_silu_mul_quantize(const void* gu, int64_t rows, int64_t f, void* y_out, 
   }
   const int64_t cap = 148 * 4;
   const unsigned grid = (unsigned)(rows < cap ? rows : cap);
-  silu_mul_kernel<<<grid, kDThreads, smem, (cudaStream_t)stream>>>(
-      (const uint4*)gu, rows, (int)(f / 8), (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale);
-  QWX_CHECK_LAUNCH();
+  if (launch_dependent(silu_mul_kernel, dim3(grid), dim3(kDThreads), smem, (cudaStream_t)stream,
+                       (const uint4*)gu, rows, (int)(f / 8), (uint4*)y_out, (uint2*)q,
+                       (__nv_bfloat16*)scale) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return QWX_ERR_LAUNCH;
+  }
   return QWX_OK;
 }
 
@@ -532,11 +678,13 @@ int qwx_rope_cache(const void* qkv, int64_t B, int64_t T, int hq, int hkv, int h
   const int64_t total = B * T * (hq + 2 * hkv) * (hd / 16);
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  rope_cache_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)qkv, B, T, hq, hkv, hd, cos_t, sin_t, pos, pos_dev,
-      (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v, cache_batch_stride,
-      cache_head_stride);
-  QWX_CHECK_LAUNCH();
+  if (launch_dependent(rope_cache_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream,
+                       (const __nv_bfloat16*)qkv, B, T, hq, hkv, hd, cos_t, sin_t, pos, pos_dev,
+                       (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v,
+                       cache_batch_stride, cache_head_stride) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return QWX_ERR_LAUNCH;
+  }
   return QWX_OK;
 }
 

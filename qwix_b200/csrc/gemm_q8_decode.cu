@@ -18,6 +18,14 @@
 // stores and clears the slot.  Nobody waits for another CTA: no cooperative launch, no spin.
 // A CTA that owns a whole tile skips the scratch.
 //
+// Where the time of a small launch goes (4096 x 4096 weight, 32 tokens, 16.7 MB = 2.6 us of HBM
+// time; measured with %globaltimer probes): about 1.8 us between two kernels of a CUDA graph,
+// 0.9 us until the first TMA issue, 1.8 us until its data arrives, 1.9 us of streaming and MMAs
+// (a tcgen05.mma of N = 32 costs about as much as one of N = 256: 0.5 us per 32 KB stage, i.e.
+// at most 60 GB/s per SM, so every SM has to take part), then the reduction of shared tiles:
+// adds + fence 1.3 us, counter 0.7 us, finishing loads and stores 2.5 us in the CTA that adds
+// last.  Programmatic dependent launch hides the first 2.7 us behind the previous kernel.
+//
 // Roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer and tensor-memory owner, warps
 // 2-5 epilogue (two accumulators ping-pong, so the epilogue of one segment overlaps the MMAs
 // of the next).  Every mbarrier wait is bounded (sm100.cuh).
@@ -131,11 +139,7 @@ gemm_q8_decode_kernel(const __grid_constant__ CUtensorMap tma_w,
     tmem_alloc(smem_u32(&ctl->tmem_base), Cfg::kTmemCols);
     tmem_relinquish();
   }
-  if (warp >= 2) {
-    // token scales, staged once
-    for (int m = threadIdx.x - 64; m < NT; m += 128)
-      ctl->sa[m] = (p.sa && m < p.M) ? dec_scale(p.sa, p.scale_dtype, m) : 1.0f;
-  }
+  griddep_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -147,7 +151,34 @@ gemm_q8_decode_kernel(const __grid_constant__ CUtensorMap tma_w,
     uint32_t phase = 0;
     long issued = 0;
     bool ok = true;
-    for (long long u = u_begin; u < u_end && ok; ++u) {
+    // The weight does not depend on the kernel before this one: the first pass through the
+    // ring fetches its weight halves at once, the token halves follow the dependency wait.
+    const long long ahead = (u_end - u_begin) < Cfg::kStages ? (u_end - u_begin) : Cfg::kStages;
+    if (lane == 0) {
+      for (long long i = 0; i < ahead; ++i) {
+        const long long u = u_begin + i;
+        const int tile = (int)(u / S), ks = (int)(u % S);
+        const uint32_t bar = smem_u32(&ctl->full[i]);
+        const uint32_t sw = ring + (uint32_t)i * Cfg::kStageBytes;
+        mbar_expect_tx(bar, Cfg::kStageBytes);
+#pragma unroll
+        for (int j = 0; j < DSK; ++j)
+          tma_load_2d(sw + j * (DT * DBK), &tma_w, (ks * DSK + j) * DBK, tile * DT, bar);
+      }
+      griddep_wait();
+      for (long long i = 0; i < ahead; ++i) {
+        const int ks = (int)((u_begin + i) % S);
+        const uint32_t bar = smem_u32(&ctl->full[i]);
+        const uint32_t sact = ring + (uint32_t)i * Cfg::kStageBytes + Cfg::kWBytes;
+#pragma unroll
+        for (int j = 0; j < DSK; ++j)
+          tma_load_2d(sact + j * (NT * DBK), &tma_a, (ks * DSK + j) * DBK, 0, bar);
+      }
+      issued = (long)ahead;
+    }
+    stage = (int)(ahead % Cfg::kStages);
+    phase = ahead == Cfg::kStages ? 1u : 0u;
+    for (long long u = u_begin + ahead; u < u_end && ok; ++u) {
       if (lane == 0) {
         ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort);
         if (ok) {
@@ -224,6 +255,12 @@ gemm_q8_decode_kernel(const __grid_constant__ CUtensorMap tma_w,
     // ---------------- epilogue ----------------
     const int q = warp & 3;                     // tensor-memory lane quarter this warp may read
     const int nl = q * 32 + lane;               // channel inside the tile
+    // Scales come from the kernel before this one, and nothing may be written before it has
+    // finished.  Every epilogue warp stages the token scales (same values: a benign overlap).
+    griddep_wait();
+    for (int m = lane; m < NT; m += 32)
+      ctl->sa[m] = (p.sa && m < p.M) ? dec_scale(p.sa, p.scale_dtype, m) : 1.0f;
+    __syncwarp();
     int acc = 0;
     uint32_t acc_phase = 0, epi_phase = 0;
     bool ok = true;
@@ -312,11 +349,19 @@ gemm_q8_decode_kernel(const __grid_constant__ CUtensorMap tma_w,
         if (ctl->last) {
           __threadfence();
           if (n_ok) {
-            for (int m = 0; m < p.M; ++m) {
-              int32_t* w = slot + m * DT;
-              const int32_t v = __ldcg(w);
-              __stcg(w, 0);
-              emit(m, n, v, sb);
+            // all loads first (one L2 round trip for the lot), then the clears, then the stores
+#pragma unroll 1
+            for (int c = 0; c * 32 < p.M; ++c) {
+              int32_t v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[j] = c * 32 + j < p.M ? __ldcg(slot + (c * 32 + j) * DT) : 0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (c * 32 + j < p.M) __stcg(slot + (c * 32 + j) * DT, 0);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (c * 32 + j < p.M) emit(c * 32 + j, n, v[j], sb);
             }
           }
         }
@@ -345,8 +390,11 @@ int launch_decode(const CUtensorMap& tw, const CUtensorMap& ta, const DecParams&
       return QWX_ERR_LAUNCH;
     configured.mark();
   }
-  kern<<<grid, kDecThreads, dec_smem_bytes<NT>(), st>>>(tw, ta, p);
-  QWX_CHECK_LAUNCH();
+  if (launch_dependent(kern, dim3(grid), dim3(kDecThreads), dec_smem_bytes<NT>(), st, tw, ta, p) !=
+      cudaSuccess) {
+    (void)cudaGetLastError();
+    return QWX_ERR_LAUNCH;
+  }
   return QWX_OK;
 }
 

@@ -143,6 +143,8 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
   using Q = typename OutTraits<O>::Q;
   constexpr int kSegs = kThreads / G;
   __shared__ float red[2][kThreads / 32];
+  griddep_launch_dependents();
+  griddep_wait();
   const int lane_in_group = threadIdx.x % G;
   const int64_t seg = (int64_t)blockIdx.x * kSegs + threadIdx.x / G;
   const bool live = seg < segments;
@@ -330,6 +332,8 @@ quantize_rows_bf16_s8_kernel(const uint4* __restrict__ x, int64_t segments, int 
   __shared__ uint32_t red[2][kThreads / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint4 cur[kRowVec];
+  griddep_launch_dependents();
+  griddep_wait();
 
   // Rows reach shared memory through 16-byte cp.async copies that every thread issues for its
   // own vectors, three rows ahead: the bytes in flight per SM no longer depend on registers.
@@ -882,28 +886,36 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
           return (int)QWX_ERR_LAUNCH;
         configured.mark();
       }
-      if (wide)
-        quantize_rows_bf16_s8_kernel<8><<<grid, kThreads, ring_bytes, st>>>(
-            (const uint4*)x, segments, (int)(tc / 8), (uint2*)q, (__nv_bfloat16*)scale);
-      else
-        quantize_rows_bf16_s8_kernel<4><<<grid, kThreads, ring_bytes, st>>>(
-            (const uint4*)x, segments, (int)(tc / 8), (uint2*)q, (__nv_bfloat16*)scale);
-      QWX_CHECK_LAUNCH();
+      const cudaError_t e =
+          wide ? launch_dependent(quantize_rows_bf16_s8_kernel<8>, dim3(grid), dim3(kThreads), ring_bytes,
+                                  st, (const uint4*)x, segments, (int)(tc / 8), (uint2*)q,
+                                  (__nv_bfloat16*)scale)
+               : launch_dependent(quantize_rows_bf16_s8_kernel<4>, dim3(grid), dim3(kThreads), ring_bytes,
+                                  st, (const uint4*)x, segments, (int)(tc / 8), (uint2*)q,
+                                  (__nv_bfloat16*)scale);
+      if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)QWX_ERR_LAUNCH;
+      }
       return (int)QWX_OK;
     }
     return dispatch_float(x_dtype, [&](auto t) {
       using T = decltype(t);
       return dispatch_out(qtype, [&](auto o) {
         constexpr Out O = decltype(o)::value;
+        cudaError_t e;
         if (tc <= 32 * 8 * kCache) {
           const int64_t blocks = (segments + 7) / 8;
-          quantize_rows_kernel<T, O, 32><<<(unsigned)blocks, kThreads, 0, st>>>(
-              x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);
+          e = launch_dependent(quantize_rows_kernel<T, O, 32>, dim3((unsigned)blocks), dim3(kThreads), 0, st,
+                               x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);
         } else {
-          quantize_rows_kernel<T, O, 256><<<(unsigned)segments, kThreads, 0, st>>>(
-              x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);
+          e = launch_dependent(quantize_rows_kernel<T, O, 256>, dim3((unsigned)segments), dim3(kThreads), 0,
+                               st, x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);
         }
-        QWX_CHECK_LAUNCH();
+        if (e != cudaSuccess) {
+          (void)cudaGetLastError();
+          return (int)QWX_ERR_LAUNCH;
+        }
         return (int)QWX_OK;
       });
     });

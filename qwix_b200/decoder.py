@@ -148,12 +148,21 @@ class RowParallelDense(nn.Dense):
       # dtype: the nearest a sharded contraction gets to the unsharded result
       y = dg.dot_general(xq, kernel.array, dn, preferred_element_type=torch.float32)
       return self.comm.all_reduce_sum(y).to(x.dtype)
-    y = ops.dot_general(x, kernel, dn)
     ex = self.comm.exchange
-    if (self.comm.peer_active and ex is not None and y.dtype == torch.bfloat16
-        and y.numel() <= ex.capacity):
-      # leave the partial where the peers can read it: the next add + norm kernel sums the ranks
-      return ex.publish(y)
+    out_shape = tuple(x.shape[:-1]) + (kernel.shape[-1],)
+    numel = math.prod(out_shape)
+    if (self.comm.peer_active and ex is not None and x.dtype == torch.bfloat16
+        and numel <= ex.capacity):
+      # Leave the partial where the peers can read it (the next add + norm kernel sums the
+      # ranks): the GEMM is offered the exchange buffer as its output, so nothing is copied.
+      from qwix_b200.core import dot_general as dg
+      which, view = ex.reserve(out_shape)
+      with dg.output_into(view):
+        y = ops.dot_general(x, kernel, dn)
+      if y.data_ptr() != view.data_ptr():      # the contraction took another path: copy
+        view.copy_(y)
+      return fused.PeerPartial(ex, which, view)
+    y = ops.dot_general(x, kernel, dn)
     return self.comm.all_reduce_sum(y)
 
 
@@ -375,10 +384,11 @@ class Decoder(torch.nn.Module):
       self.comm.open_exchange(max(self.prefill_rows, batch) * cfg.d_model, self.device)
 
   def forward(self, tokens: torch.Tensor, pos=0, batch_offset: int = 0,
-              last_only: bool = True) -> torch.Tensor:
+              last_only: bool = True, local_logits: bool = False) -> torch.Tensor:
     """tokens [B, T] at positions pos..pos+T-1 of sequences batch_offset..batch_offset+B-1.
     `pos` is an int, or for single-token steps a one-element int64 device tensor.
-    Returns full-vocabulary logits [B, 1 or T, vocab] (float32)."""
+    Returns full-vocabulary logits [B, 1 or T, vocab] (float32), or with `local_logits` this
+    rank's vocabulary shard [B, 1 or T, vocab / ranks] in the model dtype."""
     B, T = tokens.shape
     x = self.embed[tokens]
     mask = None
@@ -410,7 +420,30 @@ class Decoder(torch.nn.Module):
         x = blk(x, cos, sin, ck, cv, pos, mask)
       x = self.final_norm(x[:, -1:] if last_only else x)
     logits = self.lm_head(x)
+    if local_logits:
+      return logits
     return self.comm.all_gather_last(logits).float()
+
+  def greedy_ids(self, tokens: torch.Tensor, pos=0, batch_offset: int = 0) -> torch.Tensor:
+    """The argmax token of the last position, [B]: every rank takes the argmax of its own
+    vocabulary shard and the ranks exchange one (value, index) pair per sequence, instead of
+    gathering and widening [B, vocab] logits.  Ties go to the lowest index, as a global argmax
+    would have it."""
+    local = self.forward(tokens, pos, batch_offset, local_logits=True)[:, -1]     # [B, vocab / t]
+    if local.is_cuda and local.dtype == torch.bfloat16:
+      if self.comm.size == 1:
+        return fused.argmax_rows(local)
+      idx, val = fused.argmax_rows(local, self.comm.rank * local.shape[-1], want_values=True)
+      pair = torch.stack([val, idx.float()], dim=-1)
+    else:
+      val, idx = local.max(dim=-1)
+      if self.comm.size == 1:
+        return idx
+      pair = torch.stack([val.float(), (idx + self.comm.rank * local.shape[-1]).float()], dim=-1)
+    parts = torch.empty((self.comm.size,) + tuple(pair.shape), dtype=pair.dtype, device=pair.device)
+    self.comm.dist.all_gather_into_tensor(parts, pair.contiguous(), group=self.comm.group)
+    best = parts[..., 0].argmax(dim=0)                # first maximum: the lowest rank, lowest ids
+    return parts[..., 1].gather(0, best[None])[0].long()
 
 
 def w8a8_rules():
@@ -427,7 +460,7 @@ class _StepGraph:
     self.graph = None
 
   def step(self):
-    self.tok.copy_(self.model(self.tok, self.pos, 0)[:, -1].argmax(-1, keepdim=True))
+    self.tok.copy_(_greedy(self.model, self.tok, self.pos, 0).view(-1, 1))
     self.pos.add_(1)
 
   def capture(self):
@@ -435,6 +468,14 @@ class _StepGraph:
     self.graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(self.graph):   # records the step; it runs only when replayed
       self.step()
+
+
+def _greedy(model, tokens, pos, batch_offset):
+  """Greedy next ids through the (possibly quantized) model: the wrapper's call activates the
+  provider, the decoder's `greedy_ids` does the rest."""
+  if isinstance(model, qwix.model.QuantizedModel):
+    return model(tokens, pos, batch_offset, _method='greedy_ids')
+  return model.greedy_ids(tokens, pos, batch_offset)
 
 
 @torch.no_grad()
@@ -454,8 +495,7 @@ def generate(model, tokens: torch.Tensor, steps: int, prefill_batch: int = 4,
   ev[0].record()
   nxt = torch.empty((B,), dtype=torch.long, device=tokens.device)
   for b0 in range(0, B, prefill_batch):
-    logits = model(tokens[b0:b0 + prefill_batch], 0, b0)
-    nxt[b0:b0 + prefill_batch] = logits[:, -1].argmax(-1)
+    nxt[b0:b0 + prefill_batch] = _greedy(model, tokens[b0:b0 + prefill_batch], 0, b0)
   ev[1].record()
   out = torch.empty((B, steps), dtype=torch.long, device=tokens.device)
   out[:, 0] = nxt

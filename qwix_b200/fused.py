@@ -103,13 +103,23 @@ class PeerExchange:
       return None
     return ex
 
-  def publish(self, y: torch.Tensor) -> 'PeerPartial':
-    """Copies this rank's partial output into the buffer whose turn it is."""
-    if y.dtype != torch.bfloat16 or y.numel() > self.capacity:
+  def reserve(self, shape) -> tuple[int, torch.Tensor]:
+    """The buffer whose turn it is, viewed as `shape`: the place where this rank's next
+    partial output belongs (a projection writes it there directly, or `publish` copies)."""
+    n = 1
+    for d in shape:
+      n *= d
+    if n > self.capacity:
       raise ValueError('partial does not fit the exchange buffers')
     which = self.turn
     self.turn ^= 1
-    view = self.partials[which][:y.numel()].view(y.shape)
+    return which, self.partials[which][:n].view(tuple(shape))
+
+  def publish(self, y: torch.Tensor) -> 'PeerPartial':
+    """Copies this rank's partial output into the buffer whose turn it is."""
+    if y.dtype != torch.bfloat16:
+      raise ValueError('partial does not fit the exchange buffers')
+    which, view = self.reserve(y.shape)
     view.copy_(y)
     return PeerPartial(self, which, view)
 
@@ -212,6 +222,31 @@ def rope_cache(qkv: torch.Tensor, hq: int, hkv: int, hd: int, cos: torch.Tensor,
       _lib.ptr(cache_v), cache_k.stride(0), cache_k.stride(1), _lib.stream_ptr(qkv.device)),
       'rope_cache')
   return q.transpose(1, 2)
+
+
+_argmax_ws: dict = {}
+
+
+def argmax_rows(x: torch.Tensor, index_offset: int = 0, want_values: bool = False):
+  """For every row of the bf16 matrix x [rows, cols]: index_offset + the lowest index of its
+  largest value (int64 [rows]), and with `want_values` that value (float32 [rows])."""
+  _lib.require_cuda(x)
+  if x.ndim != 2 or x.dtype != torch.bfloat16:
+    raise ValueError('argmax_rows takes a 2-D bfloat16 tensor.')
+  x = x.contiguous()
+  rows, cols = x.shape
+  L = _lib.lib()
+  need = L.qwx_argmax_rows_workspace_bytes(rows, cols)
+  key = (x.device, torch.cuda.current_stream(x.device).cuda_stream)
+  ws = _argmax_ws.get(key)
+  if ws is None or ws.numel() < need:
+    ws = _argmax_ws[key] = torch.zeros(max(need, 1 << 16), dtype=torch.uint8, device=x.device)
+  idx = torch.empty((rows,), dtype=torch.int64, device=x.device)
+  val = torch.empty((rows,), dtype=torch.float32, device=x.device) if want_values else None
+  _lib.check(L.qwx_argmax_rows(_lib.ptr(x), _lib.BF16, rows, cols, int(index_offset), _lib.ptr(val),
+                               _lib.ptr(idx), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(x.device)),
+             'argmax_rows')
+  return (idx, val) if want_values else idx
 
 
 def quantized_matmul(x: torch.Tensor, w: QArray, out_dtype=torch.bfloat16,

@@ -32,11 +32,13 @@ class QuantizedModel(torch.nn.Module):
       self._hooks.append(mod.register_forward_hook(
           lambda m, args, out: _context.pop_module(), always_call=True))
 
-  def forward(self, *args, **kwargs):
+  def forward(self, *args, _method: str | None = None, **kwargs):
+    """Runs the model (or, with `_method`, another method of it that ends in the model's
+    ops) under the provider."""
     model, args, kwargs = self.provider.process_model_inputs(self.model, args, kwargs)
     with _context.provider_scope(self.provider):
-      out = model(*args, **kwargs)
-    return self.provider.process_model_output('__call__', out)
+      out = model(*args, **kwargs) if _method is None else getattr(model, _method)(*args, **kwargs)
+    return self.provider.process_model_output(_method or '__call__', out)
 
   def params(self) -> dict:
     """Nested dict of the model's weights: tensors, or WithAux(QArray) once quantized --

@@ -191,3 +191,22 @@ def test_peer_wait_runs_out_and_reports():
   got = _peer_call(s, err)
   assert int(err.item()) == 0
   assert not bool((got['q'] == 7).all())
+
+
+@pytest.mark.parametrize('shape', [(32, 128256), (4, 16032), (1, 1000), (7, 50), (64, 4096), (3, 8 * 2048 + 5)])
+def test_argmax_rows_matches_library(shape):
+  g = torch.Generator(device='cuda').manual_seed(sum(shape))
+  x = torch.randn(shape, device='cuda', generator=g).to(torch.bfloat16)
+  x[0, shape[1] // 3] = x.max() + 1                     # a clear winner
+  if shape[0] > 1:
+    top = x[1].max()
+    x[1, min(5, shape[1] - 1)] = top                    # ties: the lowest index wins
+    x[1, shape[1] - 1] = top
+  for _ in range(2):                                    # second call: counters were left zero
+    idx, val = fused.argmax_rows(x, index_offset=1000, want_values=True)
+    want_val, _ = x.float().max(dim=-1)
+    assert torch.equal(val, want_val)
+    # lowest index among the maxima (the library's own argmax documents the first maximum)
+    first = (x.float() == want_val[:, None]).float().argmax(dim=-1)
+    assert torch.equal(idx, first + 1000)
+  assert torch.equal(fused.argmax_rows(x), first)

@@ -533,8 +533,25 @@ def test_decode_kernel_through_dot_general_and_errors():
   a = rng.integers(-128, 128, (32, 1024), dtype=np.int8)
   w = rng.integers(-128, 128, (1024, 512), dtype=np.int8)       # logical [K, N]
   wt = h.to_torch(w).t().contiguous().t()                       # stored [N, K]
-  got = bdg.dot_general(h.to_torch(a), wt, DN)
+  old = bdg.DECODE_MAX_ROWS
+  try:
+    bdg.DECODE_MAX_ROWS = 128            # route this contraction through the decode kernel
+    got = bdg.dot_general(h.to_torch(a), wt, DN)
+  finally:
+    bdg.DECODE_MAX_ROWS = old
   assert np.array_equal(got.cpu().numpy(), a.astype(np.int32) @ w.astype(np.int32))
+  # with programmatic dependent launch switched on the results are the same
+  L.qwx_set_programmatic_launch(1)
+  try:
+    bdg.DECODE_MAX_ROWS = 128
+    again = bdg.dot_general(h.to_torch(a), wt, DN)
+    q = bq.quantize(torch.randn(64, 4096, device='cuda').to(torch.bfloat16),
+                    bq.HowToQuantize(qtype='int8', channelwise_axes=[0]))
+  finally:
+    bdg.DECODE_MAX_ROWS = old
+    L.qwx_set_programmatic_launch(0)
+  assert L.qwx_get_programmatic_launch() == 0
+  assert torch.equal(again, got) and q.qvalue.shape == (64, 4096)
   assert L.qwx_gemm_q8_decode_workspace_bytes(129, 512) == 0
   x = torch.zeros(16, dtype=torch.uint8, device='cuda')
   args = (_lib.ptr(x), _lib.ptr(x), 200, 512, 1024, None, None, _lib.F32, _lib.ptr(x), _lib.S32, 0,
