@@ -295,6 +295,21 @@ int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, vo
                                   const void* weight, double eps, int64_t rows, int64_t d,
                                   void* x_out, void* y_out, void* q, void* scale,
                                   int32_t* error_flag, int64_t wait_cycles, qwx_stream_t stream);
+/* The all-reduce of such partials on its own, in place, for many rows (a prefill chunk): rank
+ * r sums its share of the rows over all ranks' buffers (float32, rank order, one rounding to
+ * bf16) and writes the sums into the same rows of every rank's buffer with plain peer stores,
+ * so (world - 1) / world of the tensor crosses NVLink in each direction instead of
+ * (world - 1) x the tensor inbound.  When the call has completed on a rank, that rank's buffer
+ * [rows, d] holds the reduced tensor (what an all-reduce delivers), for an ordinary local
+ * consumer such as qwx_add_rmsnorm_quantize.  partials[r] / flags[r]: rank r's buffers as
+ * mapped in this process; flags[r]: int32 [(max_ctas + 1) * world], launches: int32
+ * [max_ctas + 2], all zero before the first call; every rank makes the same sequence of calls
+ * with the same rows.  Waits are bounded by wait_cycles (<= 0: about two seconds); if a peer
+ * never arrives the call reports QWX_ERR_DEVICE_WAIT through error_flag.  No counterpart in the
+ * reference (GSPMD inserts the all-reduce there, flax_util.py:354-357). */
+int qwx_peer_allreduce(void* const* partials, void* const* flags, int world, int rank,
+                       int* launches, int max_ctas, int64_t rows, int64_t d, int32_t* error_flag,
+                       int64_t wait_cycles, qwx_stream_t stream);
 int qwx_silu_mul_quantize(const void* gu, int64_t rows, int64_t f, void* y_out, void* q,
                           void* scale, qwx_stream_t stream);
 /* Greedy sampling over the logits a (column-parallel) lm_head projection produced: for every

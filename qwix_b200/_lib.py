@@ -66,6 +66,7 @@ _SIGNATURES = {
     'qwx_add_rmsnorm_quantize': (_int, [_vp, _vp, _vp, _dbl, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     'qwx_add_rmsnorm_quantize_peer': (_int, [_vp, _vp, _vp, _int, _int, _vp, _int, _vp, _dbl, _i64, _i64,
                                              _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    'qwx_peer_allreduce': (_int, [_vp, _vp, _int, _int, _vp, _int, _i64, _i64, _vp, _i64, _vp]),
     'qwx_silu_mul_quantize': (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     'qwx_argmax_rows_workspace_bytes': (_sz, [_i64, _i64]),
     'qwx_argmax_rows': (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),

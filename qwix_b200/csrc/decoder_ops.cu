@@ -258,13 +258,21 @@ add_rmsnorm_peer_kernel(const uint4* __restrict__ x, const PeerArgs pa,
     for (int it = 0; it < kDVec; ++it) {
       const int vi = tid + it * kDThreads;
       if (vi >= nvec) continue;
-      // sum of the ranks' partials in rank order, float32, rounded once to bf16
-      float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < pa.world; ++r) {
-        float b[8];
-        unpack_bf16x8(__ldcg(pa.partial[r] + row * nvec + vi), b);
+      // sum of the ranks' partials in rank order, float32, rounded once to bf16; all ranks'
+      // loads are issued before the first sum (a peer load takes microseconds)
+      uint4 got[kMaxPeers];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) d[j] = __fadd_rn(d[j], b[j]);
+      for (int r = 0; r < kMaxPeers; ++r)
+        if (r < pa.world) got[r] = __ldcg(pa.partial[r] + row * nvec + vi);
+      float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < pa.world) {
+          float b[8];
+          unpack_bf16x8(got[r], b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) d[j] = __fadd_rn(d[j], b[j]);
+        }
       }
       float a[8];
       unpack_bf16x8(x[row * nvec + vi], a);
@@ -310,6 +318,125 @@ add_rmsnorm_peer_kernel(const uint4* __restrict__ x, const PeerArgs pa,
       if (vi >= nvec) continue;
       const uint32_t w[4] = {cur[it].x, cur[it].y, cur[it].z, cur[it].w};
       q[row * nvec + vi] = rq.codes(w);
+    }
+  }
+}
+
+// ---- all-reduce of the partials in place, for many rows -------------------------------------
+//
+// The kernel above lets every rank read every partial: (world - 1) x the tensor crosses NVLink
+// into each GPU, which is the right trade for the 256 KB of a decode step but not for a prefill
+// chunk of 64 MB.  Here rank r sums only its share of the rows (reading world - 1 remote
+// slices), rounds once to bf16 and writes the sums back into the same rows of EVERY rank's
+// buffer (plain peer stores): (world - 1) / world of the tensor in and the same out, both
+// directions of the links busy at once, and afterwards each rank holds the reduced tensor in
+// its own memory for an ordinary local consumer.  In place is safe: a thread reads all ranks'
+// copies of a vector before it overwrites them, and no other rank touches those rows.
+//
+// Two hand-shakes, both bounded: per CTA before the first read (every rank's GEMM has
+// finished, as above), and per rank at the end -- the CTA that finishes last tells every peer
+// "my sums are in your buffer" and does not leave before all peers have said the same, so the
+// end of the kernel on a rank means its buffer is complete.
+struct PeerReduceArgs {
+  uint4* partial[kMaxPeers];   // every rank's buffer, as mapped here
+  int* flags[kMaxPeers];       // every rank's flags: [ctas][world] ready marks, then [world] done marks
+  int* launches;               // this rank: [ctas] launch counts, a finished-CTA counter, a call count
+  int world, rank, max_ctas;
+  int32_t* error_flag;
+  long long wait_cycles;
+};
+
+__device__ __forceinline__ bool wait_flag(const int* flag, int count, long long budget) {
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= count) return true;
+    if ((it & 255u) == 0 && clock64() - t0 > budget) return false;
+  }
+}
+
+__global__ void __launch_bounds__(kDThreads)
+peer_allreduce_kernel(const PeerReduceArgs pa, int64_t rows, int nvec) {
+  __shared__ int s_count, s_ok, s_last;
+  const int tid = threadIdx.x;
+  griddep_launch_dependents();
+  griddep_wait();       // this rank's GEMM has finished: its partial is complete
+  if (tid == 0) {
+    s_count = ++pa.launches[blockIdx.x];
+    s_ok = 1;
+  }
+  __syncthreads();
+  const int count = s_count;
+  if (tid < pa.world && tid != pa.rank) {
+    __threadfence_system();
+    int* theirs = pa.flags[tid] + (size_t)blockIdx.x * pa.world + pa.rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(count) : "memory");
+    if (!wait_flag(pa.flags[pa.rank] + (size_t)blockIdx.x * pa.world + tid, count, pa.wait_cycles)) {
+      s_ok = 0;
+      if (pa.error_flag) atomicExch(pa.error_flag, QWX_ERR_DEVICE_WAIT);
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    const int64_t row0 = rows * pa.rank / pa.world, row1 = rows * (pa.rank + 1) / pa.world;
+    const int64_t vec0 = row0 * nvec, vec1 = row1 * nvec;
+    // two vectors per thread and step, all ranks' loads issued before the first sum: a peer
+    // load takes microseconds, so the bytes in flight decide the rate
+    const int64_t stride = (int64_t)gridDim.x * kDThreads;
+    for (int64_t v = vec0 + (int64_t)blockIdx.x * kDThreads + tid; v < vec1; v += 2 * stride) {
+      const int64_t v2 = v + stride;
+      const bool two = v2 < vec1;
+      uint4 got[2][kMaxPeers];
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < pa.world) {
+          got[0][r] = __ldcg(pa.partial[r] + v);
+          if (two) got[1][r] = __ldcg(pa.partial[r] + v2);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (h == 1 && !two) break;
+        float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {          // rank order, float32, one rounding
+          if (r < pa.world) {
+            float b[8];
+            unpack_bf16x8(got[h][r], b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d[j] = __fadd_rn(d[j], b[j]);
+          }
+        }
+        const uint4 u = make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]),
+                                   pack_bf16(d[6], d[7]));
+        const int64_t at = h ? v2 : v;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+          if (r < pa.world) pa.partial[r][at] = u;
+      }
+    }
+  }
+  // the rank's last CTA exchanges "done" marks with the peers
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    int* finished = pa.launches + pa.max_ctas;
+    s_last = atomicAdd(finished, 1) == (int)gridDim.x - 1;
+    if (s_last) *finished = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // the done marks carry the number of this call (every rank makes the same sequence of calls)
+  if (tid == 0) s_count = ++pa.launches[pa.max_ctas + 1];
+  __syncthreads();
+  const int call = s_count;
+  if (tid < pa.world && tid != pa.rank) {
+    __threadfence_system();
+    int* done_there = pa.flags[tid] + (size_t)pa.max_ctas * pa.world + pa.rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(done_there), "r"(call) : "memory");
+    if (!wait_flag(pa.flags[pa.rank] + (size_t)pa.max_ctas * pa.world + tid, call, pa.wait_cycles)) {
+      if (pa.error_flag) atomicExch(pa.error_flag, QWX_ERR_DEVICE_WAIT);
     }
   }
 }
@@ -632,6 +759,57 @@ int qwx_add_rmsnorm_quantize_peer(const void* x, const void* const* partials, vo
   if (launch_dependent(add_rmsnorm_peer_kernel, dim3(grid), dim3(kDThreads), 0, (cudaStream_t)stream,
                        (const uint4*)x, pa, (const uint4*)weight, (float)eps, rows, (int)(d / 8),
                        (uint4*)x_out, (uint4*)y_out, (uint2*)q, (__nv_bfloat16*)scale) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return QWX_ERR_LAUNCH;
+  }
+  return QWX_OK;
+}
+
+static int peer_reduce_resident_ctas() {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int cached[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int per_sm = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, peer_allreduce_kernel, kDThreads, 0) !=
+            cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      return 0;
+    cached[dev] = per_sm * sms;
+  }
+  return cached[dev];
+}
+
+int qwx_peer_allreduce(void* const* partials, void* const* flags, int world, int rank,
+                       int* launches, int max_ctas, int64_t rows, int64_t d, int32_t* error_flag,
+                       int64_t wait_cycles, qwx_stream_t stream) {
+  if (!partials || !flags || !launches) return QWX_ERR_NULL;
+  if (world < 2 || world > kMaxPeers || rank < 0 || rank >= world || max_ctas <= 0) return QWX_ERR_SHAPE;
+  if (rows <= 0 || d <= 0 || d % 8) return QWX_ERR_SHAPE;
+  PeerReduceArgs pa;
+  for (int r = 0; r < world; ++r) {
+    if (!partials[r] || !flags[r]) return QWX_ERR_NULL;
+    if (reinterpret_cast<uintptr_t>(partials[r]) & 15) return QWX_ERR_ALIGN;
+    pa.partial[r] = (uint4*)partials[r];
+    pa.flags[r] = (int*)flags[r];
+  }
+  pa.launches = launches;
+  pa.world = world; pa.rank = rank; pa.max_ctas = max_ctas;
+  pa.error_flag = error_flag;
+  pa.wait_cycles = wait_cycles > 0 ? wait_cycles : kPeerWaitCycles;
+  // Every rank launches the same number of CTAs, all resident (the first hand-shake is per
+  // CTA): a function of the row count only, bounded by the flag capacity and the occupancy.
+  const int resident = peer_reduce_resident_ctas();
+  if (resident <= 0) return QWX_ERR_NO_DEVICE;
+  const int64_t vecs_per_rank = (rows / world + 1) * (d / 8);
+  int64_t want = (vecs_per_rank + kDThreads - 1) / kDThreads;
+  const int64_t cap = max_ctas < resident ? max_ctas : resident;
+  const unsigned grid = (unsigned)(want < cap ? (want < 1 ? 1 : want) : cap);
+  if (launch_dependent(peer_allreduce_kernel, dim3(grid), dim3(kDThreads), 0, (cudaStream_t)stream, pa,
+                       rows, (int)(d / 8)) != cudaSuccess) {
     (void)cudaGetLastError();
     return QWX_ERR_LAUNCH;
   }

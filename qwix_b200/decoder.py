@@ -408,8 +408,12 @@ class Decoder(torch.nn.Module):
           x, delta = blk.forward_fused(x, delta, self.cos, self.sin, ck, cv, pos, mask)
       finally:
         self.comm.peer_active = False
-      if isinstance(delta, fused.PeerPartial):   # the last layer's MLP output: plain all-reduce
-        delta = delta.all_reduce(self.comm)
+      if isinstance(delta, fused.PeerPartial):   # the last layer's MLP output
+        rows = delta.local.numel() // delta.shape[-1]
+        delta = (delta.reduce_in_place()
+                 if (rows >= fused.AddRmsNorm.REDUCE_ROWS
+                     and self.comm.size >= fused.AddRmsNorm.REDUCE_WORLD)
+                 else delta.all_reduce(self.comm))
       if last_only:
         x, delta = x[:, -1:], delta[:, -1:]
       x = fused.AddRmsNorm(x, delta, self.final_norm.scale, self.final_norm.eps)

@@ -210,3 +210,64 @@ def test_argmax_rows_matches_library(shape):
     first = (x.float() == want_val[:, None]).float().argmax(dim=-1)
     assert torch.equal(idx, first + 1000)
   assert torch.equal(fused.argmax_rows(x), first)
+
+
+@pytest.mark.parametrize('rows,d,world', [(8192, 512, 2), (1030, 1024, 4), (4099, 256, 8), (3, 4096, 2)])
+def test_peer_allreduce_in_place_one_gpu(rows, d, world):
+  """Every "rank" runs on this GPU, one after the other, with the marks its peers would have
+  raised written beforehand: rank r sums its share of the rows and writes the sums into all
+  buffers; after the last rank every buffer holds the all-reduced tensor."""
+  import ctypes
+  from qwix_b200 import _lib
+  max_ctas = 148 * 8
+  g = torch.Generator(device='cuda').manual_seed(rows + d)
+  parts = [torch.randn((rows, d), device='cuda', generator=g).to(torch.bfloat16) for _ in range(world)]
+  total = parts[0].float()
+  for p in parts[1:]:
+    total = total + p.float()                 # rank order, float32
+  want = total.to(torch.bfloat16)
+  flags = [torch.zeros((max_ctas + 1) * world, dtype=torch.int32, device='cuda') for _ in range(world)]
+  launches = [torch.zeros(max_ctas + 2, dtype=torch.int32, device='cuda') for _ in range(world)]
+  arr = ctypes.c_void_p * world
+  part_ptrs = arr(*[p.data_ptr() for p in parts])
+  flag_ptrs = arr(*[f.data_ptr() for f in flags])
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  for call in (1, 2):
+    if call == 2:                             # a second exchange through the same marks
+      for p in parts:
+        p.copy_(torch.randn((rows, d), device='cuda', generator=g).to(torch.bfloat16))
+      total = parts[0].float()
+      for p in parts[1:]:
+        total = total + p.float()
+      want = total.to(torch.bfloat16)
+    for r in range(world):
+      flags[r].fill_(call)                    # "all peers are ready and done" for this call
+      _lib.check(_lib.lib().qwx_peer_allreduce(
+          part_ptrs, flag_ptrs, world, r, _lib.ptr(launches[r]), max_ctas, rows, d, _lib.ptr(err), 0,
+          _lib.stream_ptr()), 'peer_allreduce')
+      torch.cuda.synchronize()
+      assert int(err.item()) == 0
+      lo, hi = rows * r // world, rows * (r + 1) // world
+      for p in parts:                         # rank r's rows are reduced everywhere
+        assert torch.equal(p[lo:hi], want[lo:hi])
+    for p in parts:
+      assert torch.equal(p, want)
+    assert all(int(l[max_ctas + 1].item()) == call and int(l[max_ctas].item()) == 0 for l in launches)
+
+
+def test_peer_allreduce_done_wait_runs_out():
+  import ctypes
+  from qwix_b200 import _lib
+  max_ctas, world, rows, d = 148 * 8, 2, 64, 512
+  parts = [torch.ones((rows, d), dtype=torch.bfloat16, device='cuda') for _ in range(world)]
+  flags = [torch.zeros((max_ctas + 1) * world, dtype=torch.int32, device='cuda') for _ in range(world)]
+  flags[0][:max_ctas * world].fill_(1)        # the peer is ready, but never says "done"
+  launches = torch.zeros(max_ctas + 2, dtype=torch.int32, device='cuda')
+  arr = ctypes.c_void_p * world
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  _lib.check(_lib.lib().qwx_peer_allreduce(
+      arr(*[p.data_ptr() for p in parts]), arr(*[f.data_ptr() for f in flags]), world, 0,
+      _lib.ptr(launches), max_ctas, rows, d, _lib.ptr(err), 2_000_000, _lib.stream_ptr()), 'peer_allreduce')
+  torch.cuda.synchronize()
+  assert int(err.item()) == 8                 # QWX_ERR_DEVICE_WAIT: reported, the context lives on
+  assert bool((parts[0][:32] == 2).all()) and bool((parts[1][:32] == 2).all())
