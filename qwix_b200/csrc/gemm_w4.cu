@@ -40,14 +40,15 @@ namespace {
 constexpr int kStrip = 16;          // channels per work item: the M of mma.m16n8k16
 constexpr int kChunkK = 128;        // K per work item: eight K16 tiles, 2 x 16 bytes per lane, one scale
 constexpr int kScaleK = 128;        // partial sums are scaled every 128 K
-constexpr int kW4Warps = 16;
-constexpr int kW4Threads = kW4Warps * 32;
+// Warps per CTA: 32 for up to 8 tokens (few registers per thread, and twice the warps hide the
+// latency of the dependent MMAs of a chunk), 16 beyond.
+__host__ __device__ constexpr int w4_warps(int nt) { return nt == 1 ? 32 : 16; }
 constexpr size_t kSmemCap = 226 * 1024;
 // Chunks (1 KB each) a warp keeps in flight in its private cp.async ring: loaded HBM latency is
 // a few microseconds, so an SM needs on the order of 100 KB in flight to stream at its share
 // of the bandwidth.  More tokens leave less room beside the activation slice.
-__host__ __device__ constexpr int w4_depth(int nt) { return nt == 1 ? 8 : (nt == 2 ? 6 : 4); }
-__host__ __device__ constexpr size_t w4_ring_bytes(int nt) { return (size_t)kW4Warps * w4_depth(nt) * 1024; }
+__host__ __device__ constexpr int w4_depth(int nt) { return nt == 1 ? 4 : (nt == 2 ? 6 : 4); }
+__host__ __device__ constexpr size_t w4_ring_bytes(int nt) { return (size_t)w4_warps(nt) * w4_depth(nt) * 1024; }
 
 struct W4Params {
   const uint4* wp;        // packed chunks, [N / 16][K / 128][2][32 lanes] x 16 bytes
@@ -104,7 +105,9 @@ __device__ __forceinline__ float load_scale_w4(const void* p, int dtype, int64_t
 }
 
 template <int NT>   // token tiles of 8: the activation is padded to NT * 8 rows
-__global__ void __launch_bounds__(kW4Threads, 1) gemm_w4_kernel(const W4Params p) {
+__global__ void __launch_bounds__(w4_warps(NT) * 32, 1) gemm_w4_kernel(const W4Params p) {
+  constexpr int kW4Warps = w4_warps(NT);
+  constexpr int kW4Threads = kW4Warps * 32;
   extern __shared__ __align__(16) uint8_t act[];
   constexpr int MPAD = NT * 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -456,9 +459,9 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
     p.counters = (int*)((char*)workspace + M * N * 4);
     const int grid = (sms / split) * split;
     const size_t smem = (size_t)nt * 8 * p.pitch + w4_ring_bytes(nt);
-    if (nt == 1) gemm_w4_kernel<1><<<grid, kW4Threads, smem, st>>>(p);
-    else if (nt == 2) gemm_w4_kernel<2><<<grid, kW4Threads, smem, st>>>(p);
-    else gemm_w4_kernel<4><<<grid, kW4Threads, smem, st>>>(p);
+    if (nt == 1) gemm_w4_kernel<1><<<grid, w4_warps(1) * 32, smem, st>>>(p);
+    else if (nt == 2) gemm_w4_kernel<2><<<grid, w4_warps(2) * 32, smem, st>>>(p);
+    else gemm_w4_kernel<4><<<grid, w4_warps(4) * 32, smem, st>>>(p);
     QWX_CHECK_LAUNCH();
   }
   return QWX_OK;
