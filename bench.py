@@ -60,7 +60,8 @@ NSETS = 3  # buffer sets cycled through so that no step finds its inputs in the 
 DN = (((1,), (0,)), ((), ()))
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of the named kernel
-# (the summaries under profiles/ give the commands).  A figure is reported only while the
+# (ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -k regex:<kernel> on this script
+# with --workload gemm --steps 2 --warmup 3).  A figure is reported only while the
 # kernel's source is the one that was profiled (sha1 of the listed files, first 12 hex digits).
 NCU_DRAM_TRAFFIC = {
     'gemm_q8_pair_kernel<i8>': {
@@ -954,6 +955,9 @@ def main():
   ap.add_argument('--warmup', type=int, default=20)
   ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
   ap.add_argument('--no-cpu-baseline', action='store_true')
+  ap.add_argument('--no-library-peaks', action='store_true',
+                  help='skip timing the vendor int8 / fp8 GEMMs (profiling aid: they dominate a '
+                       'launch list)')
   ap.add_argument('--m', type=int, default=None,
                   help='token rows per step (profiling aid; the benchmark uses its own sizes)')
   ap.add_argument('--workload', default='all', choices=['all', 'gemm', 'decoder', 'w4', 'hadamard'],
@@ -997,7 +1001,7 @@ def main():
 
   with_cpu = world == 1 and not args.no_cpu_baseline
   lib_peaks = {}
-  if rank == 0 and args.workload in ('all', 'gemm', 'hadamard', 'decoder'):
+  if rank == 0 and not args.no_library_peaks and args.workload in ('all', 'gemm', 'hadamard', 'decoder'):
     lib_peaks = library_peaks(device, sustain_s=4.0 if args.workload in ('all', 'gemm') else 0.0)
   if dist is not None:
     dist.barrier()

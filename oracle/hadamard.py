@@ -66,7 +66,7 @@ def quantize_a_tile(x: np.ndarray, axis: int, qtype='int8'):
 def hadamard_quantized_matmul(a: np.ndarray, w: np.ndarray, *, block=128,
                               qtype='float8_e4m3fn', out_dtype=None,
                               mode=qarray.STRICT):
-  """BASELINE config: rotate both operands per K block (A.H and H.W/block),
+  """The benchmarked configuration: rotate both operands per K block (A.H and H.W/block),
   quantize A per row and W per column with absmax, contract the codes with
   float32 accumulation, scale, round to the output dtype.
 

@@ -1,6 +1,6 @@
 """Llama-shaped decoder whose projections run through the quantized path, tensor-parallel.
 
-This is the workload of BASELINE configs[4]: every Dense of the decoder is issued through
+This is the decoder workload of the benchmark (Llama-3-8B shape): every Dense of the decoder is issued through
 qwix_b200.ops, so under `quantize_model(model, PtqProvider(w8a8 rule))` each projection is a
 per-token int8 activation quantization plus one int8 tcgen05 GEMM with the scales fused in its
 epilogue.  Everything that is not a contraction with a weight (RMSNorm, RoPE, the attention

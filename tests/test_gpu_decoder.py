@@ -1,4 +1,4 @@
-"""GPU: the w8a8 decoder (BASELINE configs[4] architecture, cut down to two layers) against a
+"""GPU: the w8a8 decoder (Llama-3-8B architecture, cut down to two layers) against a
 NumPy oracle decoder, decode steps against prefill, and tensor-parallel against single-GPU."""
 
 import os

@@ -243,7 +243,7 @@ def test_w8a8_dot_general_matches_oracle(qtype, dtype):
   assert got.dtype == h.to_torch(want[:1]).dtype
   g = h.to_numpy(got).astype(np.float32)
   r = want.astype(np.float32)
-  # BASELINE tolerance for dequantized outputs: max-abs 1e-2 or rel 2e-2.
+  # Stated tolerance for dequantized outputs: max-abs 1e-2 or rel 2e-2.
   assert np.all(np.abs(g - r) <= 1e-2 + 2e-2 * np.abs(r))
   if qtype == 'int8':
     # Reference-order epilogue: bit-exact with the strict oracle.

@@ -67,7 +67,7 @@ def test_rotate_quantize_matches_oracle(qtype, shape):
 
 @pytest.mark.parametrize('mkn', [(256, 1024, 512), (300, 4096, 768)])
 def test_hadamard_quantized_matmul(mkn):
-  # BASELINE configs[3] at reduced size: Student-t activations, N(0, 0.02) weights, fp8 e4m3,
+  # The benchmarked Hadamard workload at reduced size: Student-t activations, N(0, 0.02) weights, fp8 e4m3,
   # absmax per row / per column, float32 accumulation, bf16 out; rel-L2 <= 1e-2.
   M, K, N = mkn
   a = _student_t((M, K), 5)

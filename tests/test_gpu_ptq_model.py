@@ -1,4 +1,4 @@
-"""GPU: BASELINE configs[0] -- the README MLP under PtqProvider (w8a8), end to end through the
+"""GPU: the README MLP (Dense 16->64, ReLU, Dense 64->16) under PtqProvider (w8a8), end to end through the
 provider / model wrapper / quantize_params, against the CPU oracle on the same weights."""
 
 import ml_dtypes
