@@ -431,6 +431,15 @@ int sm_count_t() {
 }
 
 }  // namespace
+
+// gemm_q8_tiled_pair.cu
+int gemm_q8_tiled_pair_launch(const void* a, const void* b, int code_dtype, int b_layout,
+                              int64_t M, int64_t N, int64_t K, int64_t k_tile, const void* sa,
+                              int sa_tiled, const void* sb, int sb_tiled, int scale_dtype,
+                              const int32_t* corr_row, const int32_t* corr_col, void* out,
+                              int out_dtype, int epilogue, int32_t* error_flag, int sms,
+                              cudaStream_t st);
+
 }  // namespace qwx
 
 using namespace qwx;
@@ -484,6 +493,15 @@ extern "C" int qwx_gemm_q8_tiled(const void* a, const void* b, int code_dtype, i
   if (K % 16) return QWX_ERR_ALIGN;
   if (b_layout == QWX_B_KN && (N % 16)) return QWX_ERR_ALIGN;
   if (reinterpret_cast<uintptr_t>(out) & 15) return QWX_ERR_ALIGN;
+
+  // More than one 128-row tile: 256 x 256 tiles on CTA pairs.
+  if (M > TM) {
+    const int sms_pair = sm_count_t();
+    if (sms_pair <= 0) return QWX_ERR_NO_DEVICE;
+    return gemm_q8_tiled_pair_launch(a, b, code_dtype, b_layout, M, N, K, k_tile, sa, sa_tiled, sb,
+                                     sb_tiled, scale_dtype, corr_row, corr_col, out, out_dtype,
+                                     epilogue, error_flag, sms_pair, (cudaStream_t)stream);
+  }
 
   CUtensorMap ta, tb;
   if (!get_encode_tiled()) return QWX_ERR_NO_DEVICE;
