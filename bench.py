@@ -460,6 +460,65 @@ def w4_records(args, device, with_cpu: bool):
 
 
 # ---------------------------------------------------------------------------------------------
+# Sub-channel w8a8 dot_general: both operands carry one scale per K tile (`tile_size` rules)
+# ---------------------------------------------------------------------------------------------
+
+def subchannel_records(args, device, lib_peaks: dict):
+  """A [M, 8192] x W [8192, 8192] with int8 codes and a scale per 128 / 256 / 512 contracted
+  elements on both sides (dot_general.py:187-203, :255-259), through the public dot_general on
+  already-quantized operands; the kernel is `gemm_q8_tiled_pair_kernel`."""
+  import ml_dtypes
+  from oracle import dot_general as odg
+  from oracle import qarray as oq
+  from qwix_b200 import _lib
+  from qwix_b200.core import dot_general as bdg
+  from qwix_b200.core import qarray as bq
+  Ms, Ks, Ns = (args.m or 4096), 8192, 8192
+  peaks = _peaks()
+  peak = lib_peaks.get('int8_burst') or 2 * peaks['bf16_tflops']
+  steps = max(10, min(args.steps, 40))
+  gen = torch.Generator(device).manual_seed(11)
+  acts = [torch.randn(Ms, Ks, device=device, dtype=torch.bfloat16, generator=gen) for _ in range(2)]
+  wts = [torch.randn(Ks, Ns, device=device, dtype=torch.bfloat16, generator=gen) * 0.02 for _ in range(2)]
+  rows = np.arange(0, Ms, max(1, Ms // 32))[:32]
+  records = []
+  for tile in (128, 256, 512):
+    kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=tile, qtype='int8')
+    aq = [bq.quantize(a, bdg.get_how_to_quantize(for_lhs=True, **kw)) for a in acts]
+    wq = [bq.quantize(w, bdg.get_how_to_quantize(for_lhs=False, **kw)) for w in wts]
+    # two operand sets (2 x 96 MB of codes) + the bf16 output: 256 MB cycled, above the 126 MB L2
+    ms = _time_calls(lambda i: bdg.dot_general(aq[i % 2], wq[i % 2], DN), steps, max(args.warmup, 3))
+    _lib.raise_on_device_error()
+    got = _np(bdg.dot_general(aq[0], wq[0], DN)[torch.as_tensor(rows, device=device)])
+    a_o = oq.quantize(_np(acts[0][torch.as_tensor(rows, device=device)]), odg.get_how_to_quantize(for_lhs=True, **kw))
+    import dataclasses
+    w_o = oq.QArray(_np(wq[0].qvalue), _np(wq[0].scale).astype(np.float32), None, 'int8')
+    a_w = dataclasses.replace(a_o, scale=a_o.scale.astype(np.float32))
+    verified = _tolerance_report(got, odg.dot_general(a_w, w_o, DN))
+    verified.update({'rows': int(rows.size), 'against': 'oracle dot_general on the device\'s weight codes, '
+                     'float32 scales (the float32 epilogue\'s contract)',
+                     'act_codes_bit_exact': bool(np.array_equal(
+                         _np(aq[0].qvalue[torch.as_tensor(rows, device=device)]), a_o.qvalue.astype(np.int8)))})
+    achieved = 2.0 * Ms * Ns * Ks / (ms * 1e-3) / 1e12
+    records.append({
+        'M': Ms, 'K': Ks, 'N': Ns, 'k_tile': tile, 'ms_per_step': ms, 'steps': steps,
+        'value': achieved, 'unit': 'TOPS', 'l2': '2 operand sets + output (256 MB) cycled',
+        'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TOP/s',
+                     'frac': achieved / peak, 'traffic': None,
+                     'frac_of_sustained': (achieved / lib_peaks['int8_sustained']) if lib_peaks.get('int8_sustained') else None,
+                     'kernel': 'gemm_q8_tiled_pair_kernel<i8>',
+                     'epilogue_floor': 'per K tile and SM: 128 x 256 values x (3 float32 operations + 1 integer '
+                                       'add) on 128 lanes per clock = 1024 clocks, against 4 x k_tile clocks of MMA',
+                     'peak_source': ('torch._int_mm at 8192^3, best of 10, measured in this run (burst)'
+                                     if lib_peaks.get('int8_burst') else
+                                     f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})")},
+        'verified': verified, 'gpu_launches': steps,
+    })
+    del aq, wq
+  return records
+
+
+# ---------------------------------------------------------------------------------------------
 # Hadamard-quantized fp8 matmul: A [8192, 4096] x W [4096, 14336], 128-point blocks along K
 # ---------------------------------------------------------------------------------------------
 
@@ -960,7 +1019,7 @@ def main():
                        'launch list)')
   ap.add_argument('--m', type=int, default=None,
                   help='token rows per step (profiling aid; the benchmark uses its own sizes)')
-  ap.add_argument('--workload', default='all', choices=['all', 'gemm', 'decoder', 'w4', 'hadamard'],
+  ap.add_argument('--workload', default='all', choices=['all', 'gemm', 'decoder', 'w4', 'hadamard', 'subchannel'],
                   help="'all' (default): the headline GEMM step plus the decoder / w4 / hadamard "
                        'records in one line; the others run one workload alone')
   ap.add_argument('--layers', type=int, default=32)
@@ -1001,8 +1060,8 @@ def main():
 
   with_cpu = world == 1 and not args.no_cpu_baseline
   lib_peaks = {}
-  if rank == 0 and not args.no_library_peaks and args.workload in ('all', 'gemm', 'hadamard', 'decoder'):
-    lib_peaks = library_peaks(device, sustain_s=4.0 if args.workload in ('all', 'gemm') else 0.0)
+  if rank == 0 and not args.no_library_peaks and args.workload in ('all', 'gemm', 'hadamard', 'decoder', 'subchannel'):
+    lib_peaks = library_peaks(device, sustain_s=4.0 if args.workload in ('all', 'gemm', 'subchannel') else 0.0)
   if dist is not None:
     dist.barrier()
 
@@ -1023,6 +1082,13 @@ def main():
       line['w4'] = recs
     else:
       line = {'metric': 'int4 weight-only GEMM GB/s', 'n_gpus': 1, 'data': 'synthetic', 'w4': recs}
+    torch.cuda.empty_cache()
+  if world == 1 and args.workload in ('all', 'subchannel'):
+    recs = subchannel_records(args, device, lib_peaks)
+    if line is not None and args.workload == 'all':
+      line['subchannel'] = recs
+    else:
+      line = {'metric': 'sub-channel w8a8 GEMM TOPS', 'n_gpus': 1, 'data': 'synthetic', 'subchannel': recs}
     torch.cuda.empty_cache()
   if world == 1 and args.workload in ('all', 'hadamard'):
     rec = hadamard_record(args, device, with_cpu, lib_peaks)

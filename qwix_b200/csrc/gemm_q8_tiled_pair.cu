@@ -6,21 +6,31 @@
 //
 // (qwix/_src/core/dot_general.py:187-203 tiled contraction, :228-253 zero-point terms, :255-259
 // scale and sum over tiles, :278-399 the loop form.)  Two CTAs on the two SMs of a TPC compute
-// one 256 x 256 output tile: each holds 128 rows of A and 128 columns of B per K block (32 KB
-// instead of the 32 KB a 128 x 128 tile needs for a quarter of the products), and 128
-// accumulator rows x 256 columns in tensor memory, twice: the tensor cores fill one
-// accumulator with K tile t+1 while the epilogue warps drain K tile t from the other.
+// one 256 x 256 output tile: each holds 128 rows of A and 128 columns of B per K block (the
+// 32 KB a 128 x 128 tile needs, for twice the products per SM), and 128 accumulator rows x
+// 256 columns in tensor memory, twice: the tensor cores fill one accumulator with K tile t+1
+// while the epilogue warps drain K tile t from the other.
 //
-// The epilogue is the pace-setter when the K tile is short, so it is written for issue slots:
+// The epilogue is the pace-setter when the K tile is short, so it is written for issue slots
+// and for the float32 pipe (three float operations and one integer add per value on 128 lanes
+// per clock: 1024 clocks per K tile is its floor, twice the 512 the MMAs of a 128-wide K tile take):
 //   * eight epilogue warps per CTA, two per tensor-memory lane quarter, 128 columns each; a
-//     thread owns one output row and keeps 128 running float32 sums in registers (the
-//     register file is re-split with setmaxnreg: 232 per epilogue thread, 40 per control thread);
+//     thread owns one output row and keeps 128 running float32 sums in registers (the CTA's
+//     registers are re-split with setmaxnreg: 232 per epilogue thread, 40 per control thread,
+//     which adds up to the 168 per thread the CTA was launched with);
 //   * the variant is a template parameter, not a run-time branch in the inner loop;
-//   * int32 -> float32 through the exact magic-number add where |acc| < 2^22 is guaranteed;
-//   * the three float operations per value (subtract the magic, times sa, multiply-add with
-//     sb) are the packed two-lane forms (add/mul/fma .f32x2), rounding as the scalar forms do;
-//   * scales of a K tile are staged per warp in shared memory by the lanes that prefetched
-//     them one K tile ahead, and read back four at a time.
+//   * int8 with |acc| <= 2^22 guaranteed: int32 -> float32 by the exact magic-number add,
+//     for 128-wide K tiles alternating with cvt, which runs on another pipe (527 -> 459 us at
+//     4096 x 8192 x 8192; with 256-wide tiles the plain form is ahead, 308 vs 319 us)
+//     (starting the accumulators at the magic bits, restored with tcgen05.st after each drain,
+//     saves the integer add but measured slower: the hand-back then waits for the stores);
+//   * the three float operations per value (subtract, times sa, multiply-add with sb) are
+//     the packed two-lane forms (add/mul/fma .f32x2): half the issue slots, same rounding;
+//   * tensor-memory loads are double-buffered, and the scales of the next K tile are fetched
+//     and this one's staged in shared memory while the first load is in flight;
+//   * the hand-back of an accumulator is a relaxed arrive: what it orders is the tensor-memory
+//     traffic, which tcgen05.wait and tcgen05.fence order; a release at cluster scope would
+//     also wait for the scale loads in flight, once per K tile.
 //
 // Per CTA: warp 0 TMA producer, warp 1 MMA issuer (even CTA only), warp 2 owns the pair's
 // tensor-memory allocation, warps 4-11 epilogue.  Barriers as in gemm_q8_pair.cu, acc_full once
@@ -62,6 +72,9 @@ constexpr int kModeCvt = 1;        // cvt (int8) or float accumulators, no zero 
 constexpr int kModeCorr = 2;       // int8 with the rank-1 zero-point term, cvt
 constexpr int kModeRef = 3;        // the reference's rounding after every step
 constexpr int kModeRefCorr = 4;
+constexpr int kModeMix = 5;        // as kModeFast, every other group of four through cvt: the two
+                                   // conversions run on different pipes, and with a 128-wide K tile
+                                   // the epilogue is what the tile waits for
 
 struct ControlQ {
   uint64_t full[kQStages];
@@ -70,8 +83,8 @@ struct ControlQ {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort;
-  alignas(16) float sb[kQEpiWarps][2][QNH];    // per epilogue warp, double-buffered per K tile
-  alignas(16) int32_t zc[kQEpiWarps][2][QNH];
+  alignas(16) float sb[kQEpiWarps][QNH];    // per epilogue warp: the scales of the K tile being drained
+  alignas(16) int32_t zc[kQEpiWarps][QNH];
 };
 
 constexpr size_t kQSmemBytes = 1024 + (size_t)kQStages * kQStageBytes + sizeof(ControlQ);
@@ -91,6 +104,7 @@ struct TiledPairParams {
   int out_dtype;
   int32_t* error_flag;
   int tiles_m, tiles_n;     // 256 x 256 tiles
+  int scale_vec;            // four scales / corrections of consecutive columns load as one vector
 };
 
 __device__ __forceinline__ float load_scale_q(const void* p, int dtype, int64_t i) {
@@ -114,6 +128,26 @@ __device__ __forceinline__ void regs_claim() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
 }
 
+constexpr uint32_t kMagicBits = 0x4B400000u;      // float32 1.5 * 2^23
+constexpr float kMagic = 12582912.0f;
+
+// tcgen05.wait::ld that names the registers the load fills, so that no use of them is
+// scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
+                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                 "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),
+                 "+r"(r[31])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // One 32-column chunk of one K tile folded into the running sums v[0..16) (float2 each).
 template <MmaKind KIND, int MODE>
 __device__ __forceinline__ void fold_chunk(const uint32_t (&r)[32], const float* __restrict__ sbv,
@@ -135,10 +169,11 @@ __device__ __forceinline__ void fold_chunk(const uint32_t (&r)[32], const float*
     if (KIND != MmaKind::kI8) {
       f0 = make_float2(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]));
       f1 = make_float2(__uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
-    } else if (MODE == kModeFast) {
-      const float2 magic = make_float2(-12582912.0f, -12582912.0f);
-      f0 = __fadd2_rn(make_float2(__int_as_float(0x4B400000 + x[0]), __int_as_float(0x4B400000 + x[1])), magic);
-      f1 = __fadd2_rn(make_float2(__int_as_float(0x4B400000 + x[2]), __int_as_float(0x4B400000 + x[3])), magic);
+    } else if (MODE == kModeFast || (MODE == kModeMix && (g & 1))) {
+      // |acc| <= 2^22: the bits kMagicBits + acc are the float32 value kMagic + acc, exactly
+      const float2 magic = make_float2(-kMagic, -kMagic);
+      f0 = __fadd2_rn(make_float2(__uint_as_float(kMagicBits + r[4 * g]), __uint_as_float(kMagicBits + r[4 * g + 1])), magic);
+      f1 = __fadd2_rn(make_float2(__uint_as_float(kMagicBits + r[4 * g + 2]), __uint_as_float(kMagicBits + r[4 * g + 3])), magic);
     } else {
       f0 = make_float2((float)x[0], (float)x[1]);
       f1 = make_float2((float)x[2], (float)x[3]);
@@ -303,84 +338,126 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     uint32_t acc_phase = 0;
     bool ok = true;
 
+    const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + ch * QNH;   // + acc * QN
+
     // Scales and correction factors of one (output tile, K tile): four consecutive columns
     // per lane for the warp's shared copy, one row value per lane.
     struct Prefetch {
-      float sb[4];
-      int32_t zc[4];
+      float4 sb;
+      int4 zc;
       float sa;
       int32_t zr;
     };
-    auto fetch = [&](int tile, int t) {
+    struct Where {      // what a lane reads for one output tile
+      int m, n;         // its row; the first of its four columns
+      bool rin, nin;
+    };
+    auto where = [&](int tile) {
+      Where w;
+      w.m = (tile % p.tiles_m) * (2 * QM) + (int)rank * QM + q * 32 + lane;
+      w.n = (tile / p.tiles_m) * QN + ch * QNH + lane * 4;
+      w.rin = w.m < p.M;
+      w.nin = w.n < p.N;
+      return w;
+    };
+    const bool vec = p.scale_vec != 0;
+    auto fetch = [&](const Where& w, int t) {
       Prefetch f;
-      const int m0 = (tile % p.tiles_m) * (2 * QM) + (int)rank * QM;
-      const int n0 = (tile / p.tiles_m) * QN + ch * QNH;
-      const int64_t m = (int64_t)m0 + q * 32 + lane;
+      f.sb = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+      f.zc = make_int4(0, 0, 0, 0);
+      const int64_t at = (int64_t)t * p.N + w.n;
+      if (p.sb && w.nin) {
+        const int64_t i = p.sb_tiled ? at : (int64_t)w.n;
+        if (vec && p.scale_dtype == QWX_F32) {
+          f.sb = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.sb) + i));
+        } else if (vec && p.scale_dtype == QWX_BF16) {
+          const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.sb) + i));
+          f.sb = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                             __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+        } else {
+          float* o = &f.sb.x;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int64_t n = (int64_t)n0 + lane * 4 + i;
-        const bool in = n < p.N;
-        f.sb[i] = (p.sb && in) ? load_scale_q(p.sb, p.scale_dtype, (p.sb_tiled ? (int64_t)t * p.N : 0) + n)
-                               : 1.0f;
-        f.zc[i] = (kCorr && in) ? __ldg(p.corr_col + (int64_t)t * p.N + n) : 0;
+          for (int k = 0; k < 4; ++k)
+            if (w.n + k < p.N) o[k] = load_scale_q(p.sb, p.scale_dtype, i + k);
+        }
       }
-      const bool rin = m < p.M;
-      f.sa = (p.sa && rin) ? load_scale_q(p.sa, p.scale_dtype, p.sa_tiled ? m * p.T + t : m) : 1.0f;
-      f.zr = (kCorr && rin) ? __ldg(p.corr_row + m * p.T + t) : 0;
+      if (kCorr && w.nin) {
+        if (vec) {
+          f.zc = __ldg(reinterpret_cast<const int4*>(p.corr_col + at));
+        } else {
+          int32_t* o = &f.zc.x;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (w.n + k < p.N) o[k] = __ldg(p.corr_col + at + k);
+        }
+      }
+      f.sa = (p.sa && w.rin) ? load_scale_q(p.sa, p.scale_dtype, p.sa_tiled ? (int64_t)w.m * p.T + t : (int64_t)w.m) : 1.0f;
+      f.zr = (kCorr && w.rin) ? __ldg(p.corr_row + (int64_t)w.m * p.T + t) : 0;
       return f;
     };
 
-    int tile = pair, t = 0, it = 0;
+    int tile = pair, t = 0;
     bool have = tile < num_tiles;
     Prefetch pf;
-    if (have) pf = fetch(tile, t);
+    Where wh = where(tile);
+    if (have) pf = fetch(wh, t);
     float2 v[QNH / 2];
 
     while (have && ok) {
-      const int buf = it & 1;
-      *reinterpret_cast<float4*>(&ctl->sb[ew][buf][lane * 4]) =
-          make_float4(pf.sb[0], pf.sb[1], pf.sb[2], pf.sb[3]);
-      if (kCorr)
-        *reinterpret_cast<int4*>(&ctl->zc[ew][buf][lane * 4]) =
-            make_int4(pf.zc[0], pf.zc[1], pf.zc[2], pf.zc[3]);
+      // all lanes try once (the accumulator is usually there already); lane 0 waits otherwise
+      if (!mbar_try_wait(smem_u32(&ctl->acc_full[acc]), acc_phase)) {
+        if (lane == 0) ok = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+      }
+      tc_fence_after();
+      const uint32_t tacc = tmem_warp + acc * QN;
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(tacc, r0);
+
+      // while the first load is in flight: this K tile's scales into shared memory, the
+      // next K tile's on their way from global memory
+      *reinterpret_cast<float4*>(&ctl->sb[ew][lane * 4]) = pf.sb;
+      if (kCorr) *reinterpret_cast<int4*>(&ctl->zc[ew][lane * 4]) = pf.zc;
       const float sa = pf.sa;
       const int32_t zr = pf.zr;
       __syncwarp();
+      const Where wh_now = wh;
       int ntile = tile, nt = t + 1;
-      if (nt == p.T) { nt = 0; ntile += num_pairs; }
+      if (nt == p.T) { nt = 0; ntile += num_pairs; wh = where(ntile); }
       const bool nhave = ntile < num_tiles;
-      if (nhave) pf = fetch(ntile, nt);   // in flight while this K tile is drained
-
-      if (lane == 0) ok = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      tc_fence_after();
+      if (nhave) pf = fetch(wh, nt);
 
       if (t == 0) {
 #pragma unroll
         for (int j = 0; j < QNH / 2; ++j) v[j] = make_float2(0.0f, 0.0f);
       }
-      const float* sbv = ctl->sb[ew][buf];
-      const int32_t* zcv = ctl->zc[ew][buf];
-#pragma unroll
-      for (int c = 0; c < QNH / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * QN + ch * QNH + c * 32, r);
-        tmem_ld_wait();
-        fold_chunk<KIND, MODE>(r, sbv + c * 32, zcv + c * 32, sa, zr, p.out_dtype, v + c * 16);
-      }
+      const float* sbv = ctl->sb[ew];
+      const int32_t* zcv = ctl->zc[ew];
+      tmem_ld_wait_for(r0);
+      tmem_ld_32x32b_x32(tacc + 32, r1);
+      fold_chunk<KIND, MODE>(r0, sbv, zcv, sa, zr, p.out_dtype, v);
+      tmem_ld_wait_for(r1);
+      tmem_ld_32x32b_x32(tacc + 64, r0);
+      fold_chunk<KIND, MODE>(r1, sbv + 32, zcv + 32, sa, zr, p.out_dtype, v + 16);
+      tmem_ld_wait_for(r0);
+      tmem_ld_32x32b_x32(tacc + 96, r1);
+      fold_chunk<KIND, MODE>(r0, sbv + 64, zcv + 64, sa, zr, p.out_dtype, v + 32);
+      tmem_ld_wait_for(r1);
+      // the accumulator goes back before the last chunk is folded: its values are in registers
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
+      if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty0 + acc * 8);
+      fold_chunk<KIND, MODE>(r1, sbv + 96, zcv + 96, sa, zr, p.out_dtype, v + 48);
+      __syncwarp();      // every lane is done with the staged scales before the next K tile's are written
 
       if (t == p.T - 1) {
-        const int m0 = (tile % p.tiles_m) * (2 * QM) + (int)rank * QM;
-        const int n0 = (tile / p.tiles_m) * QN + ch * QNH;
-        const int64_t m = (int64_t)m0 + q * 32 + lane;
+        const int64_t m = wh_now.m;
+        const int64_t n0 = wh_now.n - lane * 4;
         if (m < p.M) {
 #pragma unroll
           for (int c = 0; c < QNH / 32; ++c) {
-            const int64_t ncol = (int64_t)n0 + c * 32;
+            const int64_t ncol = n0 + c * 32;
             if (ncol >= p.N) break;
             const float* vc = reinterpret_cast<const float*>(v + c * 16);
             if (p.out_dtype == QWX_F32) {
@@ -424,7 +501,6 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       tile = ntile;
       t = nt;
       have = nhave;
-      ++it;
     }
   }
 
@@ -491,6 +567,12 @@ int gemm_q8_tiled_pair_launch(const void* a, const void* b, int code_dtype, int 
   p.corr_row = corr_row; p.corr_col = corr_col;
   p.out = out; p.out_dtype = out_dtype;
   p.error_flag = error_flag;
+  {
+    const uintptr_t esz = scale_dtype == QWX_F32 ? 4 : 2;
+    p.scale_vec = (N % 4 == 0) && (!sb || reinterpret_cast<uintptr_t>(sb) % (4 * esz) == 0) &&
+                  (!corr_col || reinterpret_cast<uintptr_t>(corr_col) % 16 == 0) &&
+                  (!sb || scale_dtype == QWX_F32 || scale_dtype == QWX_BF16);
+  }
   p.tiles_m = (int)((M + 2 * QM - 1) / (2 * QM));
   p.tiles_n = (int)((N + QN - 1) / QN);
   const int64_t num_tiles = (int64_t)p.tiles_m * p.tiles_n;
@@ -503,6 +585,8 @@ int gemm_q8_tiled_pair_launch(const void* a, const void* b, int code_dtype, int 
     // int8 products over at most 256 codes stay within [-2^22, 2^22]: the magic-number
     // conversion is exact there.  A zero-point term can leave that range, so it keeps cvt.
     const bool fast = k_tile <= 256 && !corr && !reference;
+    if (fast && k_tile <= 128)
+      return launch_tiled_pair_layout<MmaKind::kI8, kModeMix>(b_layout, ta, tb, p, grid, st);
     if (fast) return launch_tiled_pair_layout<MmaKind::kI8, kModeFast>(b_layout, ta, tb, p, grid, st);
     if (reference)
       return corr ? launch_tiled_pair_layout<MmaKind::kI8, kModeRefCorr>(b_layout, ta, tb, p, grid, st)

@@ -286,6 +286,10 @@ TILED_CASES = [
     (200, 1024, 264, None, 128, 'int8', 'float32'),      # per-row activations, sub-channel weight
     (64, 2048, 512, 512, None, 'int8', 'bfloat16'),
     (130, 1024, 256, 128, 128, 'float8_e4m3fn', 'float32'),
+    # several 256 x 256 tiles of the CTA-pair form, ragged in M and N
+    (520, 1024, 784, 128, 128, 'int8', 'bfloat16'),
+    (300, 1536, 528, 512, 512, 'int8', 'float32'),
+    (260, 512, 272, 256, 256, 'float8_e4m3fn', 'bfloat16'),
 ]
 
 
@@ -325,6 +329,44 @@ def test_tiled_scales_match_oracle(case):
   # the loop form (one contraction per K tile, added in order) is the same kernel here
   if lt == rt and dtype == 'float32':
     _close(bdg.loop_dot_general(lb, rb, DN), odg.loop_dot_general(lo, ro, DN))
+
+
+@pytest.mark.parametrize('scale_dtype', [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('corr', [False, True])
+@pytest.mark.parametrize('shape', [(300, 250, 384, 128), (129, 1000, 512, 256), (640, 72, 1024, 512)],
+                         ids=['300x250x384', '129x1000x512', '640x72x1024'])
+def test_tiled_c_abi_weight_stored_n_by_k(shape, corr, scale_dtype):
+  """qwx_gemm_q8_tiled with the weight as [N, K], N a multiple of neither 4 nor 32 in two of the
+  shapes (single scale loads, ragged stores), every scale dtype, with and without the integer
+  zero-point term, against the formula in float64."""
+  M, N, K, tile = shape
+  T = K // tile
+  rng = np.random.default_rng(M * 7 + N + int(corr))
+  a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+  b = rng.integers(-128, 128, (N, K), dtype=np.int8)
+  sa = torch.as_tensor(rng.random((M, T), dtype=np.float32) + 0.5).to(scale_dtype)
+  sb = torch.as_tensor(rng.random((T, N), dtype=np.float32) + 0.5).to(scale_dtype)
+  cr = rng.integers(-128, 128, (M, T), dtype=np.int32)
+  cc = rng.integers(-2000, 2000, (T, N), dtype=np.int32)
+  want = np.zeros((M, N), dtype=np.float64)
+  for t in range(T):
+    acc = a[:, t * tile:(t + 1) * tile].astype(np.float64) @ b[:, t * tile:(t + 1) * tile].astype(np.float64).T
+    if corr:
+      acc -= cr[:, t:t + 1].astype(np.float64) * cc[t:t + 1].astype(np.float64)
+    want += acc * sa[:, t:t + 1].double().numpy() * sb[t:t + 1].double().numpy()
+  L = _lib.lib()
+  dev = [h.to_torch(x) for x in (a, b, cr, cc)]
+  sa_d, sb_d = sa.cuda(), sb.cuda()
+  out = torch.empty((M, N), dtype=torch.float32, device='cuda')
+  err = _lib.error_flag(out.device)
+  _lib.check(L.qwx_gemm_q8_tiled(_lib.ptr(dev[0]), _lib.ptr(dev[1]), _lib.S8, _lib.B_NK, M, N, K, tile,
+                                 _lib.ptr(sa_d), 1, _lib.ptr(sb_d), 1, _lib.FLOAT_CODES[scale_dtype],
+                                 _lib.ptr(dev[2]) if corr else None, _lib.ptr(dev[3]) if corr else None,
+                                 _lib.ptr(out), _lib.F32, 0, _lib.ptr(err), _lib.stream_ptr()), 'tiled')
+  _lib.raise_on_device_error()
+  got = out.cpu().numpy().astype(np.float64)
+  # float32 running sums of T terms: a few float32 ulps of the largest partial sum
+  assert np.all(np.abs(got - want) <= 1e-5 * np.abs(want) + 1e-5 * np.abs(want).max())
 
 
 @pytest.mark.parametrize('side', ['lhs', 'rhs'])

@@ -105,8 +105,8 @@ def test_lm_head_shape_many_tiles_per_cta(layout):
 
 
 def test_k_tiled_more_tiles_than_ctas():
-  """Sub-channel scales on both sides, 8 x 20 = 160 tiles of 128 x 128 on 148 CTAs."""
-  M, K, N, tile = 1024, 1024, 2560, 256
+  """Sub-channel scales on both sides, 8 x 11 = 88 tiles of 256 x 256 on 74 CTA pairs."""
+  M, K, N, tile = 2048, 1024, 2816, 256
   rng = np.random.default_rng(5)
   a = rng.standard_normal((M, K), dtype=np.float32).astype(bf16)
   w = (0.02 * rng.standard_normal((K, N), dtype=np.float32)).astype(bf16)
