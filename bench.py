@@ -475,7 +475,7 @@ def subchannel_records(args, device, lib_peaks: dict):
   from qwix_b200.core import qarray as bq
   Ms, Ks, Ns = (args.m or 4096), 8192, 8192
   peaks = _peaks()
-  peak = lib_peaks.get('int8_burst') or 2 * peaks['bf16_tflops']
+  peak = lib_peaks.get('int8_burst') or 2 * peaks['bf16_burst']
   steps = max(10, min(args.steps, 40))
   gen = torch.Generator(device).manual_seed(11)
   acts = [torch.randn(Ms, Ks, device=device, dtype=torch.bfloat16, generator=gen) for _ in range(2)]
@@ -487,7 +487,10 @@ def subchannel_records(args, device, lib_peaks: dict):
     aq = [bq.quantize(a, bdg.get_how_to_quantize(for_lhs=True, **kw)) for a in acts]
     wq = [bq.quantize(w, bdg.get_how_to_quantize(for_lhs=False, **kw)) for w in wts]
     # two operand sets (2 x 96 MB of codes) + the bf16 output: 256 MB cycled, above the 126 MB L2
-    ms = _time_calls(lambda i: bdg.dot_general(aq[i % 2], wq[i % 2], DN), steps, max(args.warmup, 3))
+    # median of five blocks: the block that follows the library's sustained loop runs power-capped
+    blocks = sorted(_time_calls(lambda i: bdg.dot_general(aq[i % 2], wq[i % 2], DN), steps, max(args.warmup, 3))
+                    for _ in range(5))
+    ms = blocks[2]
     _lib.raise_on_device_error()
     got = _np(bdg.dot_general(aq[0], wq[0], DN)[torch.as_tensor(rows, device=device)])
     a_o = oq.quantize(_np(acts[0][torch.as_tensor(rows, device=device)]), odg.get_how_to_quantize(for_lhs=True, **kw))
@@ -502,6 +505,7 @@ def subchannel_records(args, device, lib_peaks: dict):
     achieved = 2.0 * Ms * Ns * Ks / (ms * 1e-3) / 1e12
     records.append({
         'M': Ms, 'K': Ks, 'N': Ns, 'k_tile': tile, 'ms_per_step': ms, 'steps': steps,
+        'blocks_ms_per_step': blocks, 'timing': 'median of 5 blocks of `steps` calls',
         'value': achieved, 'unit': 'TOPS', 'l2': '2 operand sets + output (256 MB) cycled',
         'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TOP/s',
                      'frac': achieved / peak, 'traffic': None,
@@ -512,7 +516,7 @@ def subchannel_records(args, device, lib_peaks: dict):
                      'peak_source': ('torch._int_mm at 8192^3, best of 10, measured in this run (burst)'
                                      if lib_peaks.get('int8_burst') else
                                      f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})")},
-        'verified': verified, 'gpu_launches': steps,
+        'verified': verified, 'gpu_launches': 5 * steps,
     })
     del aq, wq
   return records

@@ -17,7 +17,10 @@
 //   * eight epilogue warps per CTA, two per tensor-memory lane quarter, 128 columns each; a
 //     thread owns one output row and keeps 128 running float32 sums in registers (the CTA's
 //     registers are re-split with setmaxnreg: 232 per epilogue thread, 40 per control thread,
-//     which adds up to the 168 per thread the CTA was launched with);
+//     which adds up to the 168 per thread the CTA was launched with).  A warp's tensor-memory
+//     loads complete one after the other, about 95 clocks per 32 x 32 words with no MMA
+//     running, so one register buffer serves.  Sixteen warps of 64 columns (112 / 24
+//     registers, which spills) measured twice as slow at a 128-wide K tile;
 //   * the variant is a template parameter, not a run-time branch in the inner loop;
 //   * int8 with |acc| <= 2^22 guaranteed: int32 -> float32 by the exact magic-number add,
 //     for 128-wide K tiles alternating with cvt, which runs on another pipe (527 -> 459 us at
@@ -26,8 +29,8 @@
 //     saves the integer add but measured slower: the hand-back then waits for the stores);
 //   * the three float operations per value (subtract, times sa, multiply-add with sb) are
 //     the packed two-lane forms (add/mul/fma .f32x2): half the issue slots, same rounding;
-//   * tensor-memory loads are double-buffered, and the scales of the next K tile are fetched
-//     and this one's staged in shared memory while the first load is in flight;
+//   * the scales of the next K tile are fetched and this one's staged in shared memory while
+//     the first tensor-memory load is in flight;
 //   * the hand-back of an accumulator is a relaxed arrive: what it orders is the tensor-memory
 //     traffic, which tcgen05.wait and tcgen05.fence order; a release at cluster scope would
 //     also wait for the scale loads in flight, once per K tile.
@@ -60,11 +63,21 @@ constexpr int kQStages = 6;
 constexpr int kQABytes = QM * QK;
 constexpr int kQBBytes = QNH * QK;
 constexpr int kQStageBytes = kQABytes + kQBBytes;
-constexpr int kQThreads = 384;       // one control warpgroup + two epilogue warpgroups
+#ifndef QWX_TP_EPI_WARPS
+#define QWX_TP_EPI_WARPS 8
+#endif
 constexpr int kQEpiWarp0 = 4;
-constexpr int kQEpiWarps = 8;
-constexpr int kQRegsControl = 40;
-constexpr int kQRegsEpilogue = 232;
+constexpr int kQEpiWarps = QWX_TP_EPI_WARPS;        // 8 or 16: two or four per tensor-memory lane quarter
+constexpr int kQThreads = 32 * (kQEpiWarp0 + kQEpiWarps);   // one control warpgroup + the epilogue warpgroups
+constexpr int QCW = QN / (kQEpiWarps / 4);          // columns one epilogue warp drains (128 or 64)
+constexpr int QVPL = QCW / 32;                      // scale values a lane stages per K tile
+// setmaxnreg moves registers inside what the CTA was launched with (threads x the launch count,
+// 168 for 384 threads, 96 for 640): control threads give up what the epilogue threads claim.
+constexpr int kQRegsControl = kQEpiWarps == 8 ? 40 : 24;
+constexpr int kQRegsEpilogue = kQEpiWarps == 8 ? 232 : 112;
+constexpr int kQRegsLaunch = kQEpiWarps == 8 ? 168 : 96;
+static_assert(128 * kQRegsControl + 32 * kQEpiWarps * kQRegsEpilogue <= kQThreads * kQRegsLaunch,
+              "the claim would wait for registers that are never released");
 
 // Epilogue variants (template parameter).
 constexpr int kModeFast = 0;       // int8, |acc| < 2^22, no zero points: magic-number conversion
@@ -83,8 +96,8 @@ struct ControlQ {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort;
-  alignas(16) float sb[kQEpiWarps][QNH];    // per epilogue warp: the scales of the K tile being drained
-  alignas(16) int32_t zc[kQEpiWarps][QNH];
+  alignas(16) float sb[kQEpiWarps][QCW];    // per epilogue warp: the scales of the K tile being drained
+  alignas(16) int32_t zc[kQEpiWarps][QCW];
 };
 
 constexpr size_t kQSmemBytes = 1024 + (size_t)kQStages * kQStageBytes + sizeof(ControlQ);
@@ -329,33 +342,33 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   } else {
     // ---------------- epilogue: drain one accumulator per K tile, keep running sums -----------
     regs_claim<kQRegsEpilogue>();
-    const int ew = warp - kQEpiWarp0;         // epilogue warp 0..7
+    const int ew = warp - kQEpiWarp0;         // epilogue warp
     const int q = warp & 3;                   // tensor-memory lane quarter of this warp
-    const int ch = ew >> 2;                   // which 128 columns of the tile
+    const int ch = ew >> 2;                   // which QCW columns of the tile
     constexpr bool kCorr = MODE == kModeCorr || MODE == kModeRefCorr;
     const uint32_t acc_empty0 = map_to_cta(smem_u32(&ctl->acc_empty[0]), 0);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
 
-    const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + ch * QNH;   // + acc * QN
+    const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + ch * QCW;   // + acc * QN
 
-    // Scales and correction factors of one (output tile, K tile): four consecutive columns
+    // Scales and correction factors of one (output tile, K tile): QVPL consecutive columns
     // per lane for the warp's shared copy, one row value per lane.
     struct Prefetch {
-      float4 sb;
-      int4 zc;
+      float sb[QVPL];
+      int32_t zc[QVPL];
       float sa;
       int32_t zr;
     };
     struct Where {      // what a lane reads for one output tile
-      int m, n;         // its row; the first of its four columns
+      int m, n;         // its row; the first of its columns
       bool rin, nin;
     };
     auto where = [&](int tile) {
       Where w;
       w.m = (tile % p.tiles_m) * (2 * QM) + (int)rank * QM + q * 32 + lane;
-      w.n = (tile / p.tiles_m) * QN + ch * QNH + lane * 4;
+      w.n = (tile / p.tiles_m) * QN + ch * QCW + lane * QVPL;
       w.rin = w.m < p.M;
       w.nin = w.n < p.N;
       return w;
@@ -363,32 +376,47 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     const bool vec = p.scale_vec != 0;
     auto fetch = [&](const Where& w, int t) {
       Prefetch f;
-      f.sb = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-      f.zc = make_int4(0, 0, 0, 0);
+#pragma unroll
+      for (int k = 0; k < QVPL; ++k) { f.sb[k] = 1.0f; f.zc[k] = 0; }
       const int64_t at = (int64_t)t * p.N + w.n;
       if (p.sb && w.nin) {
         const int64_t i = p.sb_tiled ? at : (int64_t)w.n;
         if (vec && p.scale_dtype == QWX_F32) {
-          f.sb = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.sb) + i));
+          const float* src = reinterpret_cast<const float*>(p.sb) + i;
+          if (QVPL == 4) {
+            const float4 u = __ldg(reinterpret_cast<const float4*>(src));
+            f.sb[0] = u.x; f.sb[1] = u.y; f.sb[QVPL - 2] = u.z; f.sb[QVPL - 1] = u.w;
+          } else {
+            const float2 u = __ldg(reinterpret_cast<const float2*>(src));
+            f.sb[0] = u.x; f.sb[1] = u.y;
+          }
         } else if (vec && p.scale_dtype == QWX_BF16) {
-          const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.sb) + i));
-          f.sb = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
-                             __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+          const uint16_t* src = reinterpret_cast<const uint16_t*>(p.sb) + i;
+          if (QVPL == 4) {
+            const uint2 u = __ldg(reinterpret_cast<const uint2*>(src));
+            f.sb[0] = __uint_as_float(u.x << 16); f.sb[1] = __uint_as_float(u.x & 0xffff0000u);
+            f.sb[QVPL - 2] = __uint_as_float(u.y << 16); f.sb[QVPL - 1] = __uint_as_float(u.y & 0xffff0000u);
+          } else {
+            const uint32_t u = __ldg(reinterpret_cast<const uint32_t*>(src));
+            f.sb[0] = __uint_as_float(u << 16); f.sb[1] = __uint_as_float(u & 0xffff0000u);
+          }
         } else {
-          float* o = &f.sb.x;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            if (w.n + k < p.N) o[k] = load_scale_q(p.sb, p.scale_dtype, i + k);
+          for (int k = 0; k < QVPL; ++k)
+            if (w.n + k < p.N) f.sb[k] = load_scale_q(p.sb, p.scale_dtype, i + k);
         }
       }
       if (kCorr && w.nin) {
-        if (vec) {
-          f.zc = __ldg(reinterpret_cast<const int4*>(p.corr_col + at));
+        if (vec && QVPL == 4) {
+          const int4 u = __ldg(reinterpret_cast<const int4*>(p.corr_col + at));
+          f.zc[0] = u.x; f.zc[1] = u.y; f.zc[QVPL - 2] = u.z; f.zc[QVPL - 1] = u.w;
+        } else if (vec) {
+          const int2 u = __ldg(reinterpret_cast<const int2*>(p.corr_col + at));
+          f.zc[0] = u.x; f.zc[1] = u.y;
         } else {
-          int32_t* o = &f.zc.x;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            if (w.n + k < p.N) o[k] = __ldg(p.corr_col + at + k);
+          for (int k = 0; k < QVPL; ++k)
+            if (w.n + k < p.N) f.zc[k] = __ldg(p.corr_col + at + k);
         }
       }
       f.sa = (p.sa && w.rin) ? load_scale_q(p.sa, p.scale_dtype, p.sa_tiled ? (int64_t)w.m * p.T + t : (int64_t)w.m) : 1.0f;
@@ -401,7 +429,7 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     Prefetch pf;
     Where wh = where(tile);
     if (have) pf = fetch(wh, t);
-    float2 v[QNH / 2];
+    float2 v[QCW / 2];
 
     while (have && ok) {
       // all lanes try once (the accumulator is usually there already); lane 0 waits otherwise
@@ -412,13 +440,18 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
       tc_fence_after();
       const uint32_t tacc = tmem_warp + acc * QN;
-      uint32_t r0[32], r1[32];
-      tmem_ld_32x32b_x32(tacc, r0);
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(tacc, r);
 
       // while the first load is in flight: this K tile's scales into shared memory, the
       // next K tile's on their way from global memory
-      *reinterpret_cast<float4*>(&ctl->sb[ew][lane * 4]) = pf.sb;
-      if (kCorr) *reinterpret_cast<int4*>(&ctl->zc[ew][lane * 4]) = pf.zc;
+      if (QVPL == 4) {
+        *reinterpret_cast<float4*>(&ctl->sb[ew][lane * QVPL]) = make_float4(pf.sb[0], pf.sb[1], pf.sb[QVPL - 2], pf.sb[QVPL - 1]);
+        if (kCorr) *reinterpret_cast<int4*>(&ctl->zc[ew][lane * QVPL]) = make_int4(pf.zc[0], pf.zc[1], pf.zc[QVPL - 2], pf.zc[QVPL - 1]);
+      } else {
+        *reinterpret_cast<float2*>(&ctl->sb[ew][lane * QVPL]) = make_float2(pf.sb[0], pf.sb[1]);
+        if (kCorr) *reinterpret_cast<int2*>(&ctl->zc[ew][lane * QVPL]) = make_int2(pf.zc[0], pf.zc[1]);
+      }
       const float sa = pf.sa;
       const int32_t zr = pf.zr;
       __syncwarp();
@@ -430,33 +463,33 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
 
       if (t == 0) {
 #pragma unroll
-        for (int j = 0; j < QNH / 2; ++j) v[j] = make_float2(0.0f, 0.0f);
+        for (int j = 0; j < QCW / 2; ++j) v[j] = make_float2(0.0f, 0.0f);
       }
       const float* sbv = ctl->sb[ew];
       const int32_t* zcv = ctl->zc[ew];
-      tmem_ld_wait_for(r0);
-      tmem_ld_32x32b_x32(tacc + 32, r1);
-      fold_chunk<KIND, MODE>(r0, sbv, zcv, sa, zr, p.out_dtype, v);
-      tmem_ld_wait_for(r1);
-      tmem_ld_32x32b_x32(tacc + 64, r0);
-      fold_chunk<KIND, MODE>(r1, sbv + 32, zcv + 32, sa, zr, p.out_dtype, v + 16);
-      tmem_ld_wait_for(r0);
-      tmem_ld_32x32b_x32(tacc + 96, r1);
-      fold_chunk<KIND, MODE>(r0, sbv + 64, zcv + 64, sa, zr, p.out_dtype, v + 32);
-      tmem_ld_wait_for(r1);
-      // the accumulator goes back before the last chunk is folded: its values are in registers
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty0 + acc * 8);
-      fold_chunk<KIND, MODE>(r1, sbv + 96, zcv + 96, sa, zr, p.out_dtype, v + 48);
+      // A warp's tensor-memory loads complete one after the other (two in flight take twice
+      // as long as one), so one register buffer serves; the other warps of the SM sub-partition
+      // fill the time.
+#pragma unroll
+      for (int c = 0; c < QCW / 32; ++c) {
+        if (c) tmem_ld_32x32b_x32(tacc + c * 32, r);
+        tmem_ld_wait_for(r);
+        if (c == QCW / 32 - 1) {
+          // the accumulator goes back before the last chunk is folded: its values are in registers
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty0 + acc * 8);
+        }
+        fold_chunk<KIND, MODE>(r, sbv + c * 32, zcv + c * 32, sa, zr, p.out_dtype, v + c * 16);
+      }
       __syncwarp();      // every lane is done with the staged scales before the next K tile's are written
 
       if (t == p.T - 1) {
         const int64_t m = wh_now.m;
-        const int64_t n0 = wh_now.n - lane * 4;
+        const int64_t n0 = wh_now.n - lane * QVPL;
         if (m < p.M) {
 #pragma unroll
-          for (int c = 0; c < QNH / 32; ++c) {
+          for (int c = 0; c < QCW / 32; ++c) {
             const int64_t ncol = n0 + c * 32;
             if (ncol >= p.N) break;
             const float* vc = reinterpret_cast<const float*>(v + c * 16);
