@@ -523,6 +523,88 @@ def subchannel_records(args, device, lib_peaks: dict):
 
 
 # ---------------------------------------------------------------------------------------------
+# MXFP8 block-scaled dot_general: e4m3 codes, one power-of-two scale per 32 contracted elements
+# ---------------------------------------------------------------------------------------------
+
+def mxfp8_record(args, device, lib_peaks: dict):
+  """A [M, 8192] x W [8192, 8192], both quantized under a `qtype='mxfp8', tile_size=32` rule;
+  the timed call is the public dot_general on the quantized operands (the activation's scale
+  bytes are re-laid out inside the call, the weight's once).  Beside it, where this PyTorch
+  offers it, the vendor's block-scaled GEMM on the same codes and scales."""
+  from oracle import dot_general as odg
+  from oracle import mxfp_dot as omx
+  from oracle import qarray as oq
+  from qwix_b200 import _lib
+  from qwix_b200.core import dot_general as bdg
+  from qwix_b200.core import qarray as bq
+  Ms, Ks, Ns = (args.m or 4096), 8192, 8192
+  peaks = _peaks()
+  peak = lib_peaks.get('fp8_burst') or 2 * peaks['bf16_burst']
+  steps = max(10, min(args.steps, 40))
+  gen = torch.Generator(device).manual_seed(21)
+  kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=32, qtype='mxfp8')
+  acts = [torch.randn(Ms, Ks, device=device, dtype=torch.bfloat16, generator=gen) for _ in range(2)]
+  wts = [torch.randn(Ks, Ns, device=device, dtype=torch.bfloat16, generator=gen) * 0.02 for _ in range(2)]
+  how_a, how_w = bdg.get_how_to_quantize(for_lhs=True, **kw), bdg.get_how_to_quantize(for_lhs=False, **kw)
+  q_ms = _time_calls(lambda i: bq.quantize(acts[i % 2], how_a), steps, max(args.warmup, 3))
+  aq = [bq.quantize(a, how_a) for a in acts]
+  wq = [bq.quantize(w, how_w) for w in wts]
+  blocks = sorted(_time_calls(lambda i: bdg.dot_general(aq[i % 2], wq[i % 2], DN), steps, max(args.warmup, 3))
+                  for _ in range(5))
+  ms = blocks[2]
+  _lib.raise_on_device_error()
+  rows = np.arange(0, Ms, max(1, Ms // 32))[:32]
+  ri = torch.as_tensor(rows, device=device)
+  got = _np(bdg.dot_general(aq[0], wq[0], DN)[ri])
+  a_o = oq.quantize(_np(acts[0][ri]), odg.get_how_to_quantize(for_lhs=True, **kw))
+  w_o = oq.QArray(_np(wq[0].qvalue), _np(wq[0].scale), None, 'mxfp8')
+  verified = _tolerance_report(got, omx.mxfp_dot_general(a_o, w_o, DN))
+  verified.update({'rows': int(rows.size), 'against': 'oracle scaled matmul on the device\'s weight codes',
+                   'act_codes_bit_exact': bool(np.array_equal(_np(aq[0].qvalue[ri]).view(np.uint8),
+                                                              a_o.qvalue.view(np.uint8))),
+                   'act_scales_bit_exact': bool(np.array_equal(_np(aq[0].scale[ri]).view(np.uint8),
+                                                               a_o.scale.view(np.uint8)))})
+  achieved = 2.0 * Ms * Ns * Ks / (ms * 1e-3) / 1e12
+  library = {}
+  try:
+    # The vendor's block-scaled GEMM takes E8M0 scales in 128-row x 4-block groups, the
+    # layout qwx_mx_pack_scales writes for a row-major operand.
+    L = _lib.lib()
+    def packed(scale_rows_by_blocks, n_rows):
+      nb = L.qwx_mx_scales_packed_bytes(0, n_rows, Ks)
+      out = torch.empty(nb, dtype=torch.uint8, device=device)
+      sc = scale_rows_by_blocks.contiguous()
+      _lib.check(L.qwx_mx_pack_scales(0, _lib.ptr(sc), _lib.FLOAT_CODES[sc.dtype], n_rows, Ks, 0,
+                                      _lib.ptr(out), nb, _lib.stream_ptr(device)), 'pack')
+      return out.view(torch.float8_e8m0fnu)
+    sa = packed(aq[0].scale, Ms)
+    sb = packed(wq[0].scale.t(), Ns)
+    b_nk = wq[0].qvalue.t().contiguous()          # [N, K] storage, passed as its [K, N] view
+    lib_call = lambda: torch._scaled_mm(aq[0].qvalue, b_nk.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+    ref = lib_call()
+    mine = bdg.dot_general(aq[0], wq[0], DN)
+    library['max_abs_diff_to_ours'] = float((ref.float() - mine.float()).abs().max())
+    lib_ms = sorted(_time_calls(lambda i: lib_call(), steps, 3) for _ in range(3))[1]
+    library.update({'ms_per_step': lib_ms, 'tops': 2.0 * Ms * Ns * Ks / (lib_ms * 1e-3) / 1e12,
+                    'how': 'torch._scaled_mm with float8_e8m0fnu block scales, one operand set'})
+  except Exception as e:  # noqa: BLE001 -- context only
+    library['unavailable'] = repr(e)[:200]
+  return {
+      'M': Ms, 'K': Ks, 'N': Ns, 'block': 32, 'ms_per_step': ms, 'steps': steps, 'blocks_ms_per_step': blocks,
+      'timing': 'median of 5 blocks of `steps` calls', 'value': achieved, 'unit': 'TOPS',
+      'l2': '2 operand sets + output (256 MB) cycled',
+      'quantize_ms': q_ms, 'quantize_gbs': (Ms * Ks * 3 + Ms * Ks // 32 * 2) / (q_ms * 1e-3) / 1e9,
+      'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TOP/s', 'frac': achieved / peak,
+                   'traffic': None, 'kernel': 'gemm_mx8_kernel',
+                   'frac_of_sustained': (achieved / lib_peaks['fp8_sustained']) if lib_peaks.get('fp8_sustained') else None,
+                   'peak_source': ('torch._scaled_mm (per-tensor scales) at 8192^3, best of 10, measured in this run'
+                                   if lib_peaks.get('fp8_burst') else
+                                   f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})")},
+      'library_block_scaled': library, 'verified': verified, 'gpu_launches': 5 * steps * 2,
+  }
+
+
+# ---------------------------------------------------------------------------------------------
 # Hadamard-quantized fp8 matmul: A [8192, 4096] x W [4096, 14336], 128-point blocks along K
 # ---------------------------------------------------------------------------------------------
 
@@ -1023,7 +1105,7 @@ def main():
                        'launch list)')
   ap.add_argument('--m', type=int, default=None,
                   help='token rows per step (profiling aid; the benchmark uses its own sizes)')
-  ap.add_argument('--workload', default='all', choices=['all', 'gemm', 'decoder', 'w4', 'hadamard', 'subchannel'],
+  ap.add_argument('--workload', default='all', choices=['all', 'gemm', 'decoder', 'w4', 'hadamard', 'subchannel', 'mxfp8'],
                   help="'all' (default): the headline GEMM step plus the decoder / w4 / hadamard "
                        'records in one line; the others run one workload alone')
   ap.add_argument('--layers', type=int, default=32)
@@ -1064,7 +1146,7 @@ def main():
 
   with_cpu = world == 1 and not args.no_cpu_baseline
   lib_peaks = {}
-  if rank == 0 and not args.no_library_peaks and args.workload in ('all', 'gemm', 'hadamard', 'decoder', 'subchannel'):
+  if rank == 0 and not args.no_library_peaks and args.workload in ('all', 'gemm', 'hadamard', 'decoder', 'subchannel', 'mxfp8'):
     lib_peaks = library_peaks(device, sustain_s=4.0 if args.workload in ('all', 'gemm', 'subchannel') else 0.0)
   if dist is not None:
     dist.barrier()
@@ -1093,6 +1175,13 @@ def main():
       line['subchannel'] = recs
     else:
       line = {'metric': 'sub-channel w8a8 GEMM TOPS', 'n_gpus': 1, 'data': 'synthetic', 'subchannel': recs}
+    torch.cuda.empty_cache()
+  if world == 1 and args.workload in ('all', 'mxfp8'):
+    rec = mxfp8_record(args, device, lib_peaks)
+    if line is not None and args.workload == 'all':
+      line['mxfp8'] = rec
+    else:
+      line = {'metric': 'MXFP8 block-scaled GEMM TOPS', 'n_gpus': 1, 'data': 'synthetic', 'mxfp8': rec}
     torch.cuda.empty_cache()
   if world == 1 and args.workload in ('all', 'hadamard'):
     rec = hadamard_record(args, device, with_cpu, lib_peaks)

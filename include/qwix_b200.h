@@ -42,7 +42,11 @@ enum qwx_status {
 
 enum qwx_dtype {
   QWX_F32 = 0, QWX_BF16 = 1, QWX_F16 = 2,
-  QWX_S8 = 3, QWX_S4 = 4, QWX_E4M3 = 5, QWX_S32 = 6, QWX_S4U = 7
+  QWX_S8 = 3, QWX_S4 = 4, QWX_E4M3 = 5, QWX_S32 = 6, QWX_S4U = 7,
+  /* e4m3 codes whose scale is a power of two ("mxfp8": one scale per 32 values along the
+   * contracted axis; qwix/_src/core/qarray.py:306-325, 566-579).  A quantizer qtype only: the
+   * stored codes are QWX_E4M3 bytes for every other entry point. */
+  QWX_MXFP8 = 8
 };
 
 enum qwx_calibration { QWX_ABSMAX = 0, QWX_MINMAX = 1, QWX_RMS = 2 };
@@ -254,6 +258,25 @@ int qwx_gemm_q8_tiled(const void* a, const void* b, int code_dtype, int b_layout
  * out is int32 [T, other] if t_major else [other, T], other being the non-K extent. */
 int qwx_code_sums(const void* codes, int64_t rows, int64_t cols, int k_axis, int64_t k_tile,
                   int t_major, int32_t* out, qwx_stream_t stream);
+
+/* MXFP8 block-scaled GEMM: what dot_general computes when both operands are "mxfp8" QArrays
+ * (qwix/_src/core/mxfp_dot.py:24-79, jax.nn.scaled_matmul in the reference):
+ *   out[m, n] = sum_j ( sum_{k in 32-wide block j} a[m, k] * b[k, n] ) * sa[m, j] * sb[j, n]
+ * a [M, K] and b ([K, N] for QWX_B_KN, [N, K] for QWX_B_NK) hold e4m3 codes, the scales are
+ * powers of two, accumulation is float32 inside tcgen05.mma.kind::mxf8f6f4.block_scale.
+ * K must be a multiple of 128 (QWX_ERR_UNSUPPORTED otherwise: dequantize instead).
+ *
+ * The kernel reads the scales as E8M0 bytes in its own staging order; qwx_mx_pack_scales
+ * produces that from a QArray's scale array (operand 0 = a: scale [rows = M, K / 32];
+ * operand 1 = b: scale [rows = N, K / 32], or [K / 32, N] with k_major = 1), once per weight
+ * and once per activation.  qwx_mx_scales_packed_bytes gives the size of `out` (0 for
+ * arguments the GEMM would refuse). */
+size_t qwx_mx_scales_packed_bytes(int operand, int64_t rows, int64_t K);
+int qwx_mx_pack_scales(int operand, const void* scale, int scale_dtype, int64_t rows, int64_t K,
+                       int k_major, void* out, size_t out_bytes, qwx_stream_t stream);
+int qwx_gemm_mx8(const void* a, const void* b, int b_layout, int64_t M, int64_t N, int64_t K,
+                 const void* sfa_packed, const void* sfb_packed, void* out, int out_dtype,
+                 int32_t* error_flag, qwx_stream_t stream);
 
 /* Element-wise stages of a Llama-style decoder layer fused with the per-token int8
  * quantization of the next projection's activation.  The quantization half is

@@ -387,6 +387,11 @@ def dot_general(lhs, rhs, dimension_numbers, precision=None, preferred_element_t
   """
   del precision
   kwargs.pop('out_sharding', None)
+  # dot_general.py:432-437: microscaled operands go to the block-scaled tensor-core GEMM first
+  from qwix_b200.core import mxfp_dot
+  mx = mxfp_dot.mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type)
+  if mx is not None:
+    return mx
   if use_fast_path(lhs, rhs, dimension_numbers):
     return _fast_dot_general(lhs, rhs, dimension_numbers,
                              preferred_element_type=preferred_element_type, **kwargs)

@@ -118,12 +118,15 @@ template <> __device__ __forceinline__ void store8<F16>(void* p, int64_t i, cons
 struct S8 { static constexpr int kLo = -128, kHi = 127; static constexpr bool kFloat = false; };
 struct S4 { static constexpr int kLo = -8, kHi = 7; static constexpr bool kFloat = false; };
 struct E4M3 { static constexpr bool kFloat = true; };
+// e4m3 codes under a power-of-two scale per 32 values (OCP microscaling, "mxfp8")
+struct MX8 { static constexpr bool kFloat = true; };
 
 // Symmetric bound B (codes cover [-B, B]) and asymmetric (qmin, qmax).
 template <typename Q> __host__ __device__ constexpr float sym_bound();
 template <> __host__ __device__ constexpr float sym_bound<S8>() { return 127.5f; }
 template <> __host__ __device__ constexpr float sym_bound<S4>() { return 7.5f; }
 template <> __host__ __device__ constexpr float sym_bound<E4M3>() { return 448.0f; }
+template <> __host__ __device__ constexpr float sym_bound<MX8>() { return 448.0f; }
 
 // Scaled float -> code, returned as the byte that is stored for 8-bit codes or the
 // sign-extended value for int4.  Integers: round-half-even, saturate, NaN -> 0 (the

@@ -26,12 +26,13 @@ struct CalibArgs {
   float arg;       // already narrowed to float
 };
 
-enum class Out { kS8, kS4U, kS4P, kE4M3 };
+enum class Out { kS8, kS4U, kS4P, kE4M3, kMX8 };
 template <Out O> struct OutTraits;
 template <> struct OutTraits<Out::kS8> { using Q = S8; };
 template <> struct OutTraits<Out::kS4U> { using Q = S4; };
 template <> struct OutTraits<Out::kS4P> { using Q = S4; };
 template <> struct OutTraits<Out::kE4M3> { using Q = E4M3; };
+template <> struct OutTraits<Out::kMX8> { using Q = MX8; };
 
 // ---- scalar recipes -------------------------------------------------------------------
 
@@ -50,7 +51,14 @@ __device__ __forceinline__ float guard_scale(float s) {
 
 template <typename T, typename Q>
 __device__ __forceinline__ float symmetric_scale(float absmax) {
-  return guard_scale<T>(round_to<T>(__fdiv_rn(absmax, sym_bound<Q>())));
+  float s = guard_scale<T>(round_to<T>(__fdiv_rn(absmax, sym_bound<Q>())));
+  if constexpr (std::is_same<Q, MX8>::value) {
+    // Microscaling: the scale becomes a power of two.  scale * 60/31 in the input dtype
+    // (outlier-aware bias), rounded to bfloat16, significand dropped (qarray.py:566-579).
+    const float biased = round_to<T>(__fmul_rn(s, round_to<T>(60.0f / 31.0f)));
+    s = __uint_as_float(__float_as_uint(round_to<BF16>(biased)) & 0x7F800000u);
+  }
+  return s;
 }
 
 template <typename T, typename Q>
@@ -314,7 +322,7 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
 
 // ---- the per-token hot path: bf16 rows -> int8, absmax, strict rounding ---------------------
 //
-// Persistent CTAs walk the rows with a stride of gridDim.x and keep three rows in flight
+// Persistent CTAs walk the rows with a stride of gridDim.x and keep the next row in flight
 // through a shared-memory ring while one is reduced and quantized.  The arithmetic is arranged to work on packed bf16
 // pairs: |x| and max on packed bf16, the division as three packed bf16 FMAs that give the
 // correctly rounded bf16 quotient, one conversion per value and a saturating pack.  Rows whose
@@ -322,10 +330,16 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
 // per-element recipe.
 
 // kRowVec: 16-byte vectors per thread; rows up to 256 * kRowVec * 8 elements (4: 8192, 8: 16384)
-constexpr int kRowDepth = 4;  // rows per CTA in the shared-memory ring: one in use, three in flight
+// Two rows per CTA in the shared-memory ring (one in use, one in flight) and six CTAs per SM:
+// the row loop is a dependent chain (wait for the row, reduce across the CTA, barrier, divide,
+// convert, store), so warps hide it better than a deeper ring does.  [4096, 8192] / [16384,
+// 8192] bf16: 25.3 / 83.9 us with four rows x three CTAs, 24.9 / 76.3 with three x four,
+// 23.1 / 74.7 with two x six, 26.2 / 88.6 with two x seven (36 registers: spills).
+constexpr int kRowDepth = 2;
+constexpr int kRowCtas = 6;
 
 template <int kRowVec>
-__global__ void __launch_bounds__(kThreads, kRowVec == 4 ? 3 : 2)
+__global__ void __launch_bounds__(kThreads, kRowVec == 4 ? kRowCtas : kRowCtas / 2)
 quantize_rows_bf16_s8_kernel(const uint4* __restrict__ x, int64_t segments, int nvec,
                              uint2* __restrict__ q, __nv_bfloat16* __restrict__ scale) {
   extern __shared__ uint4 ring[];   // [kRowDepth][nvec]; thread t only touches vectors t + 256 i
@@ -336,7 +350,7 @@ quantize_rows_bf16_s8_kernel(const uint4* __restrict__ x, int64_t segments, int 
   griddep_wait();
 
   // Rows reach shared memory through 16-byte cp.async copies that every thread issues for its
-  // own vectors, three rows ahead: the bytes in flight per SM no longer depend on registers.
+  // own vectors, kRowDepth - 1 rows ahead: the bytes in flight per SM do not depend on registers.
   int64_t fetch_row = blockIdx.x;
   int fetch_stage = 0;
   auto fetch = [&]() {
@@ -652,7 +666,7 @@ dequantize_kernel(const void* __restrict__ q, View vw, const void* __restrict__ 
       else for (int j = 0; j < nvalid; ++j) b[j] = reinterpret_cast<const uint8_t*>(q)[off + j];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        code[j] = (O == Out::kE4M3) ? e4m3_to_float(b[j]) : (float)(int8_t)b[j];
+        code[j] = (O == Out::kE4M3 || O == Out::kMX8) ? e4m3_to_float(b[j]) : (float)(int8_t)b[j];
     }
     // scale group of each of the eight columns: one division, then a running remainder
     int64_t g = gbase + col / vw.tc;
@@ -727,6 +741,7 @@ int dispatch_out(int qtype, Fn&& fn) {
     case QWX_S4U: return fn(std::integral_constant<Out, Out::kS4U>{});
     case QWX_S4: return fn(std::integral_constant<Out, Out::kS4P>{});
     case QWX_E4M3: return fn(std::integral_constant<Out, Out::kE4M3>{});
+    case QWX_MXFP8: return fn(std::integral_constant<Out, Out::kMX8>{});
     default: return (int)QWX_ERR_DTYPE;
   }
 }
@@ -740,7 +755,7 @@ bool row_segment_view(const void* x, const void* q, int64_t tp, int64_t tr, int6
 int check_method(int method, int has_arg, int qtype) {
   if (method != QWX_ABSMAX && method != QWX_MINMAX && method != QWX_RMS) return QWX_ERR_UNSUPPORTED;
   if (method == QWX_RMS && !has_arg) return QWX_ERR_SHAPE;
-  if (method == QWX_MINMAX && qtype == QWX_E4M3) return QWX_ERR_DTYPE;  // numerics.py:64-92
+  if (method == QWX_MINMAX && (qtype == QWX_E4M3 || qtype == QWX_MXFP8)) return QWX_ERR_DTYPE;  // numerics.py:64-92
   return QWX_OK;
 }
 
@@ -816,7 +831,7 @@ int qwx_compute_scale_zero_point(const void* calib_a, const void* calib_b, int d
                                  int qtype, void* scale, void* zero_point, qwx_stream_t stream) {
   if (!calib_a || !scale) return QWX_ERR_NULL;
   if (calib_b && !zero_point) return QWX_ERR_NULL;
-  if (calib_b && qtype == QWX_E4M3) return QWX_ERR_DTYPE;
+  if (calib_b && (qtype == QWX_E4M3 || qtype == QWX_MXFP8)) return QWX_ERR_DTYPE;
   if (n <= 0) return QWX_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned blocks = (unsigned)((n + 255) / 256);
@@ -832,6 +847,9 @@ int qwx_compute_scale_zero_point(const void* calib_a, const void* calib_b, int d
       case QWX_E4M3:
         scale_zero_point_kernel<T, E4M3><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
         break;
+      case QWX_MXFP8:
+        scale_zero_point_kernel<T, MX8><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
+        break;
       default: return (int)QWX_ERR_DTYPE;
     }
     QWX_CHECK_LAUNCH();
@@ -844,7 +862,7 @@ int qwx_quantize_with_scale(const void* x, int x_dtype, int64_t P, int64_t R, in
                             const void* zero_point, int qtype, int rounding, void* q,
                             qwx_stream_t stream) {
   if (!x || !scale || !q) return QWX_ERR_NULL;
-  if (zero_point && qtype == QWX_E4M3) return QWX_ERR_DTYPE;
+  if (zero_point && (qtype == QWX_E4M3 || qtype == QWX_MXFP8)) return QWX_ERR_DTYPE;
   View vw;
   int rc = make_view(P, R, C, tp, tr, tc, &vw);
   if (rc) return rc;
@@ -872,7 +890,7 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
     if (x_dtype == QWX_BF16 && qtype == QWX_S8 && method == QWX_ABSMAX && !has_arg &&
         rounding == QWX_STRICT && tc > 32 * 8 * kCache && tc <= kThreads * 8 * 8) {
       const bool wide = tc > kThreads * 4 * 8;   // rows of 8193..16384 values: 8 vectors per thread
-      const int64_t cap = 148 * (wide ? 2 : 4);
+      const int64_t cap = 148 * (wide ? kRowCtas / 2 : kRowCtas);
       const unsigned grid = (unsigned)(segments < cap ? segments : cap);
       const size_t ring_bytes = (size_t)kRowDepth * (tc / 8) * 16;
       static PerDeviceOnce configured;

@@ -85,6 +85,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// Contiguous copy global -> shared (both 16-byte aligned, size a multiple of 16), counted on `bar`.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 // ---- tensor memory ------------------------------------------------------------------------
 
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
@@ -143,6 +150,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
   return d;
 }
 
+// The same descriptor for a matrix stored without swizzling: 8 rows x 16 bytes are one
+// contiguous 128-byte core matrix; `sbo_bytes` is the distance between core matrices along the
+// rows, `lbo_bytes` along K.
+__device__ __forceinline__ uint64_t make_smem_desc_plain(uint32_t addr, uint32_t lbo_bytes,
+                                                         uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
 // Instruction descriptor (32 bits):
 //   [4,6) D format (0 f16, 1 f32, 2 s32)   [7,10) A format   [10,13) B format
 //   [15] A is MN-major   [16] B is MN-major   [17,23) N >> 3   [24,29) M >> 4
@@ -176,6 +196,37 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
+}
+
+// Block-scaled MMA (kind::mxf8f6f4, one E8M0 scale per 32 contracted elements of every row of
+// A and of B, float32 accumulators).  Instruction descriptor:
+//   [4,6) which byte of B's scale word   [7,10) A format (0 = e4m3)   [10,13) B format
+//   [15] A is MN-major   [16] B is MN-major   [17,23) N >> 3   [23] scale format (1 = E8M0)
+//   [24,29) M >> 4   [29,31) which byte of A's scale word
+// Scales sit in tensor memory: for row r of a 128-row operand tile, lane r % 32 (the same in
+// every lane quarter), column r / 32, and the four bytes of that 32-bit word belong to four
+// consecutive 32-wide K blocks.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_fmt, uint32_t b_fmt,
+                                                     uint32_t a_mn_major, uint32_t b_mn_major,
+                                                     uint32_t m, uint32_t n, uint32_t sf_byte) {
+  return (sf_byte << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) |
+         (b_mn_major << 16) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_byte << 29);
+}
+__device__ __forceinline__ void mma_mx_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+        "r"(sfb_tmem)
+      : "memory");
+}
+// 32 rows x 16 bytes of shared memory into 32 lanes x 4 columns of tensor memory, the same
+// data in all four lane quarters.  Ordered with the MMAs this thread issues before and after.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc)
+               : "memory");
 }
 
 // Arrive on `bar` once every MMA issued so far by this thread has finished (implies

@@ -201,6 +201,32 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
     ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Ret<Buf>().Attr<int32_t>("k_axis")
         .Attr<int64_t>("k_tile").Attr<int32_t>("t_major"));
 
+// ---- MXFP8 block-scaled contraction --------------------------------------------------------------
+
+ffi::Error MxPackScalesImpl(cudaStream_t stream, Buf scale, Out packed, int32_t operand, int64_t rows,
+                            int64_t k, int32_t k_major) {
+  return Status(qwx_mx_pack_scales(operand, scale.untyped_data(), FloatCode(scale.element_type()), rows, k,
+                                   k_major, packed->untyped_data(), packed->size_bytes(), S(stream)));
+}
+XLA_FFI_DEFINE_HANDLER_SYMBOL(
+    qwx_mx_pack_scales_ffi, MxPackScalesImpl,
+    ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Ret<Buf>().Attr<int32_t>("operand")
+        .Attr<int64_t>("rows").Attr<int64_t>("k").Attr<int32_t>("k_major"));
+
+ffi::Error GemmMx8Impl(cudaStream_t stream, Buf a, Buf b, Buf sfa, Buf sfb, Out out, Out err,
+                       int32_t b_layout) {
+  const auto ad = a.dimensions();
+  const auto od = out->dimensions();
+  return Status(qwx_gemm_mx8(a.untyped_data(), b.untyped_data(), b_layout, ad[0], od[1], ad[1],
+                             sfa.untyped_data(), sfb.untyped_data(), out->untyped_data(),
+                             OutCode(out->element_type()), static_cast<int32_t*>(err->untyped_data()),
+                             S(stream)));
+}
+XLA_FFI_DEFINE_HANDLER_SYMBOL(
+    qwx_gemm_mx8_ffi, GemmMx8Impl,
+    ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Arg<Buf>().Arg<Buf>().Arg<Buf>()
+        .Ret<Buf>().Ret<Buf>().Attr<int32_t>("b_layout"));
+
 ffi::Error QuantGemmQ8Impl(cudaStream_t stream, Buf a, Buf wq, Buf sw, Out out, Out workspace, Out err,
                            int32_t b_layout, int32_t rounding, int32_t epilogue) {
   const auto ad = a.dimensions();
