@@ -194,7 +194,9 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                                       ? make_smem_desc(sb + kk * XUMMA_K, 16, 1024)
                                       : make_smem_desc(sb + kk * XUMMA_K * 128, XK * 128, 1024);
               const uint32_t idesc = make_idesc_mx(0, 0, 0, BLAYOUT == QWX_B_KN ? 1 : 0, XM, XN, kk);
-              mma_mx_ss(tmem_base + acc * kXAccCols, da, db, idesc, tsfa, tsfb, kb != 0 || kk != 0);
+              // which of the word's four bytes: in the descriptor and in the two top bits of the addresses
+              mma_mx_ss(tmem_base + acc * kXAccCols, da, db, idesc, tsfa | ((uint32_t)kk << 30),
+                        tsfb | ((uint32_t)kk << 30), kb != 0 || kk != 0);
             }
             mma_commit(smem_u32(&ctl->empty[stage]));
             if (kb == kblocks - 1) mma_commit(smem_u32(&ctl->acc_full[acc]));
