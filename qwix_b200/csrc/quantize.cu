@@ -138,8 +138,9 @@ __device__ __forceinline__ void store_code1(void* q, int64_t i, int c) {
 //
 // G threads own one segment of `tc` contiguous elements: load it once into registers
 // (up to kCache vectors per thread; longer segments are re-read and mostly hit L2),
-// reduce, derive the scale, quantize from registers.  G = 32: one warp per segment,
-// G = 256: one CTA per segment.
+// reduce, derive the scale, quantize from registers.  G threads per segment: 4, 8 or 16 lanes of
+// a warp for segments of 32 / 64 / 128 values (microscaling blocks, small sub-channel tiles: a
+// whole warp would leave 28 lanes idle), 32: one warp, 256: one CTA.
 
 constexpr int kCache = 4;
 
@@ -228,7 +229,7 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
     // max over non-negative floats == max over their bit patterns (NaN sorts last).
     uint32_t b0 = __float_as_uint(r0), b1 = __float_as_uint(r1);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int o = (G < 32 ? G : 32) / 2; o > 0; o >>= 1) {
       b0 = max(b0, __shfl_xor_sync(0xffffffffu, b0, o));
       b1 = max(b1, __shfl_xor_sync(0xffffffffu, b1, o));
     }
@@ -922,10 +923,22 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
       return dispatch_out(qtype, [&](auto o) {
         constexpr Out O = decltype(o)::value;
         cudaError_t e;
-        if (tc <= 32 * 8 * kCache) {
-          const int64_t blocks = (segments + 7) / 8;
-          e = launch_dependent(quantize_rows_kernel<T, O, 32>, dim3((unsigned)blocks), dim3(kThreads), 0, st,
-                               x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);
+        auto small = [&](auto g) {
+          constexpr int G = decltype(g)::value;
+          const int64_t blocks = (segments + kThreads / G - 1) / (kThreads / G);
+          return launch_dependent(quantize_rows_kernel<T, O, G>, dim3((unsigned)blocks), dim3(kThreads), 0, st,
+                                  x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);
+        };
+        // one 16-byte vector per lane where the segment is shorter than a warp's worth (the sum
+        // of squares keeps the whole-warp order)
+        if (tc <= 32 && method != QWX_RMS) {
+          e = small(std::integral_constant<int, 4>{});
+        } else if (tc <= 64 && method != QWX_RMS) {
+          e = small(std::integral_constant<int, 8>{});
+        } else if (tc <= 128 && method != QWX_RMS) {
+          e = small(std::integral_constant<int, 16>{});
+        } else if (tc <= 32 * 8 * kCache) {
+          e = small(std::integral_constant<int, 32>{});
         } else {
           e = launch_dependent(quantize_rows_kernel<T, O, 256>, dim3((unsigned)segments), dim3(kThreads), 0,
                                st, x, segments, tc, cal, rounding, q, scale, (int8_t*)zero_point);

@@ -161,6 +161,38 @@ def test_int4_weight_only_full_size(tokens):
   assert ok, msg
 
 
+def test_mxfp8_block_scaled_full_size():
+  """A [4096, 8192] x W [8192, 8192] under an mxfp8 rule: 32 x 37 tiles of 128 x 224, eight per
+  CTA; the oracle recomputes a sample of rows against the device's weight codes."""
+  from oracle import mxfp_dot as omx
+  M, K, N = 4096, 8192, 8192
+  a = np.random.default_rng(8).standard_normal((M, K), dtype=np.float32)
+  a[:, np.random.default_rng(9).choice(K, K // 100, replace=False)] *= 20.0
+  a = a.astype(bf16)
+  w = (0.02 * np.random.default_rng(10).standard_normal((K, N), dtype=np.float32)).astype(bf16)
+  kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=32, qtype='mxfp8')
+  aq = bq.quantize(h.to_torch(a), bdg.get_how_to_quantize(for_lhs=True, **kw))
+  wq = bq.quantize(h.to_torch(w), bdg.get_how_to_quantize(for_lhs=False, **kw))
+  out = bdg.dot_general(aq, wq, DN)
+  _lib.raise_on_device_error()
+  rows = np.array([t * 128 + (37 * t + 11) % 128 for t in range(32)])
+  a_o = oq.quantize(a[rows], odg.get_how_to_quantize(for_lhs=True, **kw))
+  ri = torch.as_tensor(rows, device='cuda')
+  assert h.codes_equal(aq.qvalue[ri], a_o.qvalue)
+  assert np.array_equal(h.to_numpy(aq.scale[ri]).view(np.uint8), a_o.scale.view(np.uint8))
+  cols = np.random.default_rng(11).choice(N, 256, replace=False)
+  w_o = oq.quantize(w[:, cols], odg.get_how_to_quantize(for_lhs=False, **kw))
+  ci = torch.as_tensor(cols, device='cuda')
+  assert h.codes_equal(wq.qvalue[:, ci], w_o.qvalue)
+  assert np.array_equal(h.to_numpy(wq.scale[:, ci]).view(np.uint8), w_o.scale.view(np.uint8))
+  w_full = oq.QArray(h.to_numpy(wq.qvalue), h.to_numpy(wq.scale), None, 'mxfp8')
+  want = omx.mxfp_dot_general(a_o, w_full, DN).astype(np.float32)
+  got = h.to_numpy(out[ri]).astype(np.float32)
+  # float32 accumulation of exact block products, one rounding to bf16
+  assert np.all(np.abs(got - want) <= 2.0 ** -7 * np.maximum(np.abs(want), 2.0 ** -6))
+  assert np.mean(got == want) > 0.98
+
+
 def test_hadamard_fp8_full_size():
   """A [8192, 4096] Student-t x W [4096, 14336]: 128-point blocks, e4m3 per row / per column."""
   M, K, N = 8192, 4096, 14336
