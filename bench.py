@@ -387,13 +387,24 @@ def w4_records(args, device, with_cpu: bool):
     a = torch.randn(Mw, Kw, device=device, dtype=torch.bfloat16,
                     generator=torch.Generator(device).manual_seed(4))
     out = torch.empty(Mw, Nw, device=device, dtype=torch.bfloat16)
-    ws = torch.zeros(L.qwx_gemm_a16w4_workspace_bytes(Mw, Nw), dtype=torch.uint8, device=device)
+    tensor_core = Mw >= weight_only.TENSOR_CORE_MIN_ROWS      # the dispatch of weight_only.matmul
+    if tensor_core:
+      for wq in sets:
+        weight_only.prepare_tiles(wq)
+      ws = torch.zeros(L.qwx_gemm_a16w4_mma_workspace_bytes(Mw, Nw), dtype=torch.uint8, device=device)
+    else:
+      ws = torch.zeros(L.qwx_gemm_a16w4_workspace_bytes(Mw, Nw), dtype=torch.uint8, device=device)
     fused_path = weight_only.eligible(a, sets[0], DN)
 
     def call(i):
       wq = sets[i % len(sets)]
       if not fused_path:
         return bdg.dot_general(a, wq, DN, preferred_element_type=torch.bfloat16)
+      if tensor_core:
+        _lib.check(L.qwx_gemm_a16w4_mma(_lib.ptr(a), _lib.ptr(wq._w4_tiles), _lib.ptr(wq._w4_scale), _lib.F32,
+                                        Mw, Nw, Kw, 128, _lib.ptr(out), _lib.BF16, _lib.ptr(ws), ws.numel(), 1,
+                                        _lib.ptr(err), _lib.stream_ptr(device)), 'gemm_a16w4_mma')
+        return None
       _lib.check(L.qwx_gemm_a16w4(_lib.ptr(a), _lib.ptr(wq._w4_packed), _lib.ptr(wq._w4_scale), _lib.F32,
                                   Mw, Nw, Kw, 128, _lib.ptr(out), _lib.BF16, _lib.ptr(ws), ws.numel(), 1,
                                   _lib.ptr(err), _lib.stream_ptr(device)), 'gemm_a16w4')
@@ -431,7 +442,7 @@ def w4_records(args, device, with_cpu: bool):
         'roofline': {'bound': 'hbm', 'achieved': nbytes / ms / 1e6, 'peak': peaks['hbm_gbs'],
                      'unit': 'GB/s', 'frac': nbytes / ms / 1e6 / peaks['hbm_gbs'], 'traffic': None,
                      'algorithmic_bytes': nbytes,
-                     'kernel': 'gemm_w4_kernel' if fused_path else 'dequantize_kernel + library bf16 GEMM',
+                     'kernel': ('gemm_w4_mma_kernel (tcgen05)' if tensor_core else 'gemm_w4_kernel') if fused_path else 'dequantize_kernel + library bf16 GEMM',
                      'peak_source': f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})"},
         'e2e': {'value': nbytes / e2e_ms / 1e6, 'unit': 'GB/s', 'ms_per_step': e2e_ms,
                 'h2d_bytes_per_step': Mw * Kw * 2, 'd2h_bytes_per_step': Mw * Nw * 2},

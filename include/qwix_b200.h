@@ -375,6 +375,29 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
                    void* workspace, size_t workspace_bytes, int workspace_is_zero,
                    int32_t* error_flag, qwx_stream_t stream);
 
+/* The same contraction on the tcgen05 tensor cores, for batches the warp-level kernel above
+ * would stream the weight several times for (33 tokens and more; M <= 128 per call):
+ *   out[m, n] = sum_k a[m, k] * bf16( q[k, n] * scale[k / k_tile, n] )
+ * The codes are unpacked and scaled into shared memory as bfloat16 and contracted with the
+ * activation in one float32 accumulation over all of K.  With bf16 scales that is the
+ * reference's arithmetic (dequantize to the scale dtype, qarray.py:692-708, then a bf16 dot with
+ * float32 accumulation, dot_general.py:264-275); with float32 scales the reference keeps q * s in
+ * float32 and this kernel rounds it once to bfloat16.
+ * w_tiles: the weight in this kernel's layout, made once by qwx_pack_w4_tiles from the logical
+ * codes q[K, N] (QWX_S4U): [N / 128][K / 128][128 channels][64 bytes].  K a multiple of 128;
+ * scale [K / k_tile, N] in f32 or bf16, k_tile a multiple of 128; out bf16 or f32 [M, N].
+ * workspace: qwx_gemm_a16w4_mma_workspace_bytes(M, N) bytes, zero on entry, left zero (partial
+ * sums of channel tiles that several CTAs share, added with float32 atomics: the order of those
+ * additions, and with it the last bits of such tiles, can differ between runs).
+ * error_flag receives QWX_ERR_DEVICE_WAIT if a bounded device-side wait runs out. */
+size_t qwx_w4_tiles_packed_bytes(int64_t K, int64_t N);
+int qwx_pack_w4_tiles(const void* q, int64_t K, int64_t N, void* packed, qwx_stream_t stream);
+size_t qwx_gemm_a16w4_mma_workspace_bytes(int64_t M, int64_t N);
+int qwx_gemm_a16w4_mma(const void* a, const void* w_tiles, const void* scale, int scale_dtype,
+                       int64_t M, int64_t N, int64_t K, int64_t k_tile, void* out, int out_dtype,
+                       void* workspace, size_t workspace_bytes, int workspace_is_zero,
+                       int32_t* error_flag, qwx_stream_t stream);
+
 /* Blockwise Hadamard rotation, the arithmetic of qwix/contrib/hadamard_rot.py:35-117 with the
  * Sylvester matrix H of size `block` (= 128) and optional +/-1 sign vectors (int8, one entry
  * per index of the rotated axis; `signs_in` is applied before H, `signs_out` after it, as in

@@ -48,6 +48,11 @@ _SIGNATURES = {
     'qwx_w4_packed_bytes': (_sz, [_i64, _i64]),
     'qwx_pack_w4': (_int, [_vp, _i64, _i64, _vp, _vp]),
     'qwx_gemm_a16w4_workspace_bytes': (_sz, [_i64, _i64]),
+    'qwx_w4_tiles_packed_bytes': (_sz, [_i64, _i64]),
+    'qwx_pack_w4_tiles': (_int, [_vp, _i64, _i64, _vp, _vp]),
+    'qwx_gemm_a16w4_mma_workspace_bytes': (_sz, [_i64, _i64]),
+    'qwx_gemm_a16w4_mma': (_int, [_vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _sz, _int,
+                                  _vp, _vp]),
     'qwx_gemm_a16w4': (_int, [_vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _int, _vp, _sz, _int,
                               _vp, _vp]),
     'qwx_hadamard_rotate': (_int, [_vp, _int, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp]),

@@ -70,6 +70,38 @@ def prepare(rhs: QArray) -> torch.Tensor:
   return packed
 
 
+# From this many token rows on the contraction runs on the tcgen05 tensor cores
+# (csrc/gemm_w4_mma.cu: int4 -> scaled bf16 in shared memory, one float32 accumulation over all
+# of K); below it the warp-level kernel keeps float32 scales in float32.
+TENSOR_CORE_MIN_ROWS = 33
+
+
+def prepare_tiles(rhs: QArray) -> torch.Tensor:
+  """Packs the weight into the tensor-core kernel's tile layout (once; cached on the QArray)."""
+  cached = getattr(rhs, '_w4_tiles', None)
+  if cached is not None:
+    return cached
+  K, N = rhs.shape
+  L = _lib.lib()
+  q = rhs.qvalue.contiguous()
+  packed = torch.empty(L.qwx_w4_tiles_packed_bytes(K, N), dtype=torch.uint8, device=q.device)
+  _lib.check(L.qwx_pack_w4_tiles(_lib.ptr(q), K, N, _lib.ptr(packed), _lib.stream_ptr(q.device)),
+             'pack_w4_tiles')
+  rhs._w4_tiles = packed
+  rhs._w4_scale = rhs.scale.contiguous()
+  return packed
+
+
+def _workspace_mma(device, M: int, N: int) -> torch.Tensor:
+  key = (device, torch.cuda.current_stream(device).cuda_stream, 'mma', 32 if M <= 32 else (64 if M <= 64 else 128))
+  with _ws_lock:
+    ws = _ws_cache.get(key)
+    if ws is None:
+      ws = torch.zeros(_lib.lib().qwx_gemm_a16w4_mma_workspace_bytes(M, N), dtype=torch.uint8, device=device)
+      _ws_cache[key] = ws
+  return ws
+
+
 def _workspace(device, M: int, N: int) -> torch.Tensor:
   """A zero-filled scratch buffer per (device, stream, shape).  The kernel leaves it zero, so
   it is cleared only once."""
@@ -86,8 +118,6 @@ def _workspace(device, M: int, N: int) -> torch.Tensor:
 def matmul(lhs: torch.Tensor, rhs: QArray, out_dtype: torch.dtype) -> torch.Tensor:
   """lhs [.., K] @ dequantize(rhs) [K, N] -> [.., N]."""
   K, N = rhs.shape
-  packed = prepare(rhs)
-  scale = rhs._w4_scale
   x = lhs.reshape(-1, K).contiguous()
   rows = x.shape[0]
   out = torch.empty((rows, N), dtype=out_dtype, device=x.device)
@@ -95,6 +125,19 @@ def matmul(lhs: torch.Tensor, rhs: QArray, out_dtype: torch.dtype) -> torch.Tens
   L = _lib.lib()
   tile = K // rhs.scale.shape[0]
   oc = _lib.BF16 if out_dtype == torch.bfloat16 else _lib.F32
+  if rows >= TENSOR_CORE_MIN_ROWS:
+    tiles = prepare_tiles(rhs)
+    scale = rhs._w4_scale
+    for r0 in range(0, rows, _MAX_ROWS_PER_CALL):
+      m = min(_MAX_ROWS_PER_CALL, rows - r0)
+      ws = _workspace_mma(x.device, m, N)
+      _lib.check(L.qwx_gemm_a16w4_mma(
+          _lib.ptr(x[r0:r0 + m]), _lib.ptr(tiles), _lib.ptr(scale),
+          numerics.code_of_float(scale.dtype), m, N, K, tile, _lib.ptr(out[r0:r0 + m]), oc,
+          _lib.ptr(ws), ws.numel(), 1, _lib.ptr(err), _lib.stream_ptr(x.device)), 'gemm_a16w4_mma')
+    return out.reshape(*lhs.shape[:-1], N)
+  packed = prepare(rhs)
+  scale = rhs._w4_scale
   for r0 in range(0, rows, _MAX_ROWS_PER_CALL):
     m = min(_MAX_ROWS_PER_CALL, rows - r0)
     ws = _workspace(x.device, m, N)

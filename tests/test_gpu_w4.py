@@ -91,3 +91,55 @@ def test_a16w4_float32_output_is_tight(sdt):
                        scale_dtype=torch.float32 if sdt == 'float32' else torch.bfloat16)
   got = bdg.dot_general(h.to_torch(a), wq, DN, preferred_element_type=torch.float32)
   assert np.abs(got.cpu().numpy() - want).max() <= 2e-5 * np.abs(want).max()
+
+
+@pytest.mark.parametrize('M', [33, 64, 100, 128])
+def test_tensor_core_path_with_bf16_scales_is_the_reference_arithmetic(M):
+  """From 33 tokens on the weight is dequantized to bfloat16 in shared memory and contracted on
+  the tcgen05 tensor cores with one float32 accumulation: with bfloat16 scales exactly what the
+  reference does (qarray.py:692-708, dot_general.py:264-275), so only the order of the float32
+  sum and the final rounding can differ."""
+  K, N = 2048, 1152           # nine channel tiles on 148 CTAs: every tile is shared (split K)
+  rng = np.random.default_rng(M)
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32).astype(ml_dtypes.bfloat16)
+  a = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.bfloat16)
+  wo = oq.quantize_api(w, 'int4', channelwise_axes=[1], tiled_axes={0: 128},
+                       scale_dtype=ml_dtypes.bfloat16)
+  wq = bq.quantize_api(h.to_torch(w), 'int4', channelwise_axes=[1], tiled_axes={0: 128},
+                       scale_dtype=torch.bfloat16)
+  assert M >= weight_only.TENSOR_CORE_MIN_ROWS
+  got = bdg.dot_general(h.to_torch(a), wq, DN, preferred_element_type=torch.float32)
+  from qwix_b200 import _lib
+  _lib.raise_on_device_error()
+  wt = oq.dequantize(wo)                                  # bf16( q * s ), the reference's weight
+  assert wt.dtype == np.dtype(ml_dtypes.bfloat16)
+  want = a.astype(np.float64) @ wt.astype(np.float64)
+  assert np.abs(got.cpu().numpy() - want).max() <= 2e-5 * np.abs(want).max()
+
+
+def test_tensor_core_entry_point_takes_few_tokens_too():
+  """qwx_gemm_a16w4_mma called directly with 5 and 32 tokens (32 tensor-memory columns)."""
+  from qwix_b200 import _lib
+  L = _lib.lib()
+  K, N = 1024, 400            # N is no multiple of 128: the last channel tile is ragged
+  rng = np.random.default_rng(3)
+  w = (0.02 * rng.standard_normal((K, N))).astype(np.float32).astype(ml_dtypes.bfloat16)
+  wo = oq.quantize_api(w, 'int4', channelwise_axes=[1], tiled_axes={0: 256}, scale_dtype=np.float32)
+  wq = bq.quantize_api(h.to_torch(w), 'int4', channelwise_axes=[1], tiled_axes={0: 256},
+                       scale_dtype=torch.float32)
+  tiles = weight_only.prepare_tiles(wq)
+  for M in (5, 32):
+    a = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    at = h.to_torch(a)
+    out = torch.empty((M, N), dtype=torch.float32, device='cuda')
+    nws = L.qwx_gemm_a16w4_mma_workspace_bytes(M, N)
+    ws = torch.zeros(nws, dtype=torch.uint8, device='cuda')
+    err = _lib.error_flag(out.device)
+    _lib.check(L.qwx_gemm_a16w4_mma(_lib.ptr(at), _lib.ptr(tiles), _lib.ptr(wq._w4_scale), _lib.F32, M, N, K,
+                                    256, _lib.ptr(out), _lib.F32, _lib.ptr(ws), nws, 1, _lib.ptr(err),
+                                    _lib.stream_ptr()), 'gemm_a16w4_mma')
+    _lib.raise_on_device_error()
+    wt = (wo.qvalue.astype(np.float32) * np.repeat(wo.scale, 256, axis=0)).astype(ml_dtypes.bfloat16)
+    want = a.astype(np.float64) @ wt.astype(np.float64)
+    assert np.abs(out.cpu().numpy() - want).max() <= 2e-5 * np.abs(want).max()
+    assert int(ws.view(torch.int32).abs().max().item()) == 0      # the scratch is left zero
