@@ -265,6 +265,30 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
     ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Arg<Buf>().Arg<Buf>().Ret<Buf>()
         .Ret<Buf>().Attr<int64_t>("K").Attr<int64_t>("k_tile"));
 
+ffi::Error PackW4TilesImpl(cudaStream_t stream, Buf q, Out packed) {
+  const auto d = q.dimensions();
+  if ((int64_t)q.size_bytes() != d[0] * d[1])   // one code per byte is what the packer reads
+    return Status(QWX_ERR_SHAPE);
+  return Status(qwx_pack_w4_tiles(q.untyped_data(), d[0], d[1], packed->untyped_data(), S(stream)));
+}
+XLA_FFI_DEFINE_HANDLER_SYMBOL(qwx_pack_w4_tiles_ffi, PackW4TilesImpl,
+                              ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Ret<Buf>());
+
+ffi::Error GemmA16W4MmaImpl(cudaStream_t stream, Buf a, Buf w_tiles, Buf scale, Out out, Out workspace,
+                            Out err, int64_t K, int64_t k_tile) {
+  const auto od = out->dimensions();
+  return Status(qwx_gemm_a16w4_mma(a.untyped_data(), w_tiles.untyped_data(), scale.untyped_data(),
+                                   FloatCode(scale.element_type()), od[0], od[1], K, k_tile,
+                                   out->untyped_data(), FloatCode(out->element_type()),
+                                   workspace->untyped_data(), workspace->size_bytes(),
+                                   /*workspace_is_zero=*/0, static_cast<int32_t*>(err->untyped_data()),
+                                   S(stream)));
+}
+XLA_FFI_DEFINE_HANDLER_SYMBOL(
+    qwx_gemm_a16w4_mma_ffi, GemmA16W4MmaImpl,
+    ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Arg<Buf>().Arg<Buf>().Ret<Buf>()
+        .Ret<Buf>().Ret<Buf>().Attr<int64_t>("K").Attr<int64_t>("k_tile"));
+
 // ---- Hadamard family ------------------------------------------------------------------------
 
 ffi::Error HadamardRotateImpl(cudaStream_t stream, Buf x, Buf signs_in, Buf signs_out, Out out, int32_t axis,
