@@ -184,7 +184,8 @@ def test_mxfp8_block_scaled_full_size():
   w_o = oq.quantize(w[:, cols], odg.get_how_to_quantize(for_lhs=False, **kw))
   ci = torch.as_tensor(cols, device='cuda')
   assert h.codes_equal(wq.qvalue[:, ci], w_o.qvalue)
-  assert np.array_equal(h.to_numpy(wq.scale[:, ci]).view(np.uint8), w_o.scale.view(np.uint8))
+  assert np.array_equal(h.to_numpy(wq.scale[:, ci]).view(np.uint8),
+                        np.ascontiguousarray(w_o.scale).view(np.uint8))
   w_full = oq.QArray(h.to_numpy(wq.qvalue), h.to_numpy(wq.scale), None, 'mxfp8')
   want = omx.mxfp_dot_general(a_o, w_full, DN).astype(np.float32)
   got = h.to_numpy(out[ri]).astype(np.float32)
