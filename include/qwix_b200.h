@@ -384,7 +384,7 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
  * float32 accumulation, dot_general.py:264-275); with float32 scales the reference keeps q * s in
  * float32 and this kernel rounds it once to bfloat16.
  * w_tiles: the weight in this kernel's layout, made once by qwx_pack_w4_tiles from the logical
- * codes q[K, N] (QWX_S4U): [N / 128][K / 128][128 channels][64 bytes].  K a multiple of 128;
+ * codes q[K, N] (QWX_S4U): [N / 128][K / 128][4 quarters of 32 K][128 channels][16 bytes].  K a multiple of 128;
  * scale [K / k_tile, N] in f32 or bf16, k_tile a multiple of 128; out bf16 or f32 [M, N].
  * workspace: qwx_gemm_a16w4_mma_workspace_bytes(M, N) bytes, zero on entry, left zero (partial
  * sums of channel tiles that several CTAs share, added with float32 atomics: the order of those

@@ -93,7 +93,7 @@ constexpr size_t wm_smem_bytes() {
 struct WmParams {
   int M;
   int64_t N, K;
-  const uint4* wp;        // [N / 128][K / 128][128 channels][64 B]
+  const uint4* wp;        // [N / 128][K / 128][4 quarters of 32 K][128 channels][16 B]
   const void* scale;      // [K / tile, N], f32 or bf16
   int scale_dtype;
   int tile;               // scale tile along K (multiple of 128)
@@ -301,8 +301,11 @@ gemm_w4_mma_kernel(const __grid_constant__ CUtensorMap tma_a, const WmParams p) 
     const int gt = threadIdx.x - (kWmConvWarp0 + group * kWmGroupWarps) * 32;      // 0..127
     const bool f32scale = p.scale_dtype == QWX_F32;
     bool ok = true;
-    // a thread's four 16-byte pieces of a unit: (row, quarter of the 128 K) = (gt / 4 + 32 h, gt % 4)
-    const int row0 = gt >> 2, quarter = gt & 3;
+    // a thread's four 16-byte pieces of a unit: quarter gt / 32 of the 128 K (one per warp), rows
+    // gt % 32 + 32 h.  Eight neighbouring lanes then write eight different rows of one 16-byte
+    // column, which the 128-byte swizzle spreads over all banks (rows x quarters per warp gave
+    // 2-way conflicts on every store: 54 % of the shared-memory wavefronts).
+    const int row0 = gt & 31, quarter = gt >> 5;
     for (long long u = u_begin + group; u < u_end && ok; u += kWmGroups) {
       const long long i = u - u_begin;
       const int tile = (int)(u / S);
@@ -316,7 +319,7 @@ gemm_w4_mma_kernel(const __grid_constant__ CUtensorMap tma_a, const WmParams p) 
       const uint8_t* src = packed_ptr + (size_t)slot * kWmSlotBytes;
       uint4 c[4];
 #pragma unroll
-      for (int h = 0; h < 4; ++h) c[h] = reinterpret_cast<const uint4*>(src)[h * 128 + gt];
+      for (int h = 0; h < 4; ++h) c[h] = reinterpret_cast<const uint4*>(src)[quarter * 128 + row0 + 32 * h];
       const int valid = (int)(p.N - (int64_t)tile * WT < WT ? p.N - (int64_t)tile * WT : WT);
       float t[4];
 #pragma unroll
@@ -458,15 +461,16 @@ gemm_w4_mma_kernel(const __grid_constant__ CUtensorMap tma_a, const WmParams p) 
   if (threadIdx.x == 0 && ctl->abort && p.error_flag) atomicExch(p.error_flag, QWX_ERR_DEVICE_WAIT);
 }
 
-// Logical codes q[K, N] (one sign-extended code per byte) -> [N / 128][K / 128][128][64 B]:
-// per channel and 128 K, sixteen 32-bit words of eight offset-binary nibbles each; nibble i of
-// a word holds K offset 2i for i < 4 and 2(i - 4) + 1 for i >= 4.  Channels past N hold zeros.
+// Logical codes q[K, N] (one sign-extended code per byte) -> [N / 128][K / 128][4][128][16 B]:
+// per 128 channels x 128 K, four quarters of 32 K, each holding 16 bytes (four 32-bit words of
+// eight offset-binary nibbles) per channel; nibble i of a word holds K offset 2i for i < 4 and
+// 2(i - 4) + 1 for i >= 4.  Channels past N hold zeros.
 __global__ void pack_w4_tiles_kernel(const int8_t* __restrict__ q, int64_t K, int64_t N,
                                      uint32_t* __restrict__ out, int64_t words) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= words) return;
-  const int word = (int)(i % 16);
-  const int row = (int)((i / 16) % WT);
+  const int word = (int)(i % 4) + 4 * (int)((i / (4 * WT)) % 4);    // word of the channel's 16
+  const int row = (int)((i / 4) % WT);
   const int64_t unit = i / (16 * WT);
   const int64_t S = K / WK;
   const int64_t tile = unit / S, ks = unit % S;
