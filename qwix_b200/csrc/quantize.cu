@@ -321,6 +321,53 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
   }
 }
 
+// ---- microscaling blocks: 32 consecutive values -> e4m3 codes + one power-of-two scale ------
+//
+// Four lanes per block, one 16-byte vector of input each (a warp reads 512 contiguous values),
+// absmax over the block with two shuffles, the scale by the outlier-aware rule, and -- the
+// scale being a power of two -- x / scale as an exact multiplication by its reciprocal.  Two
+// values per fp8 conversion instruction.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+quantize_mx8_blocks_kernel(const void* __restrict__ x, int64_t nvec, void* __restrict__ q,
+                           void* __restrict__ scale) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  const bool live = i < nvec;                 // whole groups of four: nvec is a multiple of 4
+  float v[8];
+  if (live) {
+    load8<T>(x, i * 8, v);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  }
+  uint32_t bits = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) bits = max(bits, __float_as_uint(v[j]) & 0x7fffffffu);   // NaN sorts last
+  bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 1));
+  bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 2));
+  if (!live) return;
+  const float s = symmetric_scale<T, MX8>(__uint_as_float(bits));
+  if ((threadIdx.x & 3) == 0) store1<T>(scale, i >> 2, s);
+  const float inv = __fdiv_rn(1.0f, s);       // exact: s is a power of two (or NaN, which propagates)
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      // the quotient in the input dtype (exact unless it underflows), NaN -> 0x7f, clip to +/-448
+      const float y0 = round_to<T>(__fmul_rn(v[4 * h + 2 * j], inv));
+      const float y1 = round_to<T>(__fmul_rn(v[4 * h + 2 * j + 1], inv));
+      const __nv_fp8x2_storage_t p2 = __nv_cvt_float2_to_fp8x2(make_float2(y0, y1), __NV_SATFINITE, __NV_E4M3);
+      packed |= (uint32_t)p2 << (16 * j);
+    }
+    w[h] = packed;
+  }
+  *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(q) + i * 8) = make_uint2(w[0], w[1]);
+}
+
 // ---- the per-token hot path: bf16 rows -> int8, absmax, strict rounding ---------------------
 //
 // Persistent CTAs walk the rows with a stride of gridDim.x and keep the next row in flight
@@ -912,6 +959,20 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
                : launch_dependent(quantize_rows_bf16_s8_kernel<4>, dim3(grid), dim3(kThreads), ring_bytes,
                                   st, (const uint4*)x, segments, (int)(tc / 8), (uint2*)q,
                                   (__nv_bfloat16*)scale);
+      if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)QWX_ERR_LAUNCH;
+      }
+      return (int)QWX_OK;
+    }
+    if (qtype == QWX_MXFP8 && tc == 32 && method == QWX_ABSMAX && !has_arg &&
+        (x_dtype == QWX_BF16 || x_dtype == QWX_F32)) {
+      const int64_t nvec = segments * 4;
+      const unsigned blocks = (unsigned)((nvec + kThreads - 1) / kThreads);
+      const cudaError_t e =
+          x_dtype == QWX_BF16
+              ? launch_dependent(quantize_mx8_blocks_kernel<BF16>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale)
+              : launch_dependent(quantize_mx8_blocks_kernel<F32>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale);
       if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return (int)QWX_ERR_LAUNCH;
