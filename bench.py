@@ -772,7 +772,8 @@ def decoder_record(args, dist, device, rank, world, lib_peaks, with_cpu: bool):
   from qwix_b200 import _lib
   from qwix_b200 import decoder as D
 
-  cfg = dataclasses.replace(D.DecoderConfig.llama3_8b(), layers=args.layers)
+  cfg = dataclasses.replace(D.DecoderConfig.llama3_8b(), layers=args.layers,
+                            attention_core=args.attention_core)
   model = D.Decoder(cfg, device=device, exact_act_scale=args.exact_act_scale)
   model.quantize_weights()
   ptq_model = qwix.quantize_model(model, qwix.PtqProvider(D.w8a8_rules()))
@@ -823,7 +824,7 @@ def decoder_record(args, dist, device, rank, world, lib_peaks, with_cpu: bool):
   if os.path.exists(GOLDEN_DECODER):
     with open(GOLDEN_DECODER) as f:
       gold = json.load(f)
-    if gold['layers'] == cfg.layers and gold['prompt'] == args.prompt:
+    if gold['layers'] == cfg.layers and gold['prompt'] == args.prompt and cfg.attention_core == 'sdpa':
       want = np.asarray(gold['logits'], np.float32)
       rel = float(np.linalg.norm(sample - want) / np.linalg.norm(want))
       # One GPU repeats the committed computation (bound 1e-2; observed ~1e-6).  Sharded runs
@@ -858,7 +859,7 @@ def decoder_record(args, dist, device, rank, world, lib_peaks, with_cpu: bool):
       'config': {'workload': 'Llama-3-8B-shaped decoder under a w8a8 rule: int8 per-channel weights, '
                              'per-token int8 activations on every projection',
                  'layers': cfg.layers, 'batch': args.batch, 'prompt': args.prompt, 'decode': args.decode,
-                 'parallelism': f'tp{world}',
+                 'parallelism': f'tp{world}', 'attention_core': cfg.attention_core,
                  'act_scale': 'global row absmax' if args.exact_act_scale else 'per shard',
                  'reduce': ('peer-memory sum inside the add+norm kernel' if model.comm.exchange is not None
                             else ('nccl all-reduce' if world > 1 else 'none'))},
@@ -1124,6 +1125,10 @@ def main():
   ap.add_argument('--prompt', type=int, default=2048)
   ap.add_argument('--decode', type=int, default=128)
   ap.add_argument('--decoder-runs', type=int, default=3)
+  ap.add_argument('--attention-core', default='sdpa', choices=['sdpa', 'einsum'],
+                  help="decoder workload: 'einsum' issues the attention core as two einsums that the "
+                       "w8a8 rule quantizes (slow: one GEMM per sequence and head); the committed logits "
+                       "sample is for 'sdpa'")
   ap.add_argument('--exact-act-scale', action='store_true')
   ap.add_argument('--write-golden', action='store_true',
                   help='decoder workload on one GPU: (re)write the logits sample under tests/golden/')

@@ -11,6 +11,7 @@ import ml_dtypes
 import numpy as np
 
 from oracle import dot_general as odg
+from oracle import einsum as oe
 from oracle import qarray as oq
 
 bf16 = ml_dtypes.bfloat16
@@ -36,13 +37,23 @@ def _rope(x, cos, sin):
   return np.concatenate([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).astype(bf16)
 
 
+def _act_einsum(einsum_str, a, b):
+  """An einsum of two activations under a rule with act_qtype set: both operands are quantized
+  per call (qwix/_src/providers/boxed_param.py:204-235)."""
+  how = lambda for_lhs: oe.get_how_to_quantize(einsum_str=einsum_str, ndims=(a.ndim, b.ndim),
+                                               for_lhs=for_lhs, tile_size=None, qtype='int8')
+  return oe.einsum(einsum_str, oq.quantize(a, how(True)), oq.quantize(b, how(False)))
+
+
 def quantize_weight(w):
   return oq.quantize(w, oq.HowToQuantize(qtype='int8', channelwise_axes=[1]))
 
 
-def forward(cfg, weights, tokens):
+def forward(cfg, weights, tokens, quantized_attention: bool = False):
   """weights: dict of bf16 NumPy arrays named like the torch model's full (unsharded) matrices.
-  tokens [B, T].  Returns float32 logits [B, T, vocab] of a causal prefill."""
+  tokens [B, T].  Returns float32 logits [B, T, vocab] of a causal prefill.
+  `quantized_attention`: the attention core as two intercepted einsums (scores and weighted
+  sum), both operands quantized per token, instead of float32 arithmetic."""
   B, T = tokens.shape
   hd, hq, hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
   x = weights['embed'][tokens]
@@ -60,12 +71,20 @@ def forward(cfg, weights, tokens):
     k = _rope(k.reshape(B, T, hkv, hd).transpose(0, 2, 1, 3), cos, sin)
     v = v.reshape(B, T, hkv, hd).transpose(0, 2, 1, 3)
     rep = hq // hkv
-    kf = np.repeat(k.astype(np.float32), rep, axis=1)
-    vf = np.repeat(v.astype(np.float32), rep, axis=1)
-    s = q.astype(np.float32) @ kf.transpose(0, 1, 3, 2) / np.sqrt(hd) + mask
-    p = np.exp(s - s.max(-1, keepdims=True))
-    p = p / p.sum(-1, keepdims=True)
-    att = (p @ vf).astype(bf16).transpose(0, 2, 1, 3).reshape(B, T, hq * hd)
+    if quantized_attention:
+      kr, vr = np.repeat(k, rep, axis=1), np.repeat(v, rep, axis=1)
+      s = _act_einsum('bnth,bnsh->bnts', q, kr).astype(np.float32) * np.float32(hd ** -0.5) + mask
+      p = np.exp(s - s.max(-1, keepdims=True))
+      p = (p / p.sum(-1, keepdims=True)).astype(bf16)
+      att = _act_einsum('bnts,bnsh->bnth', p, vr).astype(bf16)
+      att = att.transpose(0, 2, 1, 3).reshape(B, T, hq * hd)
+    else:
+      kf = np.repeat(k.astype(np.float32), rep, axis=1)
+      vf = np.repeat(v.astype(np.float32), rep, axis=1)
+      s = q.astype(np.float32) @ kf.transpose(0, 1, 3, 2) / np.sqrt(hd) + mask
+      p = np.exp(s - s.max(-1, keepdims=True))
+      p = p / p.sum(-1, keepdims=True)
+      att = (p @ vf).astype(bf16).transpose(0, 2, 1, 3).reshape(B, T, hq * hd)
     x = (x.astype(np.float32) + _dense(att, w['o']).astype(np.float32)).astype(bf16)
     h = _rms(x, cfg.norm_eps)
     gu = _dense(h, w['gate_up']).astype(np.float32)

@@ -45,6 +45,11 @@ class DecoderConfig:
   rope_theta: float = 500000.0
   norm_eps: float = 1e-5
   dtype: torch.dtype = torch.bfloat16
+  # 'sdpa': the library's fused attention on bf16 q / k / v.  'einsum': scores and the weighted
+  # sum as two einsums issued through qwix_b200.ops, so that a rule which matches them
+  # quantizes the attention core too -- both operands are activations, as in the reference
+  # (boxed_param.py:149-157, 216-224).  Eager steps only: generate() does not graph this form.
+  attention_core: str = 'sdpa'
 
   @staticmethod
   def llama3_8b() -> 'DecoderConfig':
@@ -190,7 +195,14 @@ class Attention(torch.nn.Module):
       # cos / sin are the whole tables here: the kernel indexes them by position, rotates q
       # and k and writes k and v straight into the cache
       q = fused.rope_cache(qkv, self.hq, self.hkv, hd, cos, sin, pos, cache_k, cache_v)
-      if isinstance(pos, torch.Tensor):
+      if self.cfg.attention_core == 'einsum':
+        if isinstance(pos, torch.Tensor):
+          m = mask if mask is not None else _key_mask(cache_k.shape[2], pos, q.dtype)
+          out = _einsum_attention(q, cache_k, cache_v, m)
+        else:
+          out = _einsum_attention(q, cache_k[:, :, :pos + T], cache_v[:, :, :pos + T],
+                                  _causal_mask(T, pos + T, q.device))
+      elif isinstance(pos, torch.Tensor):
         if mask is None:
           mask = _key_mask(cache_k.shape[2], pos, q.dtype)
         out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
@@ -210,18 +222,53 @@ class Attention(torch.nn.Module):
       cache_v.index_copy_(2, pos, v)
       if mask is None:
         mask = _key_mask(cache_k.shape[2], pos, q.dtype)
-      out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
+      if self.cfg.attention_core == 'einsum':
+        out = _einsum_attention(q, cache_k, cache_v, mask)
+      else:
+        out = F.scaled_dot_product_attention(q, cache_k, cache_v, attn_mask=mask, enable_gqa=True)
       out = out.transpose(1, 2).reshape(B, T, self.hq * hd)
       return self.o(out)
     cache_k[:, :, pos:pos + T] = k
     cache_v[:, :, pos:pos + T] = v
-    if pos == 0:
+    if self.cfg.attention_core == 'einsum':
+      out = _einsum_attention(q, cache_k[:, :, :pos + T], cache_v[:, :, :pos + T],
+                              _causal_mask(T, pos + T, q.device))
+    elif pos == 0:
       out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
     else:
       out = F.scaled_dot_product_attention(q, cache_k[:, :, :pos + T], cache_v[:, :, :pos + T],
                                            is_causal=False, enable_gqa=True)
     out = out.transpose(1, 2).reshape(B, T, self.hq * hd)
     return self.o(out)
+
+
+def _einsum_attention(q, k, v, mask):
+  """softmax(q k^T / sqrt(hd) + mask) v with the two contractions as interceptable einsums.
+  q [B, hq, T, hd]; k, v [B, hkv, S, hd]; mask additive, broadcastable to [B, hq, T, S]."""
+  from qwix_b200 import ops
+  rep = q.shape[1] // k.shape[1]
+  if rep > 1:
+    k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+  pad = (-k.shape[2]) % 16
+  if pad:
+    # the tensor-core contraction over the keys wants a multiple of 16: zero keys behind a
+    # -inf mask change neither the probabilities nor any scale
+    if mask is None:
+      mask = torch.zeros((1, 1, 1, k.shape[2]), device=q.device)
+    k, v = F.pad(k, (0, 0, 0, pad)), F.pad(v, (0, 0, 0, pad))
+    mask = F.pad(mask.float(), (0, pad), value=float('-inf'))
+  s = ops.einsum('bnth,bnsh->bnts', q.contiguous(), k.contiguous()).float() * (q.shape[-1] ** -0.5)
+  if mask is not None:
+    s = s + mask.float()
+  p = torch.softmax(s, dim=-1).to(q.dtype)
+  return ops.einsum('bnts,bnsh->bnth', p, v.contiguous())
+
+
+def _causal_mask(T: int, S: int, device) -> torch.Tensor:
+  """Additive mask of a block of T queries that ends at key S - 1."""
+  i = torch.arange(T, device=device).view(T, 1) + (S - T)
+  j = torch.arange(S, device=device).view(1, S)
+  return torch.zeros((T, S), device=device).masked_fill_(j > i, float('-inf'))
 
 
 def _key_mask(length: int, pos: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
@@ -491,6 +538,8 @@ def generate(model, tokens: torch.Tensor, steps: int, prefill_batch: int = 4,
   one eager step that warms every kernel up) and replayed.  Returns the ids [B, steps];
   `timings`, if given, receives the device time of the two phases in ms."""
   dec = model.model if isinstance(model, qwix.model.QuantizedModel) else model
+  if dec.cfg.attention_core == 'einsum':
+    use_graph = False      # the einsum core allocates per (batch, head) call: eager steps
   B, T = tokens.shape
   if dec.cache is None or dec.cache.shape[2] < B or dec.cache.shape[4] < T + steps:
     dec.alloc_cache(B, T + steps)

@@ -68,6 +68,46 @@ def test_tiny_decoder_matches_oracle_and_decode_matches_prefill():
   assert torch.equal(ids, replay)
 
 
+def test_attention_core_as_quantized_einsums():
+  """`attention_core='einsum'`: scores and weighted sum are einsums a rule can match, so under
+  the `.*` w8a8 rule q, k, the probabilities and v are quantized per token
+  (boxed_param.py:149-157, 216-224).  Without a provider the same code is float attention."""
+  import dataclasses
+  cfg = dataclasses.replace(D.DecoderConfig.tiny(), attention_core='einsum')
+  model = D.Decoder(cfg, device='cuda')
+  weights = _full_weights(model)
+  B, T = 2, 32
+  tokens = torch.randint(0, cfg.vocab, (B, T), generator=torch.Generator().manual_seed(1)).cuda()
+  model.alloc_cache(B, T + 8)
+  # float: the einsum core agrees with the library's fused attention
+  sdpa = D.Decoder(dataclasses.replace(cfg, attention_core='sdpa'), device='cuda')
+  sdpa.load_state_dict(model.state_dict())
+  sdpa.alloc_cache(B, T + 8)
+  with torch.no_grad():
+    a = model(tokens, 0, 0, last_only=False).float()
+    b = sdpa(tokens, 0, 0, last_only=False).float()
+  assert (a - b).norm() / b.norm() < 2e-2
+  # quantized: against the oracle decoder with the same switch
+  model.quantize_weights()
+  ptq_model = qwix.quantize_model(model, qwix.PtqProvider(D.w8a8_rules()))
+  with torch.no_grad():
+    got = ptq_model(tokens, 0, 0, last_only=False).cpu().numpy()
+  want = DO.forward(cfg, weights, tokens.cpu().numpy(), quantized_attention=True)
+  rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+  assert rel < 3e-2, rel
+  assert (got.argmax(-1) == want.argmax(-1)).mean() > 0.9
+  plain = DO.forward(cfg, weights, tokens.cpu().numpy())
+  assert np.linalg.norm(want - plain) / np.linalg.norm(plain) > 1e-4     # the switch does change the arithmetic
+  # decode steps run eagerly with this core and stay consistent with the prefill
+  with torch.no_grad():
+    ptq_model(tokens[:, :T - 1], 0, 0)
+    step = ptq_model(tokens[:, T - 1:], T - 1, 0).cpu().numpy()
+  assert np.linalg.norm(step[:, 0] - got[:, -1]) / np.linalg.norm(got[:, -1]) < 5e-2
+  ids = D.generate(ptq_model, tokens, steps=4, prefill_batch=1)
+  assert ids.shape == (B, 4)
+  assert torch.equal(ids[:, 0].cpu(), torch.from_numpy(got[:, -1].argmax(-1)))
+
+
 TP_WORKER = '''
 import os, sys, json
 sys.path.insert(0, os.environ["REPO_ROOT"])
