@@ -54,3 +54,31 @@ class Einsum(torch.nn.Module):
 
   def forward(self, x):
     return ops.einsum(self.subscripts, x, self.kernel)
+
+
+class Conv(torch.nn.Module):
+  """Channels-last convolution, y = conv(x [N, spatial..., C], kernel [window..., C, features])
+  (+ bias): the layout and defaults of flax.linen.Conv ('SAME' padding, unit strides)."""
+
+  def __init__(self, in_features: int, features: int, kernel_size: Sequence[int],
+               strides: Sequence[int] | None = None, padding='SAME', use_bias: bool = True,
+               dtype=torch.float32, device=None, generator=None):
+    super().__init__()
+    self.kernel_size = tuple(kernel_size)
+    self.strides = tuple(strides) if strides is not None else (1,) * len(self.kernel_size)
+    self.padding = padding
+    fan_in = in_features
+    for k in self.kernel_size:
+      fan_in *= k
+    self.kernel = torch.nn.Parameter(
+        lecun_normal_(torch.empty(*self.kernel_size, in_features, features, dtype=dtype, device=device),
+                      fan_in, generator), requires_grad=False)
+    self.bias = torch.nn.Parameter(torch.zeros(features, dtype=dtype, device=device),
+                                   requires_grad=False) if use_bias else None
+
+  def forward(self, x):
+    ns = len(self.kernel_size)
+    layouts = ('NHWC', 'HWIO', 'NHWC') if ns == 2 else ('NWC', 'WIO', 'NWC')
+    y = ops.conv_general_dilated(x, self.kernel, self.strides, self.padding,
+                                 dimension_numbers=layouts)
+    return y if self.bias is None else y + self.bias.to(y.dtype)

@@ -41,3 +41,17 @@ def dot(a, b, precision=None, preferred_element_type=None):
   if provider is None:
     return torch.matmul(_unbox(a), _unbox(b))
   return provider.get_intercept_map()['dot'](a, b, precision, preferred_element_type)
+
+
+def conv_general_dilated(lhs, rhs, window_strides, padding, lhs_dilation=None, rhs_dilation=None,
+                         dimension_numbers=None, feature_group_count=1, batch_group_count=1,
+                         precision=None, preferred_element_type=None):
+  from qwix_b200.core import conv_general as _cg
+  provider = _context.current_provider()
+  if provider is None:
+    return _cg.conv_general_dilated(_unbox(lhs), _unbox(rhs), window_strides, padding, lhs_dilation,
+                                    rhs_dilation, dimension_numbers, feature_group_count,
+                                    batch_group_count, precision, preferred_element_type)
+  return provider.get_intercept_map()['conv_general_dilated'](
+      lhs, rhs, window_strides, padding, lhs_dilation, rhs_dilation, dimension_numbers,
+      feature_group_count, batch_group_count, precision, preferred_element_type)

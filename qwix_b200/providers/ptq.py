@@ -18,6 +18,7 @@ import torch
 from qwix_b200 import _context
 from qwix_b200 import fused
 from qwix_b200 import qconfig
+from qwix_b200.core import conv_general as conv_lib
 from qwix_b200.core import dot as dot_lib
 from qwix_b200.core import dot_general as dot_general_lib
 from qwix_b200.core import einsum as einsum_lib
@@ -71,11 +72,13 @@ class BoxedParamProvider(qconfig.QuantizationProvider):
 
   def __init__(self, rules: Sequence[qconfig.QuantizationRule], *, disable_jit: bool = False,
                _qarray_module=qarray, _dot_general_fn=dot_general_lib.dot_general,
-               _einsum_fn=einsum_lib.einsum):
+               _einsum_fn=einsum_lib.einsum,
+               _conv_general_dilated_fn=conv_lib.conv_general_dilated):
     super().__init__(rules, disable_jit=disable_jit)
     self._qarray_module = _qarray_module
     self._dot_general_fn = _dot_general_fn
     self._einsum_fn = _einsum_fn
+    self._conv_general_dilated_fn = _conv_general_dilated_fn
 
   def _prepare(self, lhs, rhs, rule, op_id, get_how):
     """Shared operand policy of boxed_param.py:137-168 / 204-235."""
@@ -130,6 +133,39 @@ class BoxedParamProvider(qconfig.QuantizationProvider):
     lhs, rhs = self._prepare(lhs, rhs, rule, op_id, get_how)
     return self._einsum_fn(einsum_str, lhs, rhs)
 
+  def conv_general_dilated(self, lhs, rhs, window_strides, padding, lhs_dilation=None,
+                           rhs_dilation=None, dimension_numbers=None, feature_group_count=1,
+                           batch_group_count=1, precision=None, preferred_element_type=None,
+                           out_sharding=None):
+    """boxed_param.py:238-314 -- filter quantized per output channel (offline or at first use),
+    input per image; the rule must give both the same qtype."""
+    rule, op_id = self._get_current_rule_and_op_id('conv_general_dilated')
+    kw = dict(lhs_dilation=lhs_dilation, rhs_dilation=rhs_dilation,
+              dimension_numbers=dimension_numbers, feature_group_count=feature_group_count,
+              batch_group_count=batch_group_count)
+    if rule is None or rule.weight_qtype is None:
+      return conv_lib.conv_general_dilated(_plain(lhs), _plain(rhs), window_strides, padding,
+                                           preferred_element_type=preferred_element_type, **kw)
+    rshape = rhs.array.qvalue.shape if isinstance(rhs, WithAux) else rhs.shape
+    dn = conv_lib.conv_dimension_numbers(tuple(lhs.shape), tuple(rshape), dimension_numbers)
+    kw['dimension_numbers'] = dn
+    if isinstance(rhs, WithAux):
+      rhs = rhs.array
+    else:
+      weight_name = _find_param(_context.current_module(), rhs)
+      rhs_how = conv_lib.get_how_to_quantize(dimension_numbers=dn, for_lhs=False,
+                                             qtype=rule.weight_qtype,
+                                             calibration_method=rule.weight_calibration_method)
+      rhs = create_quantized_param(weight_name, rhs, rhs_how,
+                                   _qarray_module=self._qarray_module).array
+    if rule.act_qtype != rule.weight_qtype:
+      raise ValueError('conv_general_dilated requires same act_qtype and weight_qtype. Got:'
+                       f' {rule.act_qtype=} {rule.weight_qtype=}')
+    lhs_how = conv_lib.get_how_to_quantize(dimension_numbers=dn, for_lhs=True, qtype=rule.act_qtype,
+                                           calibration_method=rule.act_calibration_method)
+    lhs = quantize_act(_plain(lhs), lhs_how, rule, op_id + '_lhs', _qarray_module=self._qarray_module)
+    return self._conv_general_dilated_fn(lhs, rhs, window_strides, padding, **kw)
+
   def dot(self, a, b, precision=None, preferred_element_type=None, out_sharding=None):
     """boxed_param.py:332-348."""
     return dot_lib.dot(a, b, precision=precision,
@@ -147,7 +183,7 @@ class BoxedParamProvider(qconfig.QuantizationProvider):
   def get_intercept_map(self) -> Mapping[str, Callable]:
     """boxed_param.py:402-413 -- op name -> handler, as qwix_b200.ops dispatches."""
     return {'dot_general': self.dot_general, 'einsum': self.einsum, 'dot': self.dot,
-            'asarray': self.asarray}
+            'conv_general_dilated': self.conv_general_dilated, 'asarray': self.asarray}
 
 
 class PtqProvider(BoxedParamProvider):
