@@ -42,18 +42,18 @@ constexpr int kChunkK = 128;        // K per work item: eight K16 tiles, 2 x 16 
 constexpr int kScaleK = 128;        // partial sums are scaled every 128 K
 // Warps per CTA: 32 for up to 8 tokens (few registers per thread, and twice the warps hide the
 // latency of the dependent MMAs of a chunk), 16 beyond.
-__host__ __device__ constexpr int w4_warps(int nt) { return nt == 1 ? 32 : 16; }
+__host__ __device__ constexpr int w4_warps(int nt, int sp) { return nt == 1 && sp < 4 ? 32 : 16; }
 constexpr size_t kSmemCap = 226 * 1024;
 // Work items (1 KB per strip) a warp keeps in flight in its private cp.async ring: loaded HBM
 // latency is a few microseconds, so an SM needs on the order of 100 KB in flight to stream at
 // its share of the bandwidth.  More tokens leave less room beside the activation slice.
 __host__ __device__ constexpr int w4_depth(int nt, int sp) {
-  return (nt == 1 ? 4 : (nt == 2 ? 6 : 4)) / sp;
+  return sp == 4 ? 2 : (nt == 1 ? 4 : (nt == 2 ? 6 : 4)) / sp;
 }
 // a ring stage: one work item's codes (1 KB per strip) and scales (a 64-byte slot per strip)
 __host__ __device__ constexpr int w4_stage_bytes(int sp) { return sp * (1024 + 64); }
 __host__ __device__ constexpr size_t w4_ring_bytes(int nt, int sp) {
-  return (size_t)w4_warps(nt) * w4_depth(nt, sp) * w4_stage_bytes(sp);
+  return (size_t)w4_warps(nt, sp) * w4_depth(nt, sp) * w4_stage_bytes(sp);
 }
 
 struct W4Params {
@@ -243,8 +243,8 @@ __device__ __forceinline__ void w4_finish(const W4Params& p, float (&run)[SP][NT
 // wait_group covers an item.  Where an item lies (strip pair, chunk, addresses) is computed
 // from its linear index with a multiply-high division: no cursor state, no branches.
 template <int NT, int SP, bool F32S>
-__global__ void __launch_bounds__(w4_warps(NT) * 32, 1) gemm_w4_kernel(const W4Params p) {
-  constexpr int kW4Warps = w4_warps(NT);
+__global__ void __launch_bounds__(w4_warps(NT, SP) * 32, 1) gemm_w4_kernel(const W4Params p) {
+  constexpr int kW4Warps = w4_warps(NT, SP);
   constexpr int kW4Threads = kW4Warps * 32;
   constexpr int D = w4_depth(NT, SP);
   constexpr int kStage = w4_stage_bytes(SP);
@@ -297,11 +297,14 @@ __global__ void __launch_bounds__(w4_warps(NT) * 32, 1) gemm_w4_kernel(const W4P
   const uint32_t w_lane = (uint32_t)(slice * cps) * 64u + lane;
   const uint32_t w_pair = (uint32_t)(SP * chunks_per_strip) * 64u;   // from one strip pair to the next
   const uint32_t strip_o = (uint32_t)chunks_per_strip * 64u;
-  const bool sc_active = lane < (F32S ? 16 : 8) * SP;
-  const int sc_strip = F32S ? lane >> 4 : lane >> 3;
-  const int sc_elem = F32S ? (lane & 15) : 2 * (lane & 7);              // first channel of the lane's 4 bytes
+  constexpr int kScCopy = SP == 4 ? 8 : 4;                          // bytes per lane
+  constexpr int kScElems = kScCopy / (F32S ? 4 : 2);                 // channels per lane
+  constexpr int kScLanes = kStrip / kScElems;                        // lanes per strip
+  const bool sc_active = lane < kScLanes * SP;
+  const int sc_strip = lane / kScLanes;
+  const int sc_elem = (lane % kScLanes) * kScElems;                  // first channel of the lane's bytes
   const int sc_src = sc_strip * kStrip + sc_elem;
-  const uint32_t sc_dst = ring_warp + SP * 1024 + sc_strip * 64 + (F32S ? sc_elem * 4 : sc_elem * 2);
+  const uint32_t sc_dst = ring_warp + SP * 1024 + sc_strip * 64 + sc_elem * (F32S ? 4 : 2);
   const int row0 = slice * cps;                                          // first 128-K block of the slice
   auto fetch = [&](int cf, int stage) {
     if (cf < c_end) {
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(w4_warps(NT) * 32, 1) gemm_w4_kernel(const W4P
         const uint32_t row = __umulhi(blk, p.bps_mul) + blk * p.bps_one;
         const uint32_t e = row * (uint32_t)p.N + sp_f * (SP * kStrip) + sc_src;
         const char* src = reinterpret_cast<const char*>(p.scale) + (size_t)e * (F32S ? 4 : 2);
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sc_dst + stage * kStage), "l"(src) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(sc_dst + stage * kStage), "l"(src), "n"(kScCopy) : "memory");
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -506,8 +509,8 @@ bool w4_configure() {
 
 template <int NT, int SP>
 void w4_launch(const W4Params& p, bool f32_scales, dim3 grid, size_t smem, cudaStream_t st) {
-  if (f32_scales) gemm_w4_kernel<NT, SP, true><<<grid, w4_warps(NT) * 32, smem, st>>>(p);
-  else gemm_w4_kernel<NT, SP, false><<<grid, w4_warps(NT) * 32, smem, st>>>(p);
+  if (f32_scales) gemm_w4_kernel<NT, SP, true><<<grid, w4_warps(NT, SP) * 32, smem, st>>>(p);
+  else gemm_w4_kernel<NT, SP, false><<<grid, w4_warps(NT, SP) * 32, smem, st>>>(p);
 }
 
 // x / d for x * d < 2^32 as umulhi(x, mul) + x * one
@@ -576,7 +579,8 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
   static PerDeviceOnce configured;
   if (configured.first()) {
     if (!w4_configure<1, 1>() || !w4_configure<2, 1>() || !w4_configure<4, 1>() ||
-        !w4_configure<1, 2>() || !w4_configure<2, 2>() || !w4_configure<4, 2>())
+        !w4_configure<1, 2>() || !w4_configure<2, 2>() || !w4_configure<4, 2>() ||
+        !w4_configure<1, 4>())
       return QWX_ERR_LAUNCH;
     configured.mark();
   }
@@ -588,7 +592,8 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
   for (int64_t m0 = 0; m0 < M; m0 += kMaxTokensPerLaunch) {
     const int rows = (int)(M - m0 < kMaxTokensPerLaunch ? M - m0 : kMaxTokensPerLaunch);
     const int nt = rows <= 8 ? 1 : (rows <= 16 ? 2 : 4);
-    const int sp = (N / kStrip) % 2 == 0 ? 2 : 1;     // strips per work item
+    // strips per work item: 4 for up to 8 tokens where the strips divide so, else 2, else 1
+    const int sp = nt == 1 && (N / kStrip) % 4 == 0 ? 4 : ((N / kStrip) % 2 == 0 ? 2 : 1);
     const int split = w4_split(nt * 8, K, kSmemCap - w4_ring_bytes(nt, sp));
     if (split <= 0 || split > sms) return QWX_ERR_UNSUPPORTED;
     W4Params p;
@@ -606,7 +611,7 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
     const dim3 grid((unsigned)split, (unsigned)ctas_per_slice);
     {
       const int64_t items = (N / (kStrip * sp)) * (int64_t)(p.ks / kChunkK);
-      const int64_t warps = (int64_t)ctas_per_slice * w4_warps(nt);
+      const int64_t warps = (int64_t)ctas_per_slice * w4_warps(nt, sp);
       p.items_q = (int)(items / warps);
       p.items_r = (int)(items % warps);
     }
@@ -618,7 +623,9 @@ int qwx_gemm_a16w4(const void* a, const void* w_packed, const void* scale, int s
         (K / kChunkK) * (k_tile / kChunkK) >= (1ll << 32))
       return QWX_ERR_UNSUPPORTED;
     const bool f32s = scale_dtype == QWX_F32;
-    if (sp == 2) {
+    if (sp == 4) {
+      w4_launch<1, 4>(p, f32s, grid, smem, st);
+    } else if (sp == 2) {
       if (nt == 1) w4_launch<1, 2>(p, f32s, grid, smem, st);
       else if (nt == 2) w4_launch<2, 2>(p, f32s, grid, smem, st);
       else w4_launch<4, 2>(p, f32s, grid, smem, st);
