@@ -46,7 +46,8 @@ enum qwx_dtype {
   /* e4m3 codes whose scale is a power of two ("mxfp8": one scale per 32 values along the
    * contracted axis; qwix/_src/core/qarray.py:306-325, 566-579).  A quantizer qtype only: the
    * stored codes are QWX_E4M3 bytes for every other entry point. */
-  QWX_MXFP8 = 8
+  QWX_MXFP8 = 8,
+  QWX_MXFP4 = 9      /* e2m1 codes, one per byte (low nibble), power-of-two scale per 32 values */
 };
 
 enum qwx_calibration { QWX_ABSMAX = 0, QWX_MINMAX = 1, QWX_RMS = 2 };
@@ -275,6 +276,22 @@ size_t qwx_mx_scales_packed_bytes(int operand, int64_t rows, int64_t K);
 int qwx_mx_pack_scales(int operand, const void* scale, int scale_dtype, int64_t rows, int64_t K,
                        int k_major, void* out, size_t out_bytes, qwx_stream_t stream);
 int qwx_gemm_mx8(const void* a, const void* b, int b_layout, int64_t M, int64_t N, int64_t K,
+                 const void* sfa_packed, const void* sfb_packed, void* out, int out_dtype,
+                 int32_t* error_flag, qwx_stream_t stream);
+
+/* MXFP4 block-scaled GEMM: the same contraction for two "mxfp4" QArrays (e2m1 codes: sign,
+ * two exponent bits, one significand bit; values 0, 0.5, 1, 1.5, 2, 3, 4, 6), through
+ * tcgen05.mma.kind::mxf4.block_scale.  The kernel takes both operands K-major with two codes
+ * per byte, the even K index in the low nibble: a_packed [M, K / 2], b_packed [N, K / 2].
+ * qwx_mx4_pack_codes makes that from a QArray's codes (one per byte, low nibble): rows x K, or
+ * K x rows with k_major = 1 (a [K, N] weight).  K must be a multiple of 256
+ * (QWX_ERR_UNSUPPORTED otherwise).  Scales as for MXFP8, packed by qwx_mx4_pack_scales. */
+size_t qwx_mx4_scales_packed_bytes(int operand, int64_t rows, int64_t K);
+int qwx_mx4_pack_scales(int operand, const void* scale, int scale_dtype, int64_t rows, int64_t K,
+                        int k_major, void* out, size_t out_bytes, qwx_stream_t stream);
+int qwx_mx4_pack_codes(const void* codes, int64_t rows, int64_t K, int k_major, void* out,
+                       qwx_stream_t stream);
+int qwx_gemm_mx4(const void* a_packed, const void* b_packed, int64_t M, int64_t N, int64_t K,
                  const void* sfa_packed, const void* sfb_packed, void* out, int out_dtype,
                  int32_t* error_flag, qwx_stream_t stream);
 

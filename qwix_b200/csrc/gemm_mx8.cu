@@ -19,6 +19,11 @@
 //   warp 2      owns the tensor-memory allocation
 //   warps 4-7   epilogue: float32 accumulator -> output dtype, while the other accumulator fills
 // Every wait is bounded.
+//
+// The same kernel serves MXFP4 (e2m1 codes packed two per byte, both operands K-major):
+// `tcgen05.mma.kind::mxf4.block_scale.scale_vec::2X`, 64 contracted elements (32 bytes) per
+// MMA with two scale bytes each, so a 128-byte stage holds 256 elements and eight scale blocks
+// per row: two 512-byte scale groups per 128 rows and stage, six tcgen05.cp.
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -46,6 +51,9 @@ constexpr int kXSfaBytes = 512;              // 128 rows x 4 blocks
 constexpr int kXSfbBytes = 1024;             // two 128-row groups
 constexpr int kXStageBytes = 50 * 1024;      // A + B + scales, rounded up to the swizzle alignment
 static_assert(kXABytes + kXBBytes + kXSfaBytes + kXSfbBytes <= kXStageBytes, "stage layout");
+// 4-bit codes: twice the scale blocks per stage; B is [N, K] only (224 rows of 128 bytes)
+constexpr int kX4BBytes = XN * XK;
+static_assert(kXABytes + kX4BBytes + 2 * kXSfaBytes + 2 * kXSfbBytes <= kXStageBytes, "stage layout, 4-bit");
 constexpr int kXAccCols = XN;
 constexpr int kXSfCol = 2 * kXAccCols;       // scale columns behind the two accumulators: 4 (A) + 8 (B)
 constexpr int kXThreads = 256;
@@ -73,7 +81,7 @@ struct MxParams {
   int tiles_m, tiles_n;
 };
 
-template <int BLAYOUT>
+template <int BLAYOUT, bool FP4>
 __global__ void __launch_bounds__(kXThreads, 1)
 gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                 const MxParams p) {
@@ -81,8 +89,13 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   ControlX* ctl = reinterpret_cast<ControlX*>(smem_raw + (tiles - smem_u32(smem_raw)) +
                                               (size_t)kXStages * kXStageBytes);
+  static_assert(!FP4 || BLAYOUT == QWX_B_NK, "4-bit operands are K-major");
+  constexpr int kSfGroups = FP4 ? 2 : 1;                  // 512-byte scale groups per 128 rows and stage
+  constexpr int kSfaStage = kSfGroups * kXSfaBytes;
+  constexpr int kSfbStage = kSfGroups * kXSfbBytes;
+  constexpr int kBStage = FP4 ? kX4BBytes : kXBBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kblocks = (int)(p.K / XK);
+  const int kblocks = (int)(p.K / XK);                    // p.K: contracted bytes
   const int num_tiles = p.tiles_m * p.tiles_n;
   volatile int* abort = &ctl->abort;
 
@@ -116,12 +129,12 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     long issued = 0;
     bool ok = true;
     constexpr uint32_t kStageTx =
-        kXABytes + (BLAYOUT == QWX_B_NK ? XN * XK : 2 * 128 * XK) + kXSfaBytes + kXSfbBytes;
+        kXABytes + (BLAYOUT == QWX_B_NK ? XN * XK : 2 * 128 * XK) + kSfaStage + kSfbStage;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
       const int m0 = tm * XM, n0 = tn * XN;
-      const uint8_t* sfa = p.sfa + (size_t)tm * kblocks * kXSfaBytes;
-      const uint8_t* sfb = p.sfb + (size_t)tn * kblocks * kXSfbBytes;
+      const uint8_t* sfa = p.sfa + (size_t)tm * kblocks * kSfaStage;
+      const uint8_t* sfb = p.sfb + (size_t)tn * kblocks * kSfbStage;
       for (int kb = 0; kb < kblocks && ok; ++kb) {
         if (lane == 0) {
           ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort);
@@ -129,8 +142,8 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const uint32_t bar = smem_u32(&ctl->full[stage]);
             const uint32_t sa = tiles + stage * kXStageBytes;
             const uint32_t sb = sa + kXABytes;
-            const uint32_t ssfa = sb + kXBBytes;
-            const uint32_t ssfb = ssfa + kXSfaBytes;
+            const uint32_t ssfa = sb + kBStage;
+            const uint32_t ssfb = ssfa + kSfaStage;
             mbar_expect_tx(bar, kStageTx);
             tma_load_2d(sa, &tma_a, kb * XK, m0, bar);
             if (BLAYOUT == QWX_B_NK) {
@@ -139,8 +152,8 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
               tma_load_2d(sb, &tma_b, n0, kb * XK, bar);
               tma_load_2d(sb + XK * 128, &tma_b, n0 + 128, kb * XK, bar);
             }
-            bulk_load(ssfa, sfa + (size_t)kb * kXSfaBytes, kXSfaBytes, bar);
-            bulk_load(ssfb, sfb + (size_t)kb * kXSfbBytes, kXSfbBytes, bar);
+            bulk_load(ssfa, sfa + (size_t)kb * kSfaStage, kSfaStage, bar);
+            bulk_load(ssfb, sfb + (size_t)kb * kSfbStage, kSfbStage, bar);
             ++issued;
           }
         }
@@ -166,8 +179,8 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const uint32_t tsfa = tmem_base + kXSfCol;        // 4 columns
-    const uint32_t tsfb = tsfa + 4;                   // 8 columns
+    const uint32_t tsfa = tmem_base + kXSfCol;        // 4 columns per scale group
+    const uint32_t tsfb = tsfa + 4 * kSfGroups;       // 8 columns per scale group
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       if (lane == 0) {
         ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort);
@@ -181,22 +194,33 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             tc_fence_after();
             const uint32_t sa = tiles + stage * kXStageBytes;
             const uint32_t sb = sa + kXABytes;
-            const uint32_t ssfa = sb + kXBBytes;
-            const uint32_t ssfb = ssfa + kXSfaBytes;
+            const uint32_t ssfa = sb + kBStage;
+            const uint32_t ssfb = ssfa + kSfaStage;
             // scale bytes: 32 rows of 16 B per 128 operand rows, four 8-row core matrices 128 B apart
-            tmem_cp_32x128b_warpx4(tsfa, make_smem_desc_plain(ssfa, 16, 128));
-            tmem_cp_32x128b_warpx4(tsfb, make_smem_desc_plain(ssfb, 16, 128));
-            tmem_cp_32x128b_warpx4(tsfb + 4, make_smem_desc_plain(ssfb + 512, 16, 128));
+#pragma unroll
+            for (int sg = 0; sg < kSfGroups; ++sg) {
+              tmem_cp_32x128b_warpx4(tsfa + 4 * sg, make_smem_desc_plain(ssfa + sg * kXSfaBytes, 16, 128));
+              tmem_cp_32x128b_warpx4(tsfb + 8 * sg, make_smem_desc_plain(ssfb + sg * kXSfbBytes, 16, 128));
+              tmem_cp_32x128b_warpx4(tsfb + 8 * sg + 4, make_smem_desc_plain(ssfb + sg * kXSfbBytes + 512, 16, 128));
+            }
 #pragma unroll
             for (int kk = 0; kk < XK / XUMMA_K; ++kk) {
               const uint64_t da = make_smem_desc(sa + kk * XUMMA_K, 16, 1024);
               const uint64_t db = BLAYOUT == QWX_B_NK
                                       ? make_smem_desc(sb + kk * XUMMA_K, 16, 1024)
                                       : make_smem_desc(sb + kk * XUMMA_K * 128, XK * 128, 1024);
-              const uint32_t idesc = make_idesc_mx(0, 0, 0, BLAYOUT == QWX_B_KN ? 1 : 0, XM, XN, kk);
-              // which of the word's four bytes: in the descriptor and in the two top bits of the addresses
-              mma_mx_ss(tmem_base + acc * kXAccCols, da, db, idesc, tsfa | ((uint32_t)kk << 30),
-                        tsfb | ((uint32_t)kk << 30), kb != 0 || kk != 0);
+              if constexpr (FP4) {
+                // two scale bytes per MMA: bytes 0-1 or 2-3 of the word, a word per two MMAs
+                const uint32_t id = (uint32_t)(kk & 1) * 2u, sg = (uint32_t)(kk >> 1);
+                const uint32_t idesc = make_idesc_mx(1, 1, 0, 0, XM, XN, id);
+                mma_mx4_ss(tmem_base + acc * kXAccCols, da, db, idesc, (tsfa + 4 * sg) | (id << 30),
+                           (tsfb + 8 * sg) | (id << 30), kb != 0 || kk != 0);
+              } else {
+                const uint32_t idesc = make_idesc_mx(0, 0, 0, BLAYOUT == QWX_B_KN ? 1 : 0, XM, XN, kk);
+                // which of the word's four bytes: in the descriptor and in the two top bits of the addresses
+                mma_mx_ss(tmem_base + acc * kXAccCols, da, db, idesc, tsfa | ((uint32_t)kk << 30),
+                          tsfb | ((uint32_t)kk << 30), kb != 0 || kk != 0);
+              }
             }
             mma_commit(smem_u32(&ctl->empty[stage]));
             if (kb == kblocks - 1) mma_commit(smem_u32(&ctl->acc_full[acc]));
@@ -281,8 +305,11 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 // per operand tile of `tile_rows` rows and per 128 contracted elements, groups of 128 rows, each
 // 512 bytes: byte (r % 32) * 16 + (r / 32) * 4 + j for row r of the group and 32-wide block j.
 // `k_major`: scale array is [K / 32, rows] (a [K, N] weight) instead of [rows, K / 32].
+// `stage_groups`: 512-byte groups per 128 rows and stage: 1 (four blocks per stage, 8-bit codes)
+// or 2 (eight blocks per stage, 4-bit codes; the stage's groups of one operand tile lie
+// [group][128-row part]).
 __global__ void mx_pack_scales_kernel(const void* __restrict__ scale, int dtype, int64_t rows,
-                                      int64_t blocks, int k_major, int tile_rows,
+                                      int64_t blocks, int k_major, int tile_rows, int stage_groups,
                                       uint8_t* __restrict__ out) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * blocks) return;
@@ -297,9 +324,10 @@ __global__ void mx_pack_scales_kernel(const void* __restrict__ scale, int dtype,
   const int groups = (tile_rows + 127) / 128;
   const int64_t tile = r / tile_rows, rr = r % tile_rows;
   const int64_t g = rr / 128, r128 = rr % 128;
-  const int64_t kb = j / 4, jj = j % 4;
-  const int64_t kblocks = blocks / 4;
-  out[((tile * kblocks + kb) * groups + g) * 512 + (r128 % 32) * 16 + (r128 / 32) * 4 + jj] = e;
+  const int64_t kb = j / (4 * stage_groups), sg = (j / 4) % stage_groups, jj = j % 4;
+  const int64_t kblocks = blocks / (4 * stage_groups);
+  out[(((tile * kblocks + kb) * stage_groups + sg) * groups + g) * 512 + (r128 % 32) * 16 +
+      (r128 / 32) * 4 + jj] = e;
 }
 
 int sm_count_x() {
@@ -312,9 +340,27 @@ int sm_count_x() {
   return n;
 }
 
-template <int BLAYOUT>
+// Unpacked 4-bit codes (one per byte) -> two per byte along K (even index in the low nibble),
+// rows K-major: out[r, k / 2].  `k_major`: the codes are [K, rows] (a [K, N] weight).
+__global__ void mx4_pack_codes_kernel(const uint8_t* __restrict__ codes, int64_t rows, int64_t K,
+                                      int k_major, uint8_t* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // output byte
+  const int64_t kh = K / 2;
+  if (i >= rows * kh) return;
+  if (k_major) {
+    // consecutive threads take consecutive rows: both reads run along the fast axis
+    const int64_t r = i % rows, k2 = i / rows;
+    const uint8_t lo = codes[(2 * k2) * rows + r], hi = codes[(2 * k2 + 1) * rows + r];
+    out[r * kh + k2] = (uint8_t)((lo & 0xf) | (hi << 4));
+  } else {
+    const uchar2 c = reinterpret_cast<const uchar2*>(codes)[i];
+    out[i] = (uint8_t)((c.x & 0xf) | (c.y << 4));
+  }
+}
+
+template <int BLAYOUT, bool FP4>
 int launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const MxParams& p, int grid, cudaStream_t st) {
-  auto kern = gemm_mx8_kernel<BLAYOUT>;
+  auto kern = gemm_mx8_kernel<BLAYOUT, FP4>;
   static PerDeviceOnce configured;
   if (configured.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kXSmemBytes) != cudaSuccess)
@@ -356,7 +402,7 @@ extern "C" int qwx_mx_pack_scales(int operand, const void* scale, int scale_dtyp
   if (cudaMemsetAsync(out, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
   const int64_t blocks = K / 32, n = rows * blocks;
   mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), (uint8_t*)out);
+      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 1, (uint8_t*)out);
   QWX_CHECK_LAUNCH();
   return QWX_OK;
 }
@@ -398,6 +444,81 @@ extern "C" int qwx_gemm_mx8(const void* a, const void* b, int b_layout, int64_t 
   if (sms <= 0) return QWX_ERR_NO_DEVICE;
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);
   cudaStream_t st = (cudaStream_t)stream;
-  return b_layout == QWX_B_NK ? launch_mx<QWX_B_NK>(ta, tb, p, grid, st)
-                              : launch_mx<QWX_B_KN>(ta, tb, p, grid, st);
+  return b_layout == QWX_B_NK ? launch_mx<QWX_B_NK, false>(ta, tb, p, grid, st)
+                              : launch_mx<QWX_B_KN, false>(ta, tb, p, grid, st);
+}
+
+// ---- MXFP4: e2m1 codes, two per byte, 256 contracted elements per stage ----------------------
+
+extern "C" size_t qwx_mx4_scales_packed_bytes(int operand, int64_t rows, int64_t K) {
+  if (rows <= 0 || K <= 0 || K % (2 * XK) || (operand != 0 && operand != 1)) return 0;
+  const int tr = tile_rows_of(operand);
+  const int64_t tiles = (rows + tr - 1) / tr;
+  return (size_t)tiles * (size_t)(K / (2 * XK)) * 2 * (size_t)((tr + 127) / 128) * 512;
+}
+
+extern "C" int qwx_mx4_pack_scales(int operand, const void* scale, int scale_dtype, int64_t rows,
+                                   int64_t K, int k_major, void* out, size_t out_bytes,
+                                   qwx_stream_t stream) {
+  if (!scale || !out) return QWX_ERR_NULL;
+  if (operand != 0 && operand != 1) return QWX_ERR_SHAPE;
+  if (rows <= 0 || K <= 0) return QWX_ERR_SHAPE;
+  if (K % (2 * XK)) return QWX_ERR_UNSUPPORTED;
+  if (scale_dtype != QWX_F32 && scale_dtype != QWX_BF16 && scale_dtype != QWX_F16) return QWX_ERR_DTYPE;
+  const size_t need = qwx_mx4_scales_packed_bytes(operand, rows, K);
+  if (out_bytes < need) return QWX_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return QWX_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(out, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
+  const int64_t blocks = K / 32, n = rows * blocks;
+  mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 2, (uint8_t*)out);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+extern "C" int qwx_mx4_pack_codes(const void* codes, int64_t rows, int64_t K, int k_major, void* out,
+                                  qwx_stream_t stream) {
+  if (!codes || !out) return QWX_ERR_NULL;
+  if (rows <= 0 || K <= 0) return QWX_ERR_SHAPE;
+  if (K % 2) return QWX_ERR_UNSUPPORTED;
+  if (!k_major && (reinterpret_cast<uintptr_t>(codes) & 1)) return QWX_ERR_ALIGN;
+  const int64_t n = rows * (K / 2);
+  mx4_pack_codes_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)codes, rows, K, k_major ? 1 : 0, (uint8_t*)out);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+extern "C" int qwx_gemm_mx4(const void* a_packed, const void* b_packed, int64_t M, int64_t N,
+                            int64_t K, const void* sfa_packed, const void* sfb_packed, void* out,
+                            int out_dtype, int32_t* error_flag, qwx_stream_t stream) {
+  if (!a_packed || !b_packed || !sfa_packed || !sfb_packed || !out) return QWX_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0) return QWX_ERR_SHAPE;
+  if (M > INT32_MAX - XM || N > INT32_MAX - 256 || K > INT32_MAX - 2 * XK) return QWX_ERR_SHAPE;
+  if (K % (2 * XK)) return QWX_ERR_UNSUPPORTED;      // whole stages of eight scale blocks
+  if (out_dtype != QWX_BF16 && out_dtype != QWX_F32 && out_dtype != QWX_F16) return QWX_ERR_DTYPE;
+  if ((reinterpret_cast<uintptr_t>(a_packed) & 15) || (reinterpret_cast<uintptr_t>(b_packed) & 15) ||
+      (reinterpret_cast<uintptr_t>(sfa_packed) & 15) || (reinterpret_cast<uintptr_t>(sfb_packed) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return QWX_ERR_ALIGN;
+  const int64_t kbytes = K / 2;
+  CUtensorMap ta, tb;
+  if (!get_encode_tiled()) return QWX_ERR_NO_DEVICE;
+  if (!encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_packed, (uint64_t)M, (uint64_t)kbytes, XM, XK) ||
+      !encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_packed, (uint64_t)N, (uint64_t)kbytes, XN, XK))
+    return QWX_ERR_LAUNCH;
+  MxParams p;
+  p.M = M; p.N = N; p.K = kbytes;
+  p.sfa = reinterpret_cast<const uint8_t*>(sfa_packed);
+  p.sfb = reinterpret_cast<const uint8_t*>(sfb_packed);
+  p.out = out; p.out_dtype = out_dtype; p.error_flag = error_flag;
+  p.tiles_m = (int)((M + XM - 1) / XM);
+  p.tiles_n = (int)((N + XN - 1) / XN);
+  const int64_t num_tiles = (int64_t)p.tiles_m * p.tiles_n;
+  if (num_tiles > INT32_MAX / 2) return QWX_ERR_SHAPE;
+  const int sms = sm_count_x();
+  if (sms <= 0) return QWX_ERR_NO_DEVICE;
+  const int grid = (int)(num_tiles < sms ? num_tiles : sms);
+  return launch_mx<QWX_B_NK, true>(ta, tb, p, grid, (cudaStream_t)stream);
 }

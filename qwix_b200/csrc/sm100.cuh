@@ -222,6 +222,18 @@ __device__ __forceinline__ void mma_mx_ss(uint32_t d_tmem, uint64_t a_desc, uint
         "r"(sfb_tmem)
       : "memory");
 }
+// e2m1 codes packed two per byte, 64 contracted elements per MMA, two E8M0 scale bytes each
+// (bytes 0-1 or 2-3 of the word: scale id 0 or 2 in the descriptor and the address).
+__device__ __forceinline__ void mma_mx4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+        "r"(sfb_tmem)
+      : "memory");
+}
 // 32 rows x 16 bytes of shared memory into 32 lanes x 4 columns of tensor memory, the same
 // data in all four lane quarters.  Ordered with the MMAs this thread issues before and after.
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
