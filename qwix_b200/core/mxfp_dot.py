@@ -3,8 +3,10 @@
 When both operands are MXFP8 QArrays (e4m3 codes, one power-of-two scale per 32 contracted
 elements) the contraction runs as one block-scaled tensor-core GEMM: `qwx_gemm_mx8` applies
 the scales inside `tcgen05.mma.kind::mxf8f6f4.block_scale` and accumulates in float32, which
-is what `jax.nn.scaled_matmul` computes for the reference.  Anything else returns None and the
-caller falls back to the ordinary paths, as in the reference.
+is what `jax.nn.scaled_matmul` computes for the reference.  Two MXFP4 QArrays (e2m1 codes) take
+`qwx_gemm_mx4` (`kind::mxf4.block_scale`) after their codes are packed two per byte along the
+contracted axis.  Anything else returns None and the caller falls back to the ordinary paths,
+as in the reference.
 """
 
 import math
@@ -52,8 +54,9 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
   scale layouts do not match, or the format has no kernel here (mxfp4 / nvfp4)."""
   if not (_is_mxfp(lhs) and _is_mxfp(rhs)):
     return None
-  if lhs.qtype != 'mxfp8' or rhs.qtype != 'mxfp8':
-    return None          # 16-wide and 4-bit blocks: not built; the caller dequantizes
+  if lhs.qtype != rhs.qtype or lhs.qtype not in ('mxfp8', 'mxfp4'):
+    return None          # 16-wide blocks, mixed formats: not built; the caller dequantizes
+  four_bit = lhs.qtype == 'mxfp4'
   (lca, rca), (lba, rba) = dimension_numbers
   lca, rca, lba, rba = map(list, (lca, rca, lba, rba))
   lval, lscale, ldims = _flatten_to_3d(lhs, lca, lba)
@@ -62,8 +65,8 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
     return None
   B, M, K, Ks = ldims
   N = rdims[1]
-  if Ks * _MX_BLOCK != K or K % 128:
-    return None          # blocks of flattened K must be the 32-wide blocks; whole 128-wide stages
+  if Ks * _MX_BLOCK != K or K % (256 if four_bit else 128):
+    return None          # blocks of flattened K must be the 32-wide blocks; whole 128-byte stages
   _, res_t = qarray.get_accumulator_and_result_type(
       lhs, rhs, preferred_element_type=preferred_element_type)
   if res_t not in _lib.FLOAT_CODES:
@@ -91,6 +94,11 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
   stream = _lib.stream_ptr(dev)
   out = torch.empty((B, M, N), dtype=res_t, device=dev)
   err = _lib.error_flag(dev)
+  if four_bit:
+    _mx4_batches(L, lhs, rhs, a3, sa3, b3, sb3, k_major, layout, B, M, N, K, out, res_t, err, stream)
+    bshape = [lhs.qvalue.shape[i] for i in lba]
+    lfree = [lhs.qvalue.shape[i] for i in range(lhs.qvalue.ndim) if i not in lca and i not in lba]
+    return out.reshape(bshape + lfree + [rhs.qvalue.shape[i] for i in rfree])
   na = L.qwx_mx_scales_packed_bytes(0, M, K)
   nb = L.qwx_mx_scales_packed_bytes(1, N, K)
   for b in range(B):
@@ -116,3 +124,34 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
   lfree = [lhs.qvalue.shape[i] for i in range(lhs.qvalue.ndim) if i not in lca and i not in lba]
   rfree_shape = [rhs.qvalue.shape[i] for i in rfree]
   return out.reshape(bshape + lfree + rfree_shape)
+
+
+def _mx4_batches(L, lhs, rhs, a3, sa3, b3, sb3, k_major, layout, B, M, N, K, out, res_t, err, stream):
+  """The MXFP4 leg: codes packed two per byte along K (the weight's packed codes and scale bytes
+  are kept beside the QArray), then one `qwx_gemm_mx4` per batch element."""
+  dev = a3.device
+  na = L.qwx_mx4_scales_packed_bytes(0, M, K)
+  nb = L.qwx_mx4_scales_packed_bytes(1, N, K)
+  for b in range(B):
+    ap = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    _lib.check(L.qwx_mx4_pack_codes(_lib.ptr(a3[b]), M, K, 0, _lib.ptr(ap), stream), 'mx4_pack_codes')
+    pa = torch.empty(na, dtype=torch.uint8, device=dev)
+    _lib.check(L.qwx_mx4_pack_scales(0, _lib.ptr(sa3[b]), numerics.code_of_float(sa3.dtype), M, K, 0,
+                                     _lib.ptr(pa), na, stream), 'mx4_pack_scales')
+    key = (layout, N, K, rhs.qvalue.data_ptr(), rhs.scale.data_ptr())
+    cached = getattr(rhs, '_mx4_packed', None) if B == 1 else None
+    if cached is not None and cached[0] == key:
+      bp, pb = cached[1], cached[2]
+    else:
+      bp = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+      _lib.check(L.qwx_mx4_pack_codes(_lib.ptr(b3[b]), N, K, k_major, _lib.ptr(bp), stream), 'mx4_pack_codes')
+      pb = torch.empty(nb, dtype=torch.uint8, device=dev)
+      _lib.check(L.qwx_mx4_pack_scales(1, _lib.ptr(sb3[b]), numerics.code_of_float(sb3.dtype), N, K, k_major,
+                                       _lib.ptr(pb), nb, stream), 'mx4_pack_scales')
+      if B == 1:
+        try:
+          object.__setattr__(rhs, '_mx4_packed', (key, bp, pb))
+        except Exception:  # noqa: BLE001 -- a QArray that cannot carry the cache just repacks
+          pass
+    _lib.check(L.qwx_gemm_mx4(_lib.ptr(ap), _lib.ptr(bp), M, N, K, _lib.ptr(pa), _lib.ptr(pb),
+                              _lib.ptr(out[b]), _lib.FLOAT_CODES[res_t], _lib.ptr(err), stream), 'gemm_mx4')

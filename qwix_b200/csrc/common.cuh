@@ -4,8 +4,10 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <type_traits>
 
 #include "../../include/qwix_b200.h"
 
@@ -120,6 +122,9 @@ struct S4 { static constexpr int kLo = -8, kHi = 7; static constexpr bool kFloat
 struct E4M3 { static constexpr bool kFloat = true; };
 // e4m3 codes under a power-of-two scale per 32 values (OCP microscaling, "mxfp8")
 struct MX8 { static constexpr bool kFloat = true; };
+// e2m1 codes (sign, two exponent bits, one significand bit: 0, 0.5, 1, 1.5, 2, 3, 4, 6), one
+// per byte in the low nibble, under a power-of-two scale per 32 values ("mxfp4")
+struct MX4 { static constexpr bool kFloat = true; };
 
 // Symmetric bound B (codes cover [-B, B]) and asymmetric (qmin, qmax).
 template <typename Q> __host__ __device__ constexpr float sym_bound();
@@ -127,12 +132,19 @@ template <> __host__ __device__ constexpr float sym_bound<S8>() { return 127.5f;
 template <> __host__ __device__ constexpr float sym_bound<S4>() { return 7.5f; }
 template <> __host__ __device__ constexpr float sym_bound<E4M3>() { return 448.0f; }
 template <> __host__ __device__ constexpr float sym_bound<MX8>() { return 448.0f; }
+template <> __host__ __device__ constexpr float sym_bound<MX4>() { return 6.0f; }
 
 // Scaled float -> code, returned as the byte that is stored for 8-bit codes or the
 // sign-extended value for int4.  Integers: round-half-even, saturate, NaN -> 0 (the
 // float->int convert of XLA); e4m3: clip to +/-448 then round-to-nearest-even, NaN stays.
 template <typename Q> __device__ __forceinline__ int to_code(float y) {
-  if constexpr (Q::kFloat) {
+  if constexpr (std::is_same<Q, MX4>::value) {
+    // e2m1 has neither NaN nor infinity: clip to +/-6, round to nearest even; a NaN becomes a
+    // zero of the opposite sign (what ml_dtypes' cast does; the reference pins no value)
+    if (y != y) return (__float_as_uint(y) >> 31) ? 0x0 : 0x8;
+    y = fminf(fmaxf(y, -6.0f), 6.0f);
+    return (int)__nv_cvt_float_to_fp4(y, __NV_E2M1, cudaRoundNearest);
+  } else if constexpr (Q::kFloat) {
     if (y != y) return 0x7f;
     y = fminf(fmaxf(y, -448.0f), 448.0f);
     return (int)__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
@@ -149,6 +161,13 @@ template <typename Q> __device__ __forceinline__ int to_code(float y) {
 __device__ __forceinline__ float e4m3_to_float(uint8_t b) {
   __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
   return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+__device__ __forceinline__ float e2m1_to_float(uint8_t b) {
+  const uint32_t m = b & 7u;
+  // 0, 0.5, then (1 + significand / 2) * 2^(exponent - 1)
+  const float mag = m < 2 ? 0.5f * (float)m : __uint_as_float(((126u + (m >> 1)) << 23) | ((m & 1u) << 22));
+  return (b & 8u) ? -mag : mag;
 }
 
 __device__ __forceinline__ float warp_max(float v) {

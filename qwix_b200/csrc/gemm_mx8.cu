@@ -358,6 +358,20 @@ __global__ void mx4_pack_codes_kernel(const uint8_t* __restrict__ codes, int64_t
   }
 }
 
+// The row-major case sixteen codes at a time (an activation: packed on every call).
+__global__ void mx4_pack_codes_vec_kernel(const uint4* __restrict__ codes, int64_t nvec,
+                                          uint2* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const uint4 c = codes[i];
+  // bytes b0 b1 b2 b3 of a word -> (b0 | b1 << 4) and (b2 | b3 << 4) in its low two bytes
+  auto squeeze = [](uint32_t w) {
+    const uint32_t t = (w & 0x000f000fu) | ((w >> 4) & 0x00f000f0u);   // bytes 0 and 2 hold the pairs
+    return (t & 0xffu) | ((t >> 8) & 0xff00u);
+  };
+  out[i] = make_uint2(squeeze(c.x) | (squeeze(c.y) << 16), squeeze(c.z) | (squeeze(c.w) << 16));
+}
+
 template <int BLAYOUT, bool FP4>
 int launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const MxParams& p, int grid, cudaStream_t st) {
   auto kern = gemm_mx8_kernel<BLAYOUT, FP4>;
@@ -484,6 +498,14 @@ extern "C" int qwx_mx4_pack_codes(const void* codes, int64_t rows, int64_t K, in
   if (K % 2) return QWX_ERR_UNSUPPORTED;
   if (!k_major && (reinterpret_cast<uintptr_t>(codes) & 1)) return QWX_ERR_ALIGN;
   const int64_t n = rows * (K / 2);
+  if (!k_major && (rows * K) % 16 == 0 && !(reinterpret_cast<uintptr_t>(codes) & 15) &&
+      !(reinterpret_cast<uintptr_t>(out) & 7)) {
+    const int64_t nvec = rows * K / 16;
+    mx4_pack_codes_vec_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (const uint4*)codes, nvec, (uint2*)out);
+    QWX_CHECK_LAUNCH();
+    return QWX_OK;
+  }
   mx4_pack_codes_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       (const uint8_t*)codes, rows, K, k_major ? 1 : 0, (uint8_t*)out);
   QWX_CHECK_LAUNCH();

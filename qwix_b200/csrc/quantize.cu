@@ -26,13 +26,14 @@ struct CalibArgs {
   float arg;       // already narrowed to float
 };
 
-enum class Out { kS8, kS4U, kS4P, kE4M3, kMX8 };
+enum class Out { kS8, kS4U, kS4P, kE4M3, kMX8, kMX4 };
 template <Out O> struct OutTraits;
 template <> struct OutTraits<Out::kS8> { using Q = S8; };
 template <> struct OutTraits<Out::kS4U> { using Q = S4; };
 template <> struct OutTraits<Out::kS4P> { using Q = S4; };
 template <> struct OutTraits<Out::kE4M3> { using Q = E4M3; };
 template <> struct OutTraits<Out::kMX8> { using Q = MX8; };
+template <> struct OutTraits<Out::kMX4> { using Q = MX4; };
 
 // ---- scalar recipes -------------------------------------------------------------------
 
@@ -52,10 +53,12 @@ __device__ __forceinline__ float guard_scale(float s) {
 template <typename T, typename Q>
 __device__ __forceinline__ float symmetric_scale(float absmax) {
   float s = guard_scale<T>(round_to<T>(__fdiv_rn(absmax, sym_bound<Q>())));
-  if constexpr (std::is_same<Q, MX8>::value) {
-    // Microscaling: the scale becomes a power of two.  scale * 60/31 in the input dtype
-    // (outlier-aware bias), rounded to bfloat16, significand dropped (qarray.py:566-579).
-    const float biased = round_to<T>(__fmul_rn(s, round_to<T>(60.0f / 31.0f)));
+  if constexpr (std::is_same<Q, MX8>::value || std::is_same<Q, MX4>::value) {
+    // Microscaling: the scale becomes a power of two.  scale * 60/31 (e4m3) or 12/7 (e2m1) in
+    // the input dtype (outlier-aware bias), rounded to bfloat16, significand dropped
+    // (qarray.py:566-579).
+    constexpr float c = std::is_same<Q, MX4>::value ? 12.0f / 7.0f : 60.0f / 31.0f;
+    const float biased = round_to<T>(__fmul_rn(s, round_to<T>(c)));
     s = __uint_as_float(__float_as_uint(round_to<BF16>(biased)) & 0x7F800000u);
   }
   return s;
@@ -327,7 +330,7 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
 // absmax over the block with two shuffles, the scale by the outlier-aware rule, and -- the
 // scale being a power of two -- x / scale as an exact multiplication by its reciprocal.  Two
 // values per fp8 conversion instruction.
-template <typename T>
+template <typename T, typename Q = MX8>
 __global__ void __launch_bounds__(kThreads)
 quantize_mx8_blocks_kernel(const void* __restrict__ x, int64_t nvec, void* __restrict__ q,
                            void* __restrict__ scale) {
@@ -348,9 +351,18 @@ quantize_mx8_blocks_kernel(const void* __restrict__ x, int64_t nvec, void* __res
   bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 1));
   bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 2));
   if (!live) return;
-  const float s = symmetric_scale<T, MX8>(__uint_as_float(bits));
+  const float s = symmetric_scale<T, Q>(__uint_as_float(bits));
   if ((threadIdx.x & 3) == 0) store1<T>(scale, i >> 2, s);
   const float inv = __fdiv_rn(1.0f, s);       // exact: s is a power of two (or NaN, which propagates)
+  if constexpr (std::is_same<Q, MX4>::value) {
+    // e2m1 codes, one per byte
+    uint32_t w4[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w4[j >> 2] |= (uint32_t)to_code<MX4>(round_to<T>(__fmul_rn(v[j], inv))) << (8 * (j & 3));
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(q) + i * 8) = make_uint2(w4[0], w4[1]);
+    return;
+  }
   uint32_t w[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -714,7 +726,8 @@ dequantize_kernel(const void* __restrict__ q, View vw, const void* __restrict__ 
       else for (int j = 0; j < nvalid; ++j) b[j] = reinterpret_cast<const uint8_t*>(q)[off + j];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        code[j] = (O == Out::kE4M3 || O == Out::kMX8) ? e4m3_to_float(b[j]) : (float)(int8_t)b[j];
+        code[j] = (O == Out::kE4M3 || O == Out::kMX8) ? e4m3_to_float(b[j])
+                  : (O == Out::kMX4 ? e2m1_to_float(b[j]) : (float)(int8_t)b[j]);
     }
     // scale group of each of the eight columns: one division, then a running remainder
     int64_t g = gbase + col / vw.tc;
@@ -790,6 +803,7 @@ int dispatch_out(int qtype, Fn&& fn) {
     case QWX_S4: return fn(std::integral_constant<Out, Out::kS4P>{});
     case QWX_E4M3: return fn(std::integral_constant<Out, Out::kE4M3>{});
     case QWX_MXFP8: return fn(std::integral_constant<Out, Out::kMX8>{});
+    case QWX_MXFP4: return fn(std::integral_constant<Out, Out::kMX4>{});
     default: return (int)QWX_ERR_DTYPE;
   }
 }
@@ -803,7 +817,7 @@ bool row_segment_view(const void* x, const void* q, int64_t tp, int64_t tr, int6
 int check_method(int method, int has_arg, int qtype) {
   if (method != QWX_ABSMAX && method != QWX_MINMAX && method != QWX_RMS) return QWX_ERR_UNSUPPORTED;
   if (method == QWX_RMS && !has_arg) return QWX_ERR_SHAPE;
-  if (method == QWX_MINMAX && (qtype == QWX_E4M3 || qtype == QWX_MXFP8)) return QWX_ERR_DTYPE;  // numerics.py:64-92
+  if (method == QWX_MINMAX && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4)) return QWX_ERR_DTYPE;  // numerics.py:64-92
   return QWX_OK;
 }
 
@@ -879,7 +893,7 @@ int qwx_compute_scale_zero_point(const void* calib_a, const void* calib_b, int d
                                  int qtype, void* scale, void* zero_point, qwx_stream_t stream) {
   if (!calib_a || !scale) return QWX_ERR_NULL;
   if (calib_b && !zero_point) return QWX_ERR_NULL;
-  if (calib_b && (qtype == QWX_E4M3 || qtype == QWX_MXFP8)) return QWX_ERR_DTYPE;
+  if (calib_b && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4)) return QWX_ERR_DTYPE;
   if (n <= 0) return QWX_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned blocks = (unsigned)((n + 255) / 256);
@@ -898,6 +912,9 @@ int qwx_compute_scale_zero_point(const void* calib_a, const void* calib_b, int d
       case QWX_MXFP8:
         scale_zero_point_kernel<T, MX8><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
         break;
+      case QWX_MXFP4:
+        scale_zero_point_kernel<T, MX4><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
+        break;
       default: return (int)QWX_ERR_DTYPE;
     }
     QWX_CHECK_LAUNCH();
@@ -910,7 +927,7 @@ int qwx_quantize_with_scale(const void* x, int x_dtype, int64_t P, int64_t R, in
                             const void* zero_point, int qtype, int rounding, void* q,
                             qwx_stream_t stream) {
   if (!x || !scale || !q) return QWX_ERR_NULL;
-  if (zero_point && (qtype == QWX_E4M3 || qtype == QWX_MXFP8)) return QWX_ERR_DTYPE;
+  if (zero_point && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4)) return QWX_ERR_DTYPE;
   View vw;
   int rc = make_view(P, R, C, tp, tr, tc, &vw);
   if (rc) return rc;
@@ -959,6 +976,20 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
                : launch_dependent(quantize_rows_bf16_s8_kernel<4>, dim3(grid), dim3(kThreads), ring_bytes,
                                   st, (const uint4*)x, segments, (int)(tc / 8), (uint2*)q,
                                   (__nv_bfloat16*)scale);
+      if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)QWX_ERR_LAUNCH;
+      }
+      return (int)QWX_OK;
+    }
+    if (qtype == QWX_MXFP4 && tc == 32 && method == QWX_ABSMAX && !has_arg &&
+        (x_dtype == QWX_BF16 || x_dtype == QWX_F32)) {
+      const int64_t nvec = segments * 4;
+      const unsigned blocks = (unsigned)((nvec + kThreads - 1) / kThreads);
+      const cudaError_t e =
+          x_dtype == QWX_BF16
+              ? launch_dependent(quantize_mx8_blocks_kernel<BF16, MX4>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale)
+              : launch_dependent(quantize_mx8_blocks_kernel<F32, MX4>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale);
       if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return (int)QWX_ERR_LAUNCH;
