@@ -47,7 +47,8 @@ enum qwx_dtype {
    * contracted axis; qwix/_src/core/qarray.py:306-325, 566-579).  A quantizer qtype only: the
    * stored codes are QWX_E4M3 bytes for every other entry point. */
   QWX_MXFP8 = 8,
-  QWX_MXFP4 = 9      /* e2m1 codes, one per byte (low nibble), power-of-two scale per 32 values */
+  QWX_MXFP4 = 9,     /* e2m1 codes, one per byte (low nibble), power-of-two scale per 32 values */
+  QWX_NVFP4 = 10     /* e2m1 codes, one per byte (low nibble), e4m3-valued scale per 16 values */
 };
 
 enum qwx_calibration { QWX_ABSMAX = 0, QWX_MINMAX = 1, QWX_RMS = 2 };
@@ -294,6 +295,18 @@ int qwx_mx4_pack_codes(const void* codes, int64_t rows, int64_t K, int k_major, 
 int qwx_gemm_mx4(const void* a_packed, const void* b_packed, int64_t M, int64_t N, int64_t K,
                  const void* sfa_packed, const void* sfb_packed, void* out, int out_dtype,
                  int32_t* error_flag, qwx_stream_t stream);
+
+/* NVFP4 block-scaled GEMM: two "nvfp4" QArrays (e2m1 codes, one scale per 16 contracted
+ * elements whose value is an e4m3 number: qarray.py:580-581), through
+ * tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X.  Codes packed as for MXFP4
+ * (qwx_mx4_pack_codes); the scales (scale [rows, K / 16], or [K / 16, rows] with k_major = 1)
+ * are laid out as e4m3 bytes by qwx_nvfp4_pack_scales.  K a multiple of 256. */
+size_t qwx_nvfp4_scales_packed_bytes(int operand, int64_t rows, int64_t K);
+int qwx_nvfp4_pack_scales(int operand, const void* scale, int scale_dtype, int64_t rows, int64_t K,
+                          int k_major, void* out, size_t out_bytes, qwx_stream_t stream);
+int qwx_gemm_nvfp4(const void* a_packed, const void* b_packed, int64_t M, int64_t N, int64_t K,
+                   const void* sfa_packed, const void* sfb_packed, void* out, int out_dtype,
+                   int32_t* error_flag, qwx_stream_t stream);
 
 /* Element-wise stages of a Llama-style decoder layer fused with the per-token int8
  * quantization of the next projection's activation.  The quantization half is

@@ -14,7 +14,7 @@ _lock = threading.Lock()
 _lib = None
 
 # enum qwx_dtype
-F32, BF16, F16, S8, S4, E4M3, S32, S4U, MXFP8, MXFP4 = range(10)
+F32, BF16, F16, S8, S4, E4M3, S32, S4U, MXFP8, MXFP4, NVFP4 = range(11)
 # enum qwx_calibration
 ABSMAX, MINMAX, RMS = range(3)
 # enum qwx_rounding
@@ -75,6 +75,9 @@ _SIGNATURES = {
     'qwx_mx4_pack_scales': (_int, [_int, _vp, _int, _i64, _i64, _int, _vp, _sz, _vp]),
     'qwx_mx4_pack_codes': (_int, [_vp, _i64, _i64, _int, _vp, _vp]),
     'qwx_gemm_mx4': (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _int, _vp, _vp]),
+    'qwx_nvfp4_scales_packed_bytes': (_sz, [_int, _i64, _i64]),
+    'qwx_nvfp4_pack_scales': (_int, [_int, _vp, _int, _i64, _i64, _int, _vp, _sz, _vp]),
+    'qwx_gemm_nvfp4': (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _int, _vp, _vp]),
     'qwx_add_rmsnorm_quantize': (_int, [_vp, _vp, _vp, _dbl, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     'qwx_add_rmsnorm_quantize_peer': (_int, [_vp, _vp, _vp, _int, _int, _vp, _int, _vp, _dbl, _i64, _i64,
                                              _vp, _vp, _vp, _vp, _vp, _i64, _vp]),

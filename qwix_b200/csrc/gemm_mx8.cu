@@ -81,7 +81,9 @@ struct MxParams {
   int tiles_m, tiles_n;
 };
 
-template <int BLAYOUT, bool FP4>
+// FMT: 0 = e4m3 codes, E8M0 scale per 32 (MXFP8); 1 = e2m1 codes, E8M0 scale per 32 (MXFP4);
+// 2 = e2m1 codes, e4m3 scale per 16 (NVFP4)
+template <int BLAYOUT, int FMT>
 __global__ void __launch_bounds__(kXThreads, 1)
 gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                 const MxParams p) {
@@ -89,8 +91,12 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   ControlX* ctl = reinterpret_cast<ControlX*>(smem_raw + (tiles - smem_u32(smem_raw)) +
                                               (size_t)kXStages * kXStageBytes);
+  constexpr bool FP4 = FMT != 0;
   static_assert(!FP4 || BLAYOUT == QWX_B_NK, "4-bit operands are K-major");
-  constexpr int kSfGroups = FP4 ? 2 : 1;                  // 512-byte scale groups per 128 rows and stage
+  constexpr int kSfGroups = FMT == 2 ? 4 : (FMT == 1 ? 2 : 1);   // 512-byte scale groups per 128 rows and stage
+  static_assert(kXABytes + (FP4 ? kX4BBytes : kXBBytes) + kSfGroups * (kXSfaBytes + kXSfbBytes) <= kXStageBytes,
+                "stage layout");
+  static_assert(kXSfCol + 12 * kSfGroups <= 512, "scale columns in tensor memory");
   constexpr int kSfaStage = kSfGroups * kXSfaBytes;
   constexpr int kSfbStage = kSfGroups * kXSfbBytes;
   constexpr int kBStage = FP4 ? kX4BBytes : kXBBytes;
@@ -209,7 +215,12 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
               const uint64_t db = BLAYOUT == QWX_B_NK
                                       ? make_smem_desc(sb + kk * XUMMA_K, 16, 1024)
                                       : make_smem_desc(sb + kk * XUMMA_K * 128, XK * 128, 1024);
-              if constexpr (FP4) {
+              if constexpr (FMT == 2) {
+                // four scale bytes per MMA: a word each
+                const uint32_t idesc = make_idesc_mx(1, 1, 0, 0, XM, XN, 0, /*e8m0_scales=*/0);
+                mma_nvf4_ss(tmem_base + acc * kXAccCols, da, db, idesc, tsfa + 4 * kk, tsfb + 8 * kk,
+                            kb != 0 || kk != 0);
+              } else if constexpr (FMT == 1) {
                 // two scale bytes per MMA: bytes 0-1 or 2-3 of the word, a word per two MMAs
                 const uint32_t id = (uint32_t)(kk & 1) * 2u, sg = (uint32_t)(kk >> 1);
                 const uint32_t idesc = make_idesc_mx(1, 1, 0, 0, XM, XN, id);
@@ -310,7 +321,7 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 // [group][128-row part]).
 __global__ void mx_pack_scales_kernel(const void* __restrict__ scale, int dtype, int64_t rows,
                                       int64_t blocks, int k_major, int tile_rows, int stage_groups,
-                                      uint8_t* __restrict__ out) {
+                                      int e4m3_bytes, uint8_t* __restrict__ out) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * blocks) return;
   // consecutive threads read consecutive elements of the scale array
@@ -320,7 +331,9 @@ __global__ void mx_pack_scales_kernel(const void* __restrict__ scale, int dtype,
   if (dtype == QWX_F32) s = reinterpret_cast<const float*>(scale)[i];
   else if (dtype == QWX_BF16) s = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(scale)[i]);
   else s = __half2float(reinterpret_cast<const __half*>(scale)[i]);
-  const uint8_t e = (uint8_t)((__float_as_uint(s) >> 23) & 0xffu);
+  // the biased exponent of a power of two, or the e4m3 byte of a scale that is an e4m3 value
+  const uint8_t e = e4m3_bytes ? (uint8_t)__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3)
+                               : (uint8_t)((__float_as_uint(s) >> 23) & 0xffu);
   const int groups = (tile_rows + 127) / 128;
   const int64_t tile = r / tile_rows, rr = r % tile_rows;
   const int64_t g = rr / 128, r128 = rr % 128;
@@ -372,9 +385,9 @@ __global__ void mx4_pack_codes_vec_kernel(const uint4* __restrict__ codes, int64
   out[i] = make_uint2(squeeze(c.x) | (squeeze(c.y) << 16), squeeze(c.z) | (squeeze(c.w) << 16));
 }
 
-template <int BLAYOUT, bool FP4>
+template <int BLAYOUT, int FMT>
 int launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const MxParams& p, int grid, cudaStream_t st) {
-  auto kern = gemm_mx8_kernel<BLAYOUT, FP4>;
+  auto kern = gemm_mx8_kernel<BLAYOUT, FMT>;
   static PerDeviceOnce configured;
   if (configured.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kXSmemBytes) != cudaSuccess)
@@ -416,7 +429,7 @@ extern "C" int qwx_mx_pack_scales(int operand, const void* scale, int scale_dtyp
   if (cudaMemsetAsync(out, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
   const int64_t blocks = K / 32, n = rows * blocks;
   mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 1, (uint8_t*)out);
+      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 1, 0, (uint8_t*)out);
   QWX_CHECK_LAUNCH();
   return QWX_OK;
 }
@@ -458,8 +471,8 @@ extern "C" int qwx_gemm_mx8(const void* a, const void* b, int b_layout, int64_t 
   if (sms <= 0) return QWX_ERR_NO_DEVICE;
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);
   cudaStream_t st = (cudaStream_t)stream;
-  return b_layout == QWX_B_NK ? launch_mx<QWX_B_NK, false>(ta, tb, p, grid, st)
-                              : launch_mx<QWX_B_KN, false>(ta, tb, p, grid, st);
+  return b_layout == QWX_B_NK ? launch_mx<QWX_B_NK, 0>(ta, tb, p, grid, st)
+                              : launch_mx<QWX_B_KN, 0>(ta, tb, p, grid, st);
 }
 
 // ---- MXFP4: e2m1 codes, two per byte, 256 contracted elements per stage ----------------------
@@ -486,7 +499,7 @@ extern "C" int qwx_mx4_pack_scales(int operand, const void* scale, int scale_dty
   if (cudaMemsetAsync(out, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
   const int64_t blocks = K / 32, n = rows * blocks;
   mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 2, (uint8_t*)out);
+      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 2, 0, (uint8_t*)out);
   QWX_CHECK_LAUNCH();
   return QWX_OK;
 }
@@ -512,13 +525,15 @@ extern "C" int qwx_mx4_pack_codes(const void* codes, int64_t rows, int64_t K, in
   return QWX_OK;
 }
 
-extern "C" int qwx_gemm_mx4(const void* a_packed, const void* b_packed, int64_t M, int64_t N,
-                            int64_t K, const void* sfa_packed, const void* sfb_packed, void* out,
-                            int out_dtype, int32_t* error_flag, qwx_stream_t stream) {
+namespace {
+template <int FMT>
+int gemm_fp4(const void* a_packed, const void* b_packed, int64_t M, int64_t N, int64_t K,
+             const void* sfa_packed, const void* sfb_packed, void* out, int out_dtype,
+             int32_t* error_flag, qwx_stream_t stream) {
   if (!a_packed || !b_packed || !sfa_packed || !sfb_packed || !out) return QWX_ERR_NULL;
   if (M <= 0 || N <= 0 || K <= 0) return QWX_ERR_SHAPE;
   if (M > INT32_MAX - XM || N > INT32_MAX - 256 || K > INT32_MAX - 2 * XK) return QWX_ERR_SHAPE;
-  if (K % (2 * XK)) return QWX_ERR_UNSUPPORTED;      // whole stages of eight scale blocks
+  if (K % (2 * XK)) return QWX_ERR_UNSUPPORTED;      // whole 128-byte stages
   if (out_dtype != QWX_BF16 && out_dtype != QWX_F32 && out_dtype != QWX_F16) return QWX_ERR_DTYPE;
   if ((reinterpret_cast<uintptr_t>(a_packed) & 15) || (reinterpret_cast<uintptr_t>(b_packed) & 15) ||
       (reinterpret_cast<uintptr_t>(sfa_packed) & 15) || (reinterpret_cast<uintptr_t>(sfb_packed) & 15) ||
@@ -542,5 +557,47 @@ extern "C" int qwx_gemm_mx4(const void* a_packed, const void* b_packed, int64_t 
   const int sms = sm_count_x();
   if (sms <= 0) return QWX_ERR_NO_DEVICE;
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);
-  return launch_mx<QWX_B_NK, true>(ta, tb, p, grid, (cudaStream_t)stream);
+  return launch_mx<QWX_B_NK, FMT>(ta, tb, p, grid, (cudaStream_t)stream);
+}
+}  // namespace
+
+extern "C" int qwx_gemm_mx4(const void* a_packed, const void* b_packed, int64_t M, int64_t N,
+                            int64_t K, const void* sfa_packed, const void* sfb_packed, void* out,
+                            int out_dtype, int32_t* error_flag, qwx_stream_t stream) {
+  return gemm_fp4<1>(a_packed, b_packed, M, N, K, sfa_packed, sfb_packed, out, out_dtype, error_flag, stream);
+}
+
+// ---- NVFP4: e2m1 codes, an e4m3 scale per 16 contracted elements ------------------------------
+
+extern "C" size_t qwx_nvfp4_scales_packed_bytes(int operand, int64_t rows, int64_t K) {
+  if (rows <= 0 || K <= 0 || K % (2 * XK) || (operand != 0 && operand != 1)) return 0;
+  const int tr = tile_rows_of(operand);
+  const int64_t tiles = (rows + tr - 1) / tr;
+  return (size_t)tiles * (size_t)(K / (2 * XK)) * 4 * (size_t)((tr + 127) / 128) * 512;
+}
+
+extern "C" int qwx_nvfp4_pack_scales(int operand, const void* scale, int scale_dtype, int64_t rows,
+                                     int64_t K, int k_major, void* out, size_t out_bytes,
+                                     qwx_stream_t stream) {
+  if (!scale || !out) return QWX_ERR_NULL;
+  if (operand != 0 && operand != 1) return QWX_ERR_SHAPE;
+  if (rows <= 0 || K <= 0) return QWX_ERR_SHAPE;
+  if (K % (2 * XK)) return QWX_ERR_UNSUPPORTED;
+  if (scale_dtype != QWX_F32 && scale_dtype != QWX_BF16 && scale_dtype != QWX_F16) return QWX_ERR_DTYPE;
+  const size_t need = qwx_nvfp4_scales_packed_bytes(operand, rows, K);
+  if (out_bytes < need) return QWX_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return QWX_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(out, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;   // e4m3 zero past the operand
+  const int64_t blocks = K / 16, n = rows * blocks;
+  mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 4, 1, (uint8_t*)out);
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
+extern "C" int qwx_gemm_nvfp4(const void* a_packed, const void* b_packed, int64_t M, int64_t N,
+                              int64_t K, const void* sfa_packed, const void* sfb_packed, void* out,
+                              int out_dtype, int32_t* error_flag, qwx_stream_t stream) {
+  return gemm_fp4<2>(a_packed, b_packed, M, N, K, sfa_packed, sfb_packed, out, out_dtype, error_flag, stream);
 }

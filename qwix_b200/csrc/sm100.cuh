@@ -206,11 +206,14 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
 // Scales sit in tensor memory: for row r of a 128-row operand tile, lane r % 32 (the same in
 // every lane quarter), column r / 32, and the four bytes of that 32-bit word belong to four
 // consecutive 32-wide K blocks.
+// `e8m0_scales`: bit 23, the scale type (1: unsigned power-of-two bytes, 0: unsigned e4m3).
 __host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_fmt, uint32_t b_fmt,
                                                      uint32_t a_mn_major, uint32_t b_mn_major,
-                                                     uint32_t m, uint32_t n, uint32_t sf_byte) {
+                                                     uint32_t m, uint32_t n, uint32_t sf_byte,
+                                                     uint32_t e8m0_scales = 1) {
   return (sf_byte << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) |
-         (b_mn_major << 16) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_byte << 29);
+         (b_mn_major << 16) | ((n >> 3) << 17) | (e8m0_scales << 23) | ((m >> 4) << 24) |
+         (sf_byte << 29);
 }
 __device__ __forceinline__ void mma_mx_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                           uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
@@ -230,6 +233,18 @@ __device__ __forceinline__ void mma_mx4_ss(uint32_t d_tmem, uint64_t a_desc, uin
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+        "r"(sfb_tmem)
+      : "memory");
+}
+// e2m1 codes, 64 contracted elements per MMA, four e4m3 scale bytes each (one per 16 elements:
+// the whole word, scale id 0).
+__device__ __forceinline__ void mma_nvf4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
         "r"(sfb_tmem)
       : "memory");
