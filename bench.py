@@ -600,49 +600,57 @@ def mxfp8_record(args, device, lib_peaks: dict):
                     'how': 'torch._scaled_mm with float8_e8m0fnu block scales, one operand set'})
   except Exception as e:  # noqa: BLE001 -- context only
     library['unavailable'] = repr(e)[:200]
-  # ---- the same product with e2m1 codes ("mxfp4"): public dot_general on two mxfp4 QArrays ----
-  mx4 = {}
-  try:
-    kw4 = dict(kw, qtype='mxfp4')
-    how_a4, how_w4 = bdg.get_how_to_quantize(for_lhs=True, **kw4), bdg.get_how_to_quantize(for_lhs=False, **kw4)
-    q4_ms = _time_calls(lambda i: bq.quantize(acts[i % 2], how_a4), steps, 3)
-    aq4 = [bq.quantize(a, how_a4) for a in acts]
-    wq4 = [bq.quantize(w, how_w4) for w in wts]
-    ms4 = sorted(_time_calls(lambda i: bdg.dot_general(aq4[i % 2], wq4[i % 2], DN), steps, 3) for _ in range(3))[1]
-    _lib.raise_on_device_error()
-    got4 = _np(bdg.dot_general(aq4[0], wq4[0], DN)[ri])
-    a4_o = oq.quantize(_np(acts[0][ri]), odg.get_how_to_quantize(for_lhs=True, **kw4))
-    w4_o = oq.QArray(_np(wq4[0].qvalue).view(a4_o.qvalue.dtype), _np(wq4[0].scale), None, 'mxfp4')
-    ver4 = _tolerance_report(got4, omx.mxfp_dot_general(a4_o, w4_o, DN))
-    ver4.update({'rows': int(rows.size),
-                 'act_codes_bit_exact': bool(np.array_equal(_np(aq4[0].qvalue[ri]), a4_o.qvalue.view(np.uint8))),
-                 'act_scales_bit_exact': bool(np.array_equal(_np(aq4[0].scale[ri]).view(np.uint8),
-                                                             a4_o.scale.view(np.uint8)))})
-    # the GEMM alone, on the packed operands dot_general leaves beside the weight
-    L = _lib.lib()
-    st = _lib.stream_ptr(device)
-    ap = torch.empty((Ms, Ks // 2), dtype=torch.uint8, device=device)
-    _lib.check(L.qwx_mx4_pack_codes(_lib.ptr(aq4[0].qvalue), Ms, Ks, 0, _lib.ptr(ap), st), 'pack')
-    pa = torch.empty(L.qwx_mx4_scales_packed_bytes(0, Ms, Ks), dtype=torch.uint8, device=device)
-    sc = aq4[0].scale.contiguous()
-    _lib.check(L.qwx_mx4_pack_scales(0, _lib.ptr(sc), _lib.FLOAT_CODES[sc.dtype], Ms, Ks, 0, _lib.ptr(pa),
-                                     pa.numel(), st), 'pack')
-    _, bp, pb = wq4[0]._mx4_packed
-    o4 = torch.empty((Ms, Ns), dtype=torch.bfloat16, device=device)
-    err = _lib.error_flag(device)
-    gemm4 = lambda i: _lib.check(L.qwx_gemm_mx4(_lib.ptr(ap), _lib.ptr(bp), Ms, Ns, Ks, _lib.ptr(pa), _lib.ptr(pb),
-                                                _lib.ptr(o4), _lib.BF16, _lib.ptr(err), st), 'gemm_mx4')
-    g4_ms = sorted(_time_calls(gemm4, steps, 3) for _ in range(3))[1]
-    ops = 2.0 * Ms * Ns * Ks
-    mx4 = {'ms_per_step': ms4, 'value': ops / (ms4 * 1e-3) / 1e12, 'unit': 'TOPS',
-           'gemm_alone_ms': g4_ms, 'gemm_alone_tops': ops / (g4_ms * 1e-3) / 1e12,
-           'gemm_alone_note': 'one operand set (48 MB of codes): the weight stays in L2',
-           'quantize_ms': q4_ms, 'kernel': 'gemm_mx8_kernel<., 4-bit> (tcgen05.mma.kind::mxf4.block_scale)',
-           'verified': ver4, 'timing': 'median of 3 blocks of `steps` calls'}
-  except Exception as e:  # noqa: BLE001 -- the mxfp8 record stands on its own
-    mx4 = {'unavailable': repr(e)[:300]}
+  # ---- the same product with e2m1 codes: "mxfp4" (power-of-two scale per 32) and "nvfp4"
+  # (e4m3-valued scale per 16), public dot_general on two such QArrays ----
+  def four_bit_record(qtype, tile):
+    try:
+      kw4 = dict(kw, qtype=qtype, tile_size=tile)
+      how_a4, how_w4 = bdg.get_how_to_quantize(for_lhs=True, **kw4), bdg.get_how_to_quantize(for_lhs=False, **kw4)
+      q4_ms = _time_calls(lambda i: bq.quantize(acts[i % 2], how_a4), steps, 3)
+      aq4 = [bq.quantize(a, how_a4) for a in acts]
+      wq4 = [bq.quantize(w, how_w4) for w in wts]
+      ms4 = sorted(_time_calls(lambda i: bdg.dot_general(aq4[i % 2], wq4[i % 2], DN), steps, 3) for _ in range(3))[1]
+      _lib.raise_on_device_error()
+      got4 = _np(bdg.dot_general(aq4[0], wq4[0], DN)[ri])
+      a4_o = oq.quantize(_np(acts[0][ri]), odg.get_how_to_quantize(for_lhs=True, **kw4))
+      w4_o = oq.QArray(_np(wq4[0].qvalue).view(a4_o.qvalue.dtype), _np(wq4[0].scale), None, qtype)
+      ver4 = _tolerance_report(got4, omx.mxfp_dot_general(a4_o, w4_o, DN))
+      ver4.update({'rows': int(rows.size),
+                   'act_codes_bit_exact': bool(np.array_equal(_np(aq4[0].qvalue[ri]), a4_o.qvalue.view(np.uint8))),
+                   'act_scales_bit_exact': bool(np.array_equal(_np(aq4[0].scale[ri]).view(np.uint8),
+                                                               a4_o.scale.view(np.uint8)))})
+      # the GEMM alone, on the packed operands dot_general leaves beside the weight
+      L = _lib.lib()
+      st = _lib.stream_ptr(device)
+      nv = qtype == 'nvfp4'
+      packed_bytes = L.qwx_nvfp4_scales_packed_bytes if nv else L.qwx_mx4_scales_packed_bytes
+      pack_scales = L.qwx_nvfp4_pack_scales if nv else L.qwx_mx4_pack_scales
+      gemm = L.qwx_gemm_nvfp4 if nv else L.qwx_gemm_mx4
+      ap = torch.empty((Ms, Ks // 2), dtype=torch.uint8, device=device)
+      _lib.check(L.qwx_mx4_pack_codes(_lib.ptr(aq4[0].qvalue), Ms, Ks, 0, _lib.ptr(ap), st), 'pack')
+      pa = torch.empty(packed_bytes(0, Ms, Ks), dtype=torch.uint8, device=device)
+      sc = aq4[0].scale.contiguous()
+      _lib.check(pack_scales(0, _lib.ptr(sc), _lib.FLOAT_CODES[sc.dtype], Ms, Ks, 0, _lib.ptr(pa), pa.numel(), st),
+                 'pack')
+      _, bp, pb = wq4[0]._mx4_packed
+      o4 = torch.empty((Ms, Ns), dtype=torch.bfloat16, device=device)
+      err = _lib.error_flag(device)
+      gemm4 = lambda i: _lib.check(gemm(_lib.ptr(ap), _lib.ptr(bp), Ms, Ns, Ks, _lib.ptr(pa), _lib.ptr(pb),
+                                        _lib.ptr(o4), _lib.BF16, _lib.ptr(err), st), 'gemm_fp4')
+      g4_ms = sorted(_time_calls(gemm4, steps, 3) for _ in range(3))[1]
+      ops = 2.0 * Ms * Ns * Ks
+      return {'ms_per_step': ms4, 'value': ops / (ms4 * 1e-3) / 1e12, 'unit': 'TOPS', 'block': tile,
+              'gemm_alone_ms': g4_ms, 'gemm_alone_tops': ops / (g4_ms * 1e-3) / 1e12,
+              'gemm_alone_note': 'one operand set (48 MB of codes): the weight stays in L2',
+              'quantize_ms': q4_ms,
+              'kernel': 'gemm_mx8_kernel, 4-bit form (tcgen05.mma.kind::%s.block_scale)' % ('mxf4nvf4' if nv else 'mxf4'),
+              'verified': ver4, 'timing': 'median of 3 blocks of `steps` calls'}
+    except Exception as e:  # noqa: BLE001 -- the mxfp8 record stands on its own
+      return {'unavailable': repr(e)[:300]}
+  mx4 = four_bit_record('mxfp4', 32)
+  nv4 = four_bit_record('nvfp4', 16)
   return {
-      'mxfp4': mx4,
+      'mxfp4': mx4, 'nvfp4': nv4,
       'M': Ms, 'K': Ks, 'N': Ns, 'block': 32, 'ms_per_step': ms, 'steps': steps, 'blocks_ms_per_step': blocks,
       'timing': 'median of 5 blocks of `steps` calls', 'value': achieved, 'unit': 'TOPS',
       'l2': '2 operand sets + output (256 MB) cycled',

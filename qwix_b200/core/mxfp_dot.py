@@ -5,7 +5,8 @@ elements) the contraction runs as one block-scaled tensor-core GEMM: `qwx_gemm_m
 the scales inside `tcgen05.mma.kind::mxf8f6f4.block_scale` and accumulates in float32, which
 is what `jax.nn.scaled_matmul` computes for the reference.  Two MXFP4 QArrays (e2m1 codes) take
 `qwx_gemm_mx4` (`kind::mxf4.block_scale`) after their codes are packed two per byte along the
-contracted axis.  Anything else returns None and the caller falls back to the ordinary paths,
+contracted axis; two NVFP4 QArrays (the same codes, an e4m3-valued scale per 16 elements) take
+`qwx_gemm_nvfp4` (`kind::mxf4nvf4.block_scale`).  Anything else returns None and the caller falls back to the ordinary paths,
 as in the reference.
 """
 
@@ -51,12 +52,13 @@ def _inputs_compatible(ldims, rdims) -> bool:
 
 def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
   """mxfp_dot.py:24-79.  Returns None when the operands are not both microscaled, their
-  scale layouts do not match, or the format has no kernel here (mxfp4 / nvfp4)."""
+  scale layouts do not match, or the pair has no kernel here (mxfp8_16, mixed formats)."""
   if not (_is_mxfp(lhs) and _is_mxfp(rhs)):
     return None
-  if lhs.qtype != rhs.qtype or lhs.qtype not in ('mxfp8', 'mxfp4'):
-    return None          # 16-wide blocks, mixed formats: not built; the caller dequantizes
-  four_bit = lhs.qtype == 'mxfp4'
+  if lhs.qtype != rhs.qtype or lhs.qtype not in ('mxfp8', 'mxfp4', 'nvfp4'):
+    return None          # mxfp8 with 16-wide blocks, mixed formats: not built; the caller dequantizes
+  four_bit = lhs.qtype in ('mxfp4', 'nvfp4')
+  block = 16 if lhs.qtype == 'nvfp4' else _MX_BLOCK
   (lca, rca), (lba, rba) = dimension_numbers
   lca, rca, lba, rba = map(list, (lca, rca, lba, rba))
   lval, lscale, ldims = _flatten_to_3d(lhs, lca, lba)
@@ -65,8 +67,8 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
     return None
   B, M, K, Ks = ldims
   N = rdims[1]
-  if Ks * _MX_BLOCK != K or K % (256 if four_bit else 128):
-    return None          # blocks of flattened K must be the 32-wide blocks; whole 128-byte stages
+  if Ks * block != K or K % (256 if four_bit else 128):
+    return None          # blocks of flattened K must be the format's blocks; whole 128-byte stages
   _, res_t = qarray.get_accumulator_and_result_type(
       lhs, rhs, preferred_element_type=preferred_element_type)
   if res_t not in _lib.FLOAT_CODES:
@@ -95,7 +97,7 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
   out = torch.empty((B, M, N), dtype=res_t, device=dev)
   err = _lib.error_flag(dev)
   if four_bit:
-    _mx4_batches(L, lhs, rhs, a3, sa3, b3, sb3, k_major, layout, B, M, N, K, out, res_t, err, stream)
+    _fp4_batches(L, lhs.qtype, rhs, a3, sa3, b3, sb3, k_major, layout, B, M, N, K, out, res_t, err, stream)
     bshape = [lhs.qvalue.shape[i] for i in lba]
     lfree = [lhs.qvalue.shape[i] for i in range(lhs.qvalue.ndim) if i not in lca and i not in lba]
     return out.reshape(bshape + lfree + [rhs.qvalue.shape[i] for i in rfree])
@@ -126,19 +128,23 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
   return out.reshape(bshape + lfree + rfree_shape)
 
 
-def _mx4_batches(L, lhs, rhs, a3, sa3, b3, sb3, k_major, layout, B, M, N, K, out, res_t, err, stream):
-  """The MXFP4 leg: codes packed two per byte along K (the weight's packed codes and scale bytes
-  are kept beside the QArray), then one `qwx_gemm_mx4` per batch element."""
+def _fp4_batches(L, qtype, rhs, a3, sa3, b3, sb3, k_major, layout, B, M, N, K, out, res_t, err, stream):
+  """The 4-bit leg: codes packed two per byte along K (the weight's packed codes and scale bytes
+  are kept beside the QArray), then one block-scaled GEMM per batch element."""
   dev = a3.device
-  na = L.qwx_mx4_scales_packed_bytes(0, M, K)
-  nb = L.qwx_mx4_scales_packed_bytes(1, N, K)
+  if qtype == 'nvfp4':
+    packed_bytes, pack_scales, gemm = L.qwx_nvfp4_scales_packed_bytes, L.qwx_nvfp4_pack_scales, L.qwx_gemm_nvfp4
+  else:
+    packed_bytes, pack_scales, gemm = L.qwx_mx4_scales_packed_bytes, L.qwx_mx4_pack_scales, L.qwx_gemm_mx4
+  na = packed_bytes(0, M, K)
+  nb = packed_bytes(1, N, K)
   for b in range(B):
     ap = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
     _lib.check(L.qwx_mx4_pack_codes(_lib.ptr(a3[b]), M, K, 0, _lib.ptr(ap), stream), 'mx4_pack_codes')
     pa = torch.empty(na, dtype=torch.uint8, device=dev)
-    _lib.check(L.qwx_mx4_pack_scales(0, _lib.ptr(sa3[b]), numerics.code_of_float(sa3.dtype), M, K, 0,
-                                     _lib.ptr(pa), na, stream), 'mx4_pack_scales')
-    key = (layout, N, K, rhs.qvalue.data_ptr(), rhs.scale.data_ptr())
+    _lib.check(pack_scales(0, _lib.ptr(sa3[b]), numerics.code_of_float(sa3.dtype), M, K, 0,
+                           _lib.ptr(pa), na, stream), 'pack_scales')
+    key = (qtype, layout, N, K, rhs.qvalue.data_ptr(), rhs.scale.data_ptr())
     cached = getattr(rhs, '_mx4_packed', None) if B == 1 else None
     if cached is not None and cached[0] == key:
       bp, pb = cached[1], cached[2]
@@ -146,12 +152,12 @@ def _mx4_batches(L, lhs, rhs, a3, sa3, b3, sb3, k_major, layout, B, M, N, K, out
       bp = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
       _lib.check(L.qwx_mx4_pack_codes(_lib.ptr(b3[b]), N, K, k_major, _lib.ptr(bp), stream), 'mx4_pack_codes')
       pb = torch.empty(nb, dtype=torch.uint8, device=dev)
-      _lib.check(L.qwx_mx4_pack_scales(1, _lib.ptr(sb3[b]), numerics.code_of_float(sb3.dtype), N, K, k_major,
-                                       _lib.ptr(pb), nb, stream), 'mx4_pack_scales')
+      _lib.check(pack_scales(1, _lib.ptr(sb3[b]), numerics.code_of_float(sb3.dtype), N, K, k_major,
+                             _lib.ptr(pb), nb, stream), 'pack_scales')
       if B == 1:
         try:
           object.__setattr__(rhs, '_mx4_packed', (key, bp, pb))
         except Exception:  # noqa: BLE001 -- a QArray that cannot carry the cache just repacks
           pass
-    _lib.check(L.qwx_gemm_mx4(_lib.ptr(ap), _lib.ptr(bp), M, N, K, _lib.ptr(pa), _lib.ptr(pb),
-                              _lib.ptr(out[b]), _lib.FLOAT_CODES[res_t], _lib.ptr(err), stream), 'gemm_mx4')
+    _lib.check(gemm(_lib.ptr(ap), _lib.ptr(bp), M, N, K, _lib.ptr(pa), _lib.ptr(pb),
+                    _lib.ptr(out[b]), _lib.FLOAT_CODES[res_t], _lib.ptr(err), stream), 'gemm_fp4')

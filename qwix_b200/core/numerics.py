@@ -22,9 +22,11 @@ _BUILT = {
     'mxfp8': (torch.float8_e4m3fn, _lib.MXFP8),
     # e2m1 codes, one per byte (low nibble), under power-of-two scales per 32 values
     'mxfp4': (torch.uint8, _lib.MXFP4),
+    # the same codes under an e4m3-valued scale per 16 values
+    'nvfp4': (torch.uint8, _lib.NVFP4),
 }
 _KNOWN_UNBUILT = ('nf4', 'int2', 'int3', 'int5', 'int6', 'int7', 'int16', 'uint8',
-                  'mxfp8_16', 'nvfp4', 'float8_e5m2',
+                  'mxfp8_16', 'float8_e5m2',
                   'float4_e2m1fn', 'uint4')
 
 

@@ -125,6 +125,8 @@ struct MX8 { static constexpr bool kFloat = true; };
 // e2m1 codes (sign, two exponent bits, one significand bit: 0, 0.5, 1, 1.5, 2, 3, 4, 6), one
 // per byte in the low nibble, under a power-of-two scale per 32 values ("mxfp4")
 struct MX4 { static constexpr bool kFloat = true; };
+// the same e2m1 codes under a scale per 16 values that is itself an e4m3 number ("nvfp4")
+struct NV4 { static constexpr bool kFloat = true; };
 
 // Symmetric bound B (codes cover [-B, B]) and asymmetric (qmin, qmax).
 template <typename Q> __host__ __device__ constexpr float sym_bound();
@@ -133,12 +135,13 @@ template <> __host__ __device__ constexpr float sym_bound<S4>() { return 7.5f; }
 template <> __host__ __device__ constexpr float sym_bound<E4M3>() { return 448.0f; }
 template <> __host__ __device__ constexpr float sym_bound<MX8>() { return 448.0f; }
 template <> __host__ __device__ constexpr float sym_bound<MX4>() { return 6.0f; }
+template <> __host__ __device__ constexpr float sym_bound<NV4>() { return 6.0f; }
 
 // Scaled float -> code, returned as the byte that is stored for 8-bit codes or the
 // sign-extended value for int4.  Integers: round-half-even, saturate, NaN -> 0 (the
 // float->int convert of XLA); e4m3: clip to +/-448 then round-to-nearest-even, NaN stays.
 template <typename Q> __device__ __forceinline__ int to_code(float y) {
-  if constexpr (std::is_same<Q, MX4>::value) {
+  if constexpr (std::is_same<Q, MX4>::value || std::is_same<Q, NV4>::value) {
     // e2m1 has neither NaN nor infinity: clip to +/-6, round to nearest even; a NaN becomes a
     // zero of the opposite sign (what ml_dtypes' cast does; the reference pins no value)
     if (y != y) return (__float_as_uint(y) >> 31) ? 0x0 : 0x8;

@@ -26,7 +26,7 @@ struct CalibArgs {
   float arg;       // already narrowed to float
 };
 
-enum class Out { kS8, kS4U, kS4P, kE4M3, kMX8, kMX4 };
+enum class Out { kS8, kS4U, kS4P, kE4M3, kMX8, kMX4, kNV4 };
 template <Out O> struct OutTraits;
 template <> struct OutTraits<Out::kS8> { using Q = S8; };
 template <> struct OutTraits<Out::kS4U> { using Q = S4; };
@@ -34,6 +34,7 @@ template <> struct OutTraits<Out::kS4P> { using Q = S4; };
 template <> struct OutTraits<Out::kE4M3> { using Q = E4M3; };
 template <> struct OutTraits<Out::kMX8> { using Q = MX8; };
 template <> struct OutTraits<Out::kMX4> { using Q = MX4; };
+template <> struct OutTraits<Out::kNV4> { using Q = NV4; };
 
 // ---- scalar recipes -------------------------------------------------------------------
 
@@ -60,6 +61,9 @@ __device__ __forceinline__ float symmetric_scale(float absmax) {
     constexpr float c = std::is_same<Q, MX4>::value ? 12.0f / 7.0f : 60.0f / 31.0f;
     const float biased = round_to<T>(__fmul_rn(s, round_to<T>(c)));
     s = __uint_as_float(__float_as_uint(round_to<BF16>(biased)) & 0x7F800000u);
+  } else if constexpr (std::is_same<Q, NV4>::value) {
+    // the scale becomes an e4m3 number: clip to +/-448, round to nearest even (qarray.py:580-581)
+    s = s != s ? s : e4m3_to_float((uint8_t)to_code<E4M3>(s));
   }
   return s;
 }
@@ -333,11 +337,13 @@ quantize_rows_kernel(const void* __restrict__ x, int64_t segments, int64_t tc, C
 template <typename T, typename Q = MX8>
 __global__ void __launch_bounds__(kThreads)
 quantize_mx8_blocks_kernel(const void* __restrict__ x, int64_t nvec, void* __restrict__ q,
-                           void* __restrict__ scale) {
+                           void* __restrict__ scale, int strict) {
+  // lanes per block: four 16-byte vectors of a 32-wide block, two of a 16-wide one (nvfp4)
+  constexpr int kLanes = std::is_same<Q, NV4>::value ? 2 : 4;
   griddep_launch_dependents();
   griddep_wait();
   const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  const bool live = i < nvec;                 // whole groups of four: nvec is a multiple of 4
+  const bool live = i < nvec;                 // whole groups: nvec is a multiple of kLanes
   float v[8];
   if (live) {
     load8<T>(x, i * 8, v);
@@ -349,10 +355,23 @@ quantize_mx8_blocks_kernel(const void* __restrict__ x, int64_t nvec, void* __res
 #pragma unroll
   for (int j = 0; j < 8; ++j) bits = max(bits, __float_as_uint(v[j]) & 0x7fffffffu);   // NaN sorts last
   bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 1));
-  bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 2));
+  if constexpr (kLanes == 4) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 2));
   if (!live) return;
   const float s = symmetric_scale<T, Q>(__uint_as_float(bits));
-  if ((threadIdx.x & 3) == 0) store1<T>(scale, i >> 2, s);
+  if ((threadIdx.x & (kLanes - 1)) == 0) store1<T>(scale, i / kLanes, s);
+  if constexpr (std::is_same<Q, NV4>::value) {
+    // the scale is an e4m3 number, not a power of two: the reference's true division
+    const Divider<T> div(s, strict != 0);
+    uint32_t w4[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float y = div(v[j]);
+      if (strict) y = round_to<T>(y);
+      w4[j >> 2] |= (uint32_t)to_code<NV4>(y) << (8 * (j & 3));
+    }
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(q) + i * 8) = make_uint2(w4[0], w4[1]);
+    return;
+  }
   const float inv = __fdiv_rn(1.0f, s);       // exact: s is a power of two (or NaN, which propagates)
   if constexpr (std::is_same<Q, MX4>::value) {
     // e2m1 codes, one per byte
@@ -727,7 +746,7 @@ dequantize_kernel(const void* __restrict__ q, View vw, const void* __restrict__ 
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         code[j] = (O == Out::kE4M3 || O == Out::kMX8) ? e4m3_to_float(b[j])
-                  : (O == Out::kMX4 ? e2m1_to_float(b[j]) : (float)(int8_t)b[j]);
+                  : ((O == Out::kMX4 || O == Out::kNV4) ? e2m1_to_float(b[j]) : (float)(int8_t)b[j]);
     }
     // scale group of each of the eight columns: one division, then a running remainder
     int64_t g = gbase + col / vw.tc;
@@ -804,6 +823,7 @@ int dispatch_out(int qtype, Fn&& fn) {
     case QWX_E4M3: return fn(std::integral_constant<Out, Out::kE4M3>{});
     case QWX_MXFP8: return fn(std::integral_constant<Out, Out::kMX8>{});
     case QWX_MXFP4: return fn(std::integral_constant<Out, Out::kMX4>{});
+    case QWX_NVFP4: return fn(std::integral_constant<Out, Out::kNV4>{});
     default: return (int)QWX_ERR_DTYPE;
   }
 }
@@ -817,7 +837,7 @@ bool row_segment_view(const void* x, const void* q, int64_t tp, int64_t tr, int6
 int check_method(int method, int has_arg, int qtype) {
   if (method != QWX_ABSMAX && method != QWX_MINMAX && method != QWX_RMS) return QWX_ERR_UNSUPPORTED;
   if (method == QWX_RMS && !has_arg) return QWX_ERR_SHAPE;
-  if (method == QWX_MINMAX && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4)) return QWX_ERR_DTYPE;  // numerics.py:64-92
+  if (method == QWX_MINMAX && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4 || qtype == QWX_NVFP4)) return QWX_ERR_DTYPE;  // numerics.py:64-92
   return QWX_OK;
 }
 
@@ -893,7 +913,7 @@ int qwx_compute_scale_zero_point(const void* calib_a, const void* calib_b, int d
                                  int qtype, void* scale, void* zero_point, qwx_stream_t stream) {
   if (!calib_a || !scale) return QWX_ERR_NULL;
   if (calib_b && !zero_point) return QWX_ERR_NULL;
-  if (calib_b && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4)) return QWX_ERR_DTYPE;
+  if (calib_b && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4 || qtype == QWX_NVFP4)) return QWX_ERR_DTYPE;
   if (n <= 0) return QWX_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned blocks = (unsigned)((n + 255) / 256);
@@ -915,6 +935,9 @@ int qwx_compute_scale_zero_point(const void* calib_a, const void* calib_b, int d
       case QWX_MXFP4:
         scale_zero_point_kernel<T, MX4><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
         break;
+      case QWX_NVFP4:
+        scale_zero_point_kernel<T, NV4><<<blocks, 256, 0, st>>>(calib_a, calib_b, n, scale, (int8_t*)zero_point);
+        break;
       default: return (int)QWX_ERR_DTYPE;
     }
     QWX_CHECK_LAUNCH();
@@ -927,7 +950,7 @@ int qwx_quantize_with_scale(const void* x, int x_dtype, int64_t P, int64_t R, in
                             const void* zero_point, int qtype, int rounding, void* q,
                             qwx_stream_t stream) {
   if (!x || !scale || !q) return QWX_ERR_NULL;
-  if (zero_point && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4)) return QWX_ERR_DTYPE;
+  if (zero_point && (qtype == QWX_E4M3 || qtype == QWX_MXFP8 || qtype == QWX_MXFP4 || qtype == QWX_NVFP4)) return QWX_ERR_DTYPE;
   View vw;
   int rc = make_view(P, R, C, tp, tr, tc, &vw);
   if (rc) return rc;
@@ -982,14 +1005,29 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
       }
       return (int)QWX_OK;
     }
+    if (qtype == QWX_NVFP4 && tc == 16 && method == QWX_ABSMAX && !has_arg &&
+        (x_dtype == QWX_BF16 || x_dtype == QWX_F32)) {
+      const int64_t nvec = segments * 2;
+      const unsigned blocks = (unsigned)((nvec + kThreads - 1) / kThreads);
+      const int strict = rounding == QWX_STRICT ? 1 : 0;
+      const cudaError_t e =
+          x_dtype == QWX_BF16
+              ? launch_dependent(quantize_mx8_blocks_kernel<BF16, NV4>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale, strict)
+              : launch_dependent(quantize_mx8_blocks_kernel<F32, NV4>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale, strict);
+      if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)QWX_ERR_LAUNCH;
+      }
+      return (int)QWX_OK;
+    }
     if (qtype == QWX_MXFP4 && tc == 32 && method == QWX_ABSMAX && !has_arg &&
         (x_dtype == QWX_BF16 || x_dtype == QWX_F32)) {
       const int64_t nvec = segments * 4;
       const unsigned blocks = (unsigned)((nvec + kThreads - 1) / kThreads);
       const cudaError_t e =
           x_dtype == QWX_BF16
-              ? launch_dependent(quantize_mx8_blocks_kernel<BF16, MX4>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale)
-              : launch_dependent(quantize_mx8_blocks_kernel<F32, MX4>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale);
+              ? launch_dependent(quantize_mx8_blocks_kernel<BF16, MX4>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale, 1)
+              : launch_dependent(quantize_mx8_blocks_kernel<F32, MX4>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale, 1);
       if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return (int)QWX_ERR_LAUNCH;
@@ -1002,8 +1040,8 @@ int qwx_quantize(const void* x, int x_dtype, int64_t P, int64_t R, int64_t C, in
       const unsigned blocks = (unsigned)((nvec + kThreads - 1) / kThreads);
       const cudaError_t e =
           x_dtype == QWX_BF16
-              ? launch_dependent(quantize_mx8_blocks_kernel<BF16>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale)
-              : launch_dependent(quantize_mx8_blocks_kernel<F32>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale);
+              ? launch_dependent(quantize_mx8_blocks_kernel<BF16>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale, 1)
+              : launch_dependent(quantize_mx8_blocks_kernel<F32>, dim3(blocks), dim3(kThreads), 0, st, x, nvec, q, scale, 1);
       if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return (int)QWX_ERR_LAUNCH;

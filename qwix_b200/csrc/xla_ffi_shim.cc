@@ -263,6 +263,31 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
     ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Arg<Buf>().Arg<Buf>().Arg<Buf>()
         .Ret<Buf>().Ret<Buf>().Attr<int64_t>("k"));
 
+// ---- NVFP4 block-scaled contraction (codes packed by qwx_mx4_pack_codes) --------------------------
+
+ffi::Error Nvfp4PackScalesImpl(cudaStream_t stream, Buf scale, Out packed, int32_t operand, int64_t rows,
+                               int64_t k, int32_t k_major) {
+  return Status(qwx_nvfp4_pack_scales(operand, scale.untyped_data(), FloatCode(scale.element_type()), rows, k,
+                                      k_major, packed->untyped_data(), packed->size_bytes(), S(stream)));
+}
+XLA_FFI_DEFINE_HANDLER_SYMBOL(
+    qwx_nvfp4_pack_scales_ffi, Nvfp4PackScalesImpl,
+    ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Ret<Buf>().Attr<int32_t>("operand")
+        .Attr<int64_t>("rows").Attr<int64_t>("k").Attr<int32_t>("k_major"));
+
+ffi::Error GemmNvfp4Impl(cudaStream_t stream, Buf a_packed, Buf b_packed, Buf sfa, Buf sfb, Out out, Out err,
+                         int64_t k) {
+  const auto od = out->dimensions();
+  return Status(qwx_gemm_nvfp4(a_packed.untyped_data(), b_packed.untyped_data(), od[0], od[1], k,
+                               sfa.untyped_data(), sfb.untyped_data(), out->untyped_data(),
+                               OutCode(out->element_type()), static_cast<int32_t*>(err->untyped_data()),
+                               S(stream)));
+}
+XLA_FFI_DEFINE_HANDLER_SYMBOL(
+    qwx_gemm_nvfp4_ffi, GemmNvfp4Impl,
+    ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<Buf>().Arg<Buf>().Arg<Buf>().Arg<Buf>()
+        .Ret<Buf>().Ret<Buf>().Attr<int64_t>("k"));
+
 ffi::Error QuantGemmQ8Impl(cudaStream_t stream, Buf a, Buf wq, Buf sw, Out out, Out workspace, Out err,
                            int32_t b_layout, int32_t rounding, int32_t epilogue) {
   const auto ad = a.dimensions();
