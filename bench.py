@@ -639,7 +639,32 @@ def mxfp8_record(args, device, lib_peaks: dict):
                                         _lib.ptr(o4), _lib.BF16, _lib.ptr(err), st), 'gemm_fp4')
       g4_ms = sorted(_time_calls(gemm4, steps, 3) for _ in range(3))[1]
       ops = 2.0 * Ms * Ns * Ks
+      library4 = {}
+      try:
+        # the vendor's block-scaled GEMM on the same packed codes; its scale layout (128 rows x 4
+        # blocks per group, row groups outermost) is what the 8-bit packer writes for operand 0
+        if nv:
+          raise NotImplementedError('no e4m3 scale packer in the vendor layout here')
+        def vendor_scales(scale_rows_by_blocks, n_rows):
+          nb_ = L.qwx_mx_scales_packed_bytes(0, n_rows, Ks)
+          o_ = torch.empty(nb_, dtype=torch.uint8, device=device)
+          sc_ = scale_rows_by_blocks.contiguous()
+          _lib.check(L.qwx_mx_pack_scales(0, _lib.ptr(sc_), _lib.FLOAT_CODES[sc_.dtype], n_rows, Ks, 0,
+                                          _lib.ptr(o_), nb_, st), 'pack')
+          return o_.view(torch.float8_e8m0fnu)
+        va, vb = vendor_scales(aq4[0].scale, Ms), vendor_scales(wq4[0].scale.t(), Ns)
+        a_x2, b_x2 = ap.view(torch.float4_e2m1fn_x2), bp.view(torch.float4_e2m1fn_x2)
+        lib4 = lambda: torch._scaled_mm(a_x2, b_x2.t(), scale_a=va, scale_b=vb, out_dtype=torch.bfloat16)
+        ref4 = lib4()
+        gemm4(0)
+        library4['max_abs_diff_to_ours'] = float((ref4.float() - o4.float()).abs().max())
+        l4_ms = sorted(_time_calls(lambda i: lib4(), steps, 3) for _ in range(3))[1]
+        library4.update({'ms_per_step': l4_ms, 'tops': ops / (l4_ms * 1e-3) / 1e12,
+                         'how': 'torch._scaled_mm on float4_e2m1fn_x2 operands with float8_e8m0fnu block scales'})
+      except Exception as e:  # noqa: BLE001 -- context only
+        library4['unavailable'] = repr(e)[:200]
       return {'ms_per_step': ms4, 'value': ops / (ms4 * 1e-3) / 1e12, 'unit': 'TOPS', 'block': tile,
+              'library_block_scaled': library4,
               'gemm_alone_ms': g4_ms, 'gemm_alone_tops': ops / (g4_ms * 1e-3) / 1e12,
               'gemm_alone_note': 'one operand set (48 MB of codes): the weight stays in L2',
               'quantize_ms': q4_ms,
