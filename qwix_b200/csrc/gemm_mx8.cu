@@ -36,6 +36,7 @@
 #include "sm100.cuh"
 
 namespace qwx {
+
 namespace {
 
 using namespace sm100;
@@ -187,50 +188,58 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     bool ok = true;
     const uint32_t tsfa = tmem_base + kXSfCol;        // 4 columns per scale group
     const uint32_t tsfb = tsfa + 4 * kSfGroups;       // 8 columns per scale group
+    // The issuing thread's own instruction stream is what bounds this kernel (a lone thread
+    // issues an instruction every several cycles; four M128 N224 MMAs take 448), so nothing is
+    // computed per MMA that can be computed once: descriptors of stage 0 here, the stage's offset
+    // (in the descriptors' 16-byte units) as a running sum.
+    const uint64_t da0 = make_smem_desc(tiles, 16, 1024);
+    const uint64_t db0 = BLAYOUT == QWX_B_NK ? make_smem_desc(tiles + kXABytes, 16, 1024)
+                                              : make_smem_desc(tiles + kXABytes, XK * 128, 1024);
+    const uint64_t dsa0 = make_smem_desc_plain(tiles + kXABytes + kBStage, 16, 128);
+    const uint64_t dsb0 = dsa0 + (uint64_t)(kSfaStage >> 4);
+    constexpr uint64_t kStageStep = kXStageBytes >> 4;
+    constexpr uint64_t kKStep = BLAYOUT == QWX_B_NK ? (XUMMA_K >> 4) : ((XUMMA_K * 128) >> 4);
+    uint64_t off = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       if (lane == 0) {
         ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort);
         tc_fence_after();
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
+      const uint32_t d_tmem = tmem_base + acc * kXAccCols;
       for (int kb = 0; kb < kblocks && ok; ++kb) {
         if (lane == 0) {
           ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort);
           if (ok) {
             tc_fence_after();
-            const uint32_t sa = tiles + stage * kXStageBytes;
-            const uint32_t sb = sa + kXABytes;
-            const uint32_t ssfa = sb + kBStage;
-            const uint32_t ssfb = ssfa + kSfaStage;
+            const uint64_t da = da0 + off, db = db0 + off, dsa = dsa0 + off, dsb = dsb0 + off;
             // scale bytes: 32 rows of 16 B per 128 operand rows, four 8-row core matrices 128 B apart
 #pragma unroll
             for (int sg = 0; sg < kSfGroups; ++sg) {
-              tmem_cp_32x128b_warpx4(tsfa + 4 * sg, make_smem_desc_plain(ssfa + sg * kXSfaBytes, 16, 128));
-              tmem_cp_32x128b_warpx4(tsfb + 8 * sg, make_smem_desc_plain(ssfb + sg * kXSfbBytes, 16, 128));
-              tmem_cp_32x128b_warpx4(tsfb + 8 * sg + 4, make_smem_desc_plain(ssfb + sg * kXSfbBytes + 512, 16, 128));
+              tmem_cp_32x128b_warpx4(tsfa + 4 * sg, dsa + (uint64_t)(sg * (kXSfaBytes >> 4)));
+              tmem_cp_32x128b_warpx4(tsfb + 8 * sg, dsb + (uint64_t)(sg * (kXSfbBytes >> 4)));
+              tmem_cp_32x128b_warpx4(tsfb + 8 * sg + 4, dsb + (uint64_t)(sg * (kXSfbBytes >> 4) + (512 >> 4)));
             }
 #pragma unroll
             for (int kk = 0; kk < XK / XUMMA_K; ++kk) {
-              const uint64_t da = make_smem_desc(sa + kk * XUMMA_K, 16, 1024);
-              const uint64_t db = BLAYOUT == QWX_B_NK
-                                      ? make_smem_desc(sb + kk * XUMMA_K, 16, 1024)
-                                      : make_smem_desc(sb + kk * XUMMA_K * 128, XK * 128, 1024);
+              const uint64_t dak = da + (uint64_t)(kk * (XUMMA_K >> 4));
+              const uint64_t dbk = db + (uint64_t)kk * kKStep;
+              const uint32_t accumulate = kk != 0 ? 1u : (uint32_t)(kb != 0);
               if constexpr (FMT == 2) {
                 // four scale bytes per MMA: a word each
-                const uint32_t idesc = make_idesc_mx(1, 1, 0, 0, XM, XN, 0, /*e8m0_scales=*/0);
-                mma_nvf4_ss(tmem_base + acc * kXAccCols, da, db, idesc, tsfa + 4 * kk, tsfb + 8 * kk,
-                            kb != 0 || kk != 0);
+                constexpr uint32_t idesc = make_idesc_mx(1, 1, 0, 0, XM, XN, 0, /*e8m0_scales=*/0);
+                mma_nvf4_ss(d_tmem, dak, dbk, idesc, tsfa + 4 * kk, tsfb + 8 * kk, accumulate);
               } else if constexpr (FMT == 1) {
                 // two scale bytes per MMA: bytes 0-1 or 2-3 of the word, a word per two MMAs
                 const uint32_t id = (uint32_t)(kk & 1) * 2u, sg = (uint32_t)(kk >> 1);
                 const uint32_t idesc = make_idesc_mx(1, 1, 0, 0, XM, XN, id);
-                mma_mx4_ss(tmem_base + acc * kXAccCols, da, db, idesc, (tsfa + 4 * sg) | (id << 30),
-                           (tsfb + 8 * sg) | (id << 30), kb != 0 || kk != 0);
+                mma_mx4_ss(d_tmem, dak, dbk, idesc, (tsfa + 4 * sg) | (id << 30), (tsfb + 8 * sg) | (id << 30),
+                           accumulate);
               } else {
                 const uint32_t idesc = make_idesc_mx(0, 0, 0, BLAYOUT == QWX_B_KN ? 1 : 0, XM, XN, kk);
                 // which of the word's four bytes: in the descriptor and in the two top bits of the addresses
-                mma_mx_ss(tmem_base + acc * kXAccCols, da, db, idesc, tsfa | ((uint32_t)kk << 30),
-                          tsfb | ((uint32_t)kk << 30), kb != 0 || kk != 0);
+                mma_mx_ss(d_tmem, dak, dbk, idesc, tsfa | ((uint32_t)kk << 30), tsfb | ((uint32_t)kk << 30),
+                          accumulate);
               }
             }
             mma_commit(smem_u32(&ctl->empty[stage]));
@@ -238,7 +247,8 @@ gemm_mx8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (++stage == kXStages) { stage = 0; phase ^= 1u; }
+        off += kStageStep;
+        if (++stage == kXStages) { stage = 0; phase ^= 1u; off = 0; }
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
