@@ -37,6 +37,12 @@
 
 namespace qwx {
 
+// gemm_mx_pair.cu: the CTA-pair form for more than 128 rows (both operands K-major, the
+// contracted bytes a multiple of 256)
+int gemm_mx_pair_launch(int fmt, const void* a, const void* b, int64_t M, int64_t N, int64_t kbytes,
+                        const void* sfa, size_t sfa_bytes, const void* sfb, size_t sfb_bytes, void* out,
+                        int out_dtype, int32_t* error_flag, cudaStream_t st);
+
 namespace {
 
 using namespace sm100;
@@ -458,6 +464,10 @@ extern "C" int qwx_gemm_mx8(const void* a, const void* b, int b_layout, int64_t 
       (reinterpret_cast<uintptr_t>(out) & 15))
     return QWX_ERR_ALIGN;
   if (b_layout == QWX_B_KN && (N % 16)) return QWX_ERR_ALIGN;
+  if (b_layout == QWX_B_NK && M > XM && K % 256 == 0)
+    return gemm_mx_pair_launch(0, a, b, M, N, K, sfa_packed, qwx_mx_scales_packed_bytes(0, M, K), sfb_packed,
+                               qwx_mx_scales_packed_bytes(1, N, K), out, out_dtype, error_flag,
+                               (cudaStream_t)stream);
 
   CUtensorMap ta, tb;
   if (!get_encode_tiled()) return QWX_ERR_NO_DEVICE;
@@ -550,6 +560,12 @@ int gemm_fp4(const void* a_packed, const void* b_packed, int64_t M, int64_t N, i
       (reinterpret_cast<uintptr_t>(out) & 15))
     return QWX_ERR_ALIGN;
   const int64_t kbytes = K / 2;
+  if (M > XM && kbytes % 256 == 0) {
+    const size_t na = FMT == 2 ? qwx_nvfp4_scales_packed_bytes(0, M, K) : qwx_mx4_scales_packed_bytes(0, M, K);
+    const size_t nb = FMT == 2 ? qwx_nvfp4_scales_packed_bytes(1, N, K) : qwx_mx4_scales_packed_bytes(1, N, K);
+    return gemm_mx_pair_launch(FMT, a_packed, b_packed, M, N, kbytes, sfa_packed, na, sfb_packed, nb, out,
+                               out_dtype, error_flag, (cudaStream_t)stream);
+  }
   CUtensorMap ta, tb;
   if (!get_encode_tiled()) return QWX_ERR_NO_DEVICE;
   if (!encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_packed, (uint64_t)M, (uint64_t)kbytes, XM, XK) ||
