@@ -81,7 +81,21 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
   rndim = rhs.qvalue.ndim
   rfree = [i for i in range(rndim) if i not in rca and i not in rba]
   kn = rhs.qvalue.permute(rba + rca + rfree)
-  if kn.is_contiguous() and not rval.is_contiguous() and N % 16 == 0:
+  # More than 128 rows take the CTA-pair kernel, which wants both operands K-major: a [K, N]
+  # weight is transposed once and kept beside the QArray (the 4-bit forms repack anyway).
+  pair_form = M > 128 and K % 256 == 0 and not four_bit
+  if pair_form and B == 1 and kn.is_contiguous() and not rval.is_contiguous():
+    cached = getattr(rhs, '_mx_nk', None)
+    if cached is None or cached[0] != rhs.qvalue.data_ptr():
+      cached = (rhs.qvalue.data_ptr(), rval.reshape(N, K).contiguous())
+      try:
+        object.__setattr__(rhs, '_mx_nk', cached)
+      except Exception:  # noqa: BLE001 -- a QArray that cannot carry the cache transposes per call
+        pass
+    b3, layout = cached[1].reshape(1, N, K), _lib.B_NK
+    sb3 = None       # made below only if the packed scale bytes are not beside the QArray yet
+    k_major = 0
+  elif kn.is_contiguous() and not rval.is_contiguous() and N % 16 == 0:
     b3, layout = kn.reshape(B, K, N), _lib.B_KN
     full = [rhs.scale.shape[i] if i in rca else rhs.qvalue.shape[i] for i in range(rndim)]
     sb3 = rhs.scale.expand(full).permute(rba + rca + rfree).reshape(B, Ks, N).contiguous()
@@ -111,6 +125,8 @@ def mxfp_dot_general(lhs, rhs, dimension_numbers, preferred_element_type=None):
     if cached is not None and cached[0] == (layout, N, K, rhs.scale.data_ptr()):
       pb = cached[1]
     else:
+      if sb3 is None:
+        sb3 = rscale.reshape(B, N, Ks).contiguous()
       pb = torch.empty(nb, dtype=torch.uint8, device=dev)
       _lib.check(L.qwx_mx_pack_scales(1, _lib.ptr(sb3[b]), numerics.code_of_float(sb3.dtype), N, K, k_major,
                                       _lib.ptr(pb), nb, stream), 'mx_pack_scales')
