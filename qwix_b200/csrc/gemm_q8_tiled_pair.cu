@@ -59,10 +59,14 @@ constexpr int QN = 256;        // columns per pair
 constexpr int QNH = 128;       // columns of B held by one CTA; also the columns one epilogue warp drains
 constexpr int QK = 128;        // one 128-byte swizzle row of 8-bit codes
 constexpr int QUMMA_K = 32;
-constexpr int kQStages = 6;
+// A stage holds two 128-wide K blocks ([A k0][A k1][B k0][B k1]): one round trip between the two
+// CTAs' barriers per eight MMAs.  With one block per stage (six stages of 32 KB) the round trips
+// were what wide K tiles waited for.
+constexpr int kQHalves = 2;
+constexpr int kQStages = 3;
 constexpr int kQABytes = QM * QK;
 constexpr int kQBBytes = QNH * QK;
-constexpr int kQStageBytes = kQABytes + kQBBytes;
+constexpr int kQStageBytes = kQHalves * (kQABytes + kQBBytes);
 #ifndef QWX_TP_EPI_WARPS
 #define QWX_TP_EPI_WARPS 8
 #endif
@@ -216,6 +220,7 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int kblocks = p.T * p.kb_per_tile;
+  const int kstages = (kblocks + kQHalves - 1) / kQHalves;
   volatile int* abort = &ctl->abort;
 
   if (threadIdx.x == 0) {
@@ -254,17 +259,21 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         const int m0 = (tile % p.tiles_m) * (2 * QM) + (int)rank * QM;
         const int n0 = (tile / p.tiles_m) * QN + (int)rank * QNH;
-        for (int kb = 0; kb < kblocks && ok; ++kb) {
+        for (int sb2 = 0; sb2 < kstages && ok; ++sb2) {
           if (lane == 0) {
             ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort);
             if (ok) {
               const uint32_t sa = tiles + stage * kQStageBytes;
-              const uint32_t sb = sa + kQABytes;
+              const uint32_t sb = sa + kQHalves * kQABytes;
               if (rank == 0) mbar_expect_tx(smem_u32(&ctl->full[stage]), 2 * kQStageBytes);
               const uint32_t bar = full0 + stage * 8;
-              tma_load_2d_pair(sa, &tma_a, kb * QK, m0, bar);
-              if (BLAYOUT == QWX_B_NK) tma_load_2d_pair(sb, &tma_b, kb * QK, n0, bar);
-              else tma_load_2d_pair(sb, &tma_b, n0, kb * QK, bar);
+#pragma unroll
+              for (int h = 0; h < kQHalves; ++h) {
+                const int k0 = (kQHalves * sb2 + h) * QK;     // past K (an odd count of blocks): zeros
+                tma_load_2d_pair(sa + h * kQABytes, &tma_a, k0, m0, bar);
+                if (BLAYOUT == QWX_B_NK) tma_load_2d_pair(sb + h * kQBBytes, &tma_b, k0, n0, bar);
+                else tma_load_2d_pair(sb + h * kQBBytes, &tma_b, n0, k0, bar);
+              }
               ++issued;
             }
           }
@@ -297,19 +306,23 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       const uint32_t empty_peer = map_to_cta(smem_u32(&ctl->empty[0]), 1);
       const uint32_t acc_full_peer = map_to_cta(smem_u32(&ctl->acc_full[0]), 1);
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        for (int t = 0; t < p.T && ok; ++t) {
+        int kb = 0;                 // K block inside the scale tile
+        for (int sb2 = 0; sb2 < kstages && ok; ++sb2) {
           if (lane == 0) {
-            ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort);
-            tc_fence_after();
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          for (int kb = 0; kb < p.kb_per_tile && ok; ++kb) {
-            if (lane == 0) {
-              ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort);
-              if (ok) {
-                tc_fence_after();
-                const uint32_t sa = tiles + stage * kQStageBytes;
-                const uint32_t sb = sa + kQABytes;
+            ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort);
+            if (ok) {
+              tc_fence_after();
+#pragma unroll
+              for (int h = 0; h < kQHalves; ++h) {
+                if (kQHalves * sb2 + h >= kblocks) break;    // the zero block behind an odd count
+                if (kb == 0) {
+                  // a scale tile starts: its accumulator has to be drained
+                  ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort);
+                  if (!ok) break;
+                  tc_fence_after();
+                }
+                const uint32_t sa = tiles + stage * kQStageBytes + h * kQABytes;
+                const uint32_t sb = tiles + stage * kQStageBytes + kQHalves * kQABytes + h * kQBBytes;
 #pragma unroll
                 for (int kk = 0; kk < QK / QUMMA_K; ++kk) {
                   const uint64_t da = make_smem_desc(sa + kk * QUMMA_K, 16, 1024);
@@ -318,18 +331,24 @@ gemm_q8_tiled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
                                           : make_smem_desc(sb + kk * QUMMA_K * 128, QK * 128, 1024);
                   mma_ss_pair<KIND>(tmem_base + acc * QN, da, db, idesc, kb != 0 || kk != 0);
                 }
-                mma_commit_pair(smem_u32(&ctl->empty[stage]));
-                mma_commit_pair(empty_peer + stage * 8);
-                if (kb == p.kb_per_tile - 1) {
+                if (++kb == p.kb_per_tile) {
+                  kb = 0;
                   mma_commit_pair(smem_u32(&ctl->acc_full[acc]));
                   mma_commit_pair(acc_full_peer + acc * 8);
+                  if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
                 }
               }
+              if (ok) {
+                mma_commit_pair(smem_u32(&ctl->empty[stage]));
+                mma_commit_pair(empty_peer + stage * 8);
+              }
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (++stage == kQStages) { stage = 0; phase ^= 1u; }
           }
-          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          acc = __shfl_sync(0xffffffffu, acc, 0);
+          acc_phase = __shfl_sync(0xffffffffu, acc_phase, 0);
+          kb = __shfl_sync(0xffffffffu, kb, 0);
+          if (++stage == kQStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
