@@ -359,6 +359,72 @@ __global__ void mx_pack_scales_kernel(const void* __restrict__ scale, int dtype,
       (r128 / 32) * 4 + jj] = e;
 }
 
+// The row-major case ([rows, blocks], an activation: packed on every call) four blocks per thread:
+// one vector load of four scales, one 32-bit store of their bytes.
+template <typename S>
+__global__ void mx_pack_scales_rows_kernel(const S* __restrict__ scale, int64_t rows, int64_t quads,
+                                           int tile_rows, int stage_groups, int e4m3_bytes,
+                                           uint32_t* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * quads) return;
+  const int64_t r = i / quads, jq = i % quads;          // row, group of four blocks
+  float s[4];
+  if constexpr (sizeof(S) == 4) {
+    const float4 v = reinterpret_cast<const float4*>(scale)[i];
+    s[0] = v.x; s[1] = v.y; s[2] = v.z; s[3] = v.w;
+  } else {
+    const uint2 v = reinterpret_cast<const uint2*>(scale)[i];
+    const uint32_t w[2] = {v.x, v.y};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint16_t h = (uint16_t)(w[k >> 1] >> (16 * (k & 1)));
+      if constexpr (std::is_same<S, __nv_bfloat16>::value) s[k] = __uint_as_float((uint32_t)h << 16);
+      else s[k] = __half2float(__ushort_as_half(h));
+    }
+  }
+  uint32_t word = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint32_t e = e4m3_bytes ? (uint32_t)__nv_cvt_float_to_fp8(s[k], __NV_SATFINITE, __NV_E4M3)
+                                  : ((__float_as_uint(s[k]) >> 23) & 0xffu);
+    word |= e << (8 * k);
+  }
+  const int groups = (tile_rows + 127) / 128;
+  const int64_t tile = r / tile_rows, rr = r % tile_rows;
+  const int64_t g = rr / 128, r128 = rr % 128;
+  const int64_t kb = jq / stage_groups, sg = jq % stage_groups;
+  const int64_t kblocks = quads / stage_groups;
+  out[((((tile * kblocks + kb) * stage_groups + sg) * groups + g) * 512 + (r128 % 32) * 16 + (r128 / 32) * 4) >> 2] = word;
+}
+
+// Packs `scale` ([rows, blocks] or, k_major, [blocks, rows]) into the kernels' staging order.
+int pack_scales(const void* scale, int scale_dtype, int64_t rows, int64_t blocks, int k_major,
+                int tile_rows, int stage_groups, int e4m3_bytes, void* out, size_t need, cudaStream_t st) {
+  // rows past the operand read a zero byte (2^-127, or e4m3 zero) against zero-filled codes
+  // (nothing is left unwritten when whole 128-row groups are packed)
+  if ((rows % tile_rows != 0 || tile_rows % 128 != 0) && cudaMemsetAsync(out, 0, need, st) != cudaSuccess)
+    return QWX_ERR_LAUNCH;
+  if (!k_major && blocks % 4 == 0 && !(reinterpret_cast<uintptr_t>(scale) & 15)) {
+    const int64_t quads = blocks / 4, n = rows * quads;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    if (scale_dtype == QWX_F32)
+      mx_pack_scales_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)scale, rows, quads, tile_rows,
+                                                              stage_groups, e4m3_bytes, (uint32_t*)out);
+    else if (scale_dtype == QWX_BF16)
+      mx_pack_scales_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+          (const __nv_bfloat16*)scale, rows, quads, tile_rows, stage_groups, e4m3_bytes, (uint32_t*)out);
+    else
+      mx_pack_scales_rows_kernel<__half><<<grid, 256, 0, st>>>((const __half*)scale, rows, quads, tile_rows,
+                                                               stage_groups, e4m3_bytes, (uint32_t*)out);
+  } else {
+    const int64_t n = rows * blocks;
+    mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+        scale, scale_dtype, rows, blocks, k_major, tile_rows, stage_groups, e4m3_bytes, (uint8_t*)out);
+  }
+  QWX_CHECK_LAUNCH();
+  return QWX_OK;
+}
+
 int sm_count_x() {
   static int n = [] {
     int dev = 0, v = 0;
@@ -440,14 +506,8 @@ extern "C" int qwx_mx_pack_scales(int operand, const void* scale, int scale_dtyp
   const size_t need = qwx_mx_scales_packed_bytes(operand, rows, K);
   if (out_bytes < need) return QWX_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(out) & 15) return QWX_ERR_ALIGN;
-  cudaStream_t st = (cudaStream_t)stream;
-  // rows past the operand read scale 2^-127 against zero-filled codes
-  if (cudaMemsetAsync(out, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
-  const int64_t blocks = K / 32, n = rows * blocks;
-  mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 1, 0, (uint8_t*)out);
-  QWX_CHECK_LAUNCH();
-  return QWX_OK;
+  return pack_scales(scale, scale_dtype, rows, K / 32, k_major ? 1 : 0, tile_rows_of(operand), 1, 0, out, need,
+                     (cudaStream_t)stream);
 }
 
 extern "C" int qwx_gemm_mx8(const void* a, const void* b, int b_layout, int64_t M, int64_t N,
@@ -515,13 +575,8 @@ extern "C" int qwx_mx4_pack_scales(int operand, const void* scale, int scale_dty
   const size_t need = qwx_mx4_scales_packed_bytes(operand, rows, K);
   if (out_bytes < need) return QWX_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(out) & 15) return QWX_ERR_ALIGN;
-  cudaStream_t st = (cudaStream_t)stream;
-  if (cudaMemsetAsync(out, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;
-  const int64_t blocks = K / 32, n = rows * blocks;
-  mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 2, 0, (uint8_t*)out);
-  QWX_CHECK_LAUNCH();
-  return QWX_OK;
+  return pack_scales(scale, scale_dtype, rows, K / 32, k_major ? 1 : 0, tile_rows_of(operand), 2, 0, out, need,
+                     (cudaStream_t)stream);
 }
 
 extern "C" int qwx_mx4_pack_codes(const void* codes, int64_t rows, int64_t K, int k_major, void* out,
@@ -613,13 +668,8 @@ extern "C" int qwx_nvfp4_pack_scales(int operand, const void* scale, int scale_d
   const size_t need = qwx_nvfp4_scales_packed_bytes(operand, rows, K);
   if (out_bytes < need) return QWX_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(out) & 15) return QWX_ERR_ALIGN;
-  cudaStream_t st = (cudaStream_t)stream;
-  if (cudaMemsetAsync(out, 0, need, st) != cudaSuccess) return QWX_ERR_LAUNCH;   // e4m3 zero past the operand
-  const int64_t blocks = K / 16, n = rows * blocks;
-  mx_pack_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-      scale, scale_dtype, rows, blocks, k_major ? 1 : 0, tile_rows_of(operand), 4, 1, (uint8_t*)out);
-  QWX_CHECK_LAUNCH();
-  return QWX_OK;
+  return pack_scales(scale, scale_dtype, rows, K / 16, k_major ? 1 : 0, tile_rows_of(operand), 4, 1, out, need,
+                     (cudaStream_t)stream);
 }
 
 extern "C" int qwx_gemm_nvfp4(const void* a_packed, const void* b_packed, int64_t M, int64_t N,
