@@ -47,7 +47,9 @@ def _reference(codes_a, scale_a, codes_b_kn, scale_b_kn):
   return af @ bf
 
 
-@pytest.mark.parametrize('M,N,K', [(128, 224, 256), (100, 200, 512), (300, 500, 1024), (256, 448, 2048)])
+# up to 128 rows: single CTAs; more rows and whole 256-byte K: CTA pairs (one, two, three stages)
+@pytest.mark.parametrize('M,N,K', [(128, 224, 256), (100, 200, 512), (300, 500, 512), (300, 500, 1024),
+                                   (256, 448, 2048), (513, 225, 1536), (200, 300, 768)])
 def test_block_scaled_gemm_of_e2m1_codes(M, N, K):
   rng = np.random.default_rng(M + N + K)
   ca = rng.integers(0, 16, (M, K), dtype=np.uint8)

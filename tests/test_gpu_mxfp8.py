@@ -71,6 +71,9 @@ CASES = [
     (200, 256, 272, 'bfloat16', None),
     (130, 384, 1000, 'bfloat16', 'float32'),     # N % 16 != 0: the weight is repacked [N, K]
     (640, 1024, 672, 'float32', None),           # five row tiles, three 224-column tiles
+    (300, 768, 450, 'bfloat16', None),           # CTA pairs, three stages, ragged rows and columns
+    (257, 256, 225, 'float32', None),            # CTA pairs, one stage, one row and one column over a tile
+    (300, 384, 450, 'bfloat16', None),           # K not whole 256-byte stages: single CTAs
 ]
 
 

@@ -52,7 +52,8 @@ def _e4m3_scales(rng, shape):
   return v.astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
 
 
-@pytest.mark.parametrize('M,N,K', [(128, 224, 256), (100, 200, 512), (300, 500, 1024)])
+@pytest.mark.parametrize('M,N,K', [(128, 224, 256), (100, 200, 512), (300, 500, 512), (300, 500, 1024),
+                                   (513, 225, 1536), (200, 300, 768)])
 def test_block_scaled_gemm_of_e2m1_codes(M, N, K):
   rng = np.random.default_rng(M + N + K)
   ca = rng.integers(0, 16, (M, K), dtype=np.uint8)
