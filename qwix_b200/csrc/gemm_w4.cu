@@ -7,30 +7,35 @@
 // without ever writing W~ to global memory.  The kernel is HBM-bound on the packed weight:
 // K*N/2 bytes are streamed exactly once, every warp reading its own contiguous run.
 //
-// Design.  With 1..64 tokens the arithmetic is small; what decides the time is how little
+// Design.  With 1..32 tokens the arithmetic is small; what decides the time is how little
 // happens per weight byte besides the load.  A CTA-wide tcgen05 pipeline (operand tiles in
 // shared memory, one MMA-issuing thread, mbarrier hand-overs per 8 KB of weights) was measured
 // at 80-90 us for 8192 x 28672 whatever the payload: each hand-over costs about 200 cycles of
 // a single thread and a 128 x 128 unit needs several.  Here nothing is handed over: every warp
-// owns a contiguous range of (16-channel strip, 64-wide K chunk) work items (stream-K at warp
-// granularity), loads its packed codes straight into registers (128-bit loads, eight in
-// flight per lane), converts them in registers into the A fragments of warp-level
+// owns a contiguous range of work items (1, 2 or 4 strips of 16 channels x one 128-wide K
+// chunk; stream-K at warp granularity), brings the items' packed codes and scales into a
+// private cp.async ring, converts the codes in registers into the A fragments of warp-level
 // mma.sync.m16n8k16 (channels are the MMA's M, tokens its N), and takes the B fragments with
-// ldmatrix from the activation slice that the CTA keeps resident in shared memory.  The weight
-// layout is made for this by qwx_pack_w4: a lane's 16 bytes hold exactly its fragment values
-// for four consecutive K tiles, so a warp's load is one contiguous 512-byte line.
+// ldmatrix from the activation slice that the CTA keeps resident in shared memory (one set of
+// B fragments serves all strips of an item).  The weight layout is made for this by
+// qwx_pack_w4: a lane's 16 bytes hold exactly its fragment values for four consecutive K
+// tiles, so a warp's load is one contiguous 512-byte line.
 //
-// The tensor cores multiply the activation with the integer codes themselves (exact in bf16);
-// every 128 K the float32 partial sums are multiplied by the channel's scale and added to the
-// running sums.  With float32 scales this is the reference's arithmetic up to the order of the
-// float32 sums (its dequantized weight q * s is exact in float32); with bf16 scales the
-// reference rounds q * s to bf16 first, which this kernel does not reproduce -- it is closer to
-// the unquantized product, within the stated output tolerance.
+// The tensor cores multiply the activation with 136 + code (one logic operation per pair of
+// codes makes that bf16 number; exact); per 128 K the constant is taken out again with
+// 136 x (sum of the chunk's activations) -- from the same MMAs against an operand of ones, once
+// per CTA -- and the float32 partial sums are multiplied by the channel's scale and added to
+// the running sums.  With float32 scales this is the reference's arithmetic up to the order of
+// the float32 sums (its dequantized weight q * s is exact in float32) and the cancellation of
+// the constant (about 2^-19 of a chunk's sum); with bf16 scales the reference rounds q * s to
+// bf16 first, which this kernel does not reproduce -- it is closer to the unquantized product,
+// within the stated output tolerance.
 //
 // K is cut into `split` slices so that the activation slice (tokens x K / split, bf16) fits
-// shared memory; CTA c works on slice c % split.  A strip whose chunks are spread over several
-// warps (always the case when split > 1) is summed with float atomics in a caller-provided
-// zeroed workspace; the warp that contributes last converts it and clears the workspace.
+// shared memory; CTAs with blockIdx.x = s work on slice s.  A strip whose chunks are spread
+// over several warps (always the case when split > 1) is summed with float atomics in a
+// caller-provided zeroed workspace; the warp that contributes last converts it and clears the
+// workspace.
 #include "common.cuh"
 #include <algorithm>
 
