@@ -9,7 +9,7 @@ import subprocess
 ROOT = pathlib.Path(__file__).resolve().parent
 CSRC = ROOT / 'csrc'
 LIB = ROOT / 'libqwix_b200.so'
-SOURCES = ('capi.cu', 'quantize.cu', 'gemm_q8.cu', 'gemm_q8_pair.cu', 'gemm_q8_tiled.cu', 'gemm_q8_tiled_pair.cu', 'gemm_q8_skinny.cu', 'gemm_q8_decode.cu', 'gemm_mx8.cu', 'gemm_mx_pair.cu', 'gemm_w4.cu', 'gemm_w4_mma.cu', 'hadamard.cu', 'decoder_ops.cu',
+SOURCES = ('capi.cu', 'quantize.cu', 'gemm_q8.cu', 'gemm_q8_pair.cu', 'gemm_q8_narrow.cu', 'gemm_q8_tiled.cu', 'gemm_q8_tiled_pair.cu', 'gemm_q8_skinny.cu', 'gemm_q8_decode.cu', 'gemm_mx8.cu', 'gemm_mx_pair.cu', 'gemm_w4.cu', 'gemm_w4_mma.cu', 'hadamard.cu', 'decoder_ops.cu',
            'xla_ffi_shim.cc')   # compiles to nothing where the XLA FFI headers are absent
 FLAGS = ('-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3',
          '-std=c++17', '-shared', '-Xcompiler', '-fPIC')

@@ -523,6 +523,11 @@ int sm_count() {
 }  // namespace qwx
 
 namespace qwx {
+// gemm_q8_narrow.cu
+int narrow_tile_width(int64_t N, int64_t K, int sms);
+int gemm_q8_narrow_launch(const void* a, const void* b, const void* sa, const void* sb, int scale_dtype,
+                          int64_t M, int64_t N, int64_t K, int code_dtype, void* out, int out_dtype,
+                          int epilogue, int bn, int32_t* error_flag, cudaStream_t st);
 int gemm_q8_pair_launch(const void* a, const void* b, int code_dtype, int b_layout, int64_t M,
                         int64_t N, int64_t K, const void* sa, const void* sb, int scale_dtype,
                         void* out, int out_dtype, int epilogue, int32_t* error_flag, int sms,
@@ -627,6 +632,15 @@ static int gemm_q8_impl(const void* a, const void* b, int code_dtype, int b_layo
       p.ws = (uint32_t*)((char*)workspace + counter_bytes(num_tiles));
       num_tiles *= splits;
     }
+  }
+  // Few rows against a K-major weight with a handful of 256-wide column tiles: narrow column
+  // tiles, one per SM, instead of cutting K (no partial sums through global memory; a workspace
+  // that was passed has been checked above as for the K cut, and stays untouched).
+  if (M <= BM && b_layout == QWX_B_NK && K % BK == 0) {
+    const int bn = narrow_tile_width(N, K, sms);
+    if (bn > 0)
+      return gemm_q8_narrow_launch(a, b, sa, sb, scale_dtype, M, N, K, code_dtype, out, out_dtype, epilogue, bn,
+                                   error_flag, st);
   }
   // Two or more 128-row tiles: the CTA-pair kernel, which moves a third less data per SM.
   if (p.splits == 1 && M > BM)

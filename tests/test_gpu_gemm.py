@@ -605,3 +605,64 @@ def test_decode_kernel_through_dot_general_and_errors():
   args = (_lib.ptr(x), _lib.ptr(x), 32, 512, 1024, None, None, _lib.F32, _lib.ptr(x), _lib.S32, 0,
           _lib.ptr(x), 16, 1, None, _lib.stream_ptr())
   assert L.qwx_gemm_q8_decode(*args) == 6                        # workspace too small
+
+
+# ---- decode-shaped calls on narrow column tiles (no K cut) -------------------------------------
+
+NARROW_SHAPES = [(32, 4096, 4096), (1, 4736, 512), (7, 6144, 1024), (100, 3000, 384), (128, 28672, 256),
+                 (33, 2400, 4096 + 128), (32, 14336, 5120)]
+
+
+@pytest.mark.parametrize('mnk', NARROW_SHAPES, ids=[f'{m}x{n}x{k}' for m, n, k in NARROW_SHAPES])
+def test_narrow_tiles_int8_bit_exact(mnk):
+  """Up to 128 rows against an [N, K] weight whose narrow column tiles fill at least half of the
+  SMs: raw int32 accumulator bit-exact, the float32 and the reference-order epilogue equal to
+  the wide kernel's arithmetic (restated here in NumPy)."""
+  M, N, K = mnk
+  rng = np.random.default_rng(M + N + K)
+  a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+  b = rng.integers(-128, 128, (N, K), dtype=np.int8)
+  want = a.astype(np.int32) @ b.astype(np.int32).T
+  at, bt = h.to_torch(a), h.to_torch(b)
+  L = _lib.lib()
+  err = torch.zeros(1, dtype=torch.int32, device='cuda')
+  out = torch.empty((M, N), dtype=torch.int32, device='cuda')
+  _lib.check(L.qwx_gemm_q8(_lib.ptr(at), _lib.ptr(bt), _lib.S8, _lib.B_NK, M, N, K, 0, None, 0, None, 0,
+                           _lib.F32, _lib.ptr(out), _lib.S32, 0, _lib.ptr(err), _lib.stream_ptr()), 'gemm')
+  torch.cuda.synchronize()
+  assert int(err.item()) == 0
+  assert np.array_equal(out.cpu().numpy(), want)
+  sa = (rng.random(M) + 0.5).astype(np.float32)
+  sb = (rng.random(N) * 1e-3).astype(np.float32)
+  sa_t, sb_t = h.to_torch(sa), h.to_torch(sb)
+  for epi, odt in ((0, torch.float32), (0, torch.bfloat16), (1, torch.bfloat16)):
+    o = torch.empty((M, N), dtype=odt, device='cuda')
+    oc = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}[odt]
+    _lib.check(L.qwx_gemm_q8(_lib.ptr(at), _lib.ptr(bt), _lib.S8, _lib.B_NK, M, N, K, 0,
+                             _lib.ptr(sa_t), 0, _lib.ptr(sb_t), 0, _lib.F32, _lib.ptr(o), oc,
+                             epi, _lib.ptr(err), _lib.stream_ptr()), 'gemm')
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    f = want.astype(np.float32)
+    if epi == 0:
+      ref = (f * sa[:, None]) * sb[None, :]
+      ref_t = torch.from_numpy(ref).to(odt)
+    else:
+      import ml_dtypes
+      bf = ml_dtypes.bfloat16
+      r = f.astype(bf).astype(np.float32)
+      r = (r * sa[:, None]).astype(bf).astype(np.float32)
+      r = (r * sb[None, :]).astype(bf)
+      ref_t = torch.from_numpy(r.astype(np.float32)).to(odt)
+    assert torch.equal(o.cpu(), ref_t), (epi, odt)
+
+
+def test_narrow_tiles_fp8():
+  import ml_dtypes
+  M, N, K = 16, 4096, 2048
+  rng = np.random.default_rng(5)
+  a = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+  b = rng.standard_normal((N, K)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+  want = a.astype(np.float32) @ b.astype(np.float32).T
+  got = _raw_gemm(h.to_torch(a), h.to_torch(b), _lib.B_NK, code=_lib.E4M3, out_dtype=torch.float32)
+  assert np.abs(got.cpu().numpy() - want).max() <= 1e-3 * np.abs(want).max()
