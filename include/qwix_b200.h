@@ -179,8 +179,12 @@ int qwx_gemm_q8(const void* a, const void* b, int code_dtype, int b_layout,
  * behaves exactly like qwx_gemm_q8 and workspace may be NULL).  The workspace opens with
  * two int32 counters per output tile; these must be zero on entry (workspace_is_zero = 0
  * makes the call clear them first) and are left zero on return, so one buffer cleared once
- * serves every call on a stream.  The reference has no counterpart: XLA picks its own split
- * of the contraction (dot_general.py:253-258 hands it one lax.dot_general). */
+ * serves every call on a stream.  Up to 128 rows against an [N, K] weight with K <= 5120 and
+ * enough columns to give at least half of the SMs a 32..256-wide column tile are not cut along
+ * K at all (every CTA streams whole weight rows and finishes its own tile): such calls, through
+ * either entry point, leave a workspace that was passed untouched.  The reference has no
+ * counterpart: XLA picks its own split of the contraction (dot_general.py:253-258 hands it one
+ * lax.dot_general). */
 size_t qwx_gemm_q8_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int qwx_gemm_q8_ws(const void* a, const void* b, int code_dtype, int b_layout,
                    int64_t M, int64_t N, int64_t K, int64_t k_tile,
