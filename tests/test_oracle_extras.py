@@ -58,6 +58,34 @@ def test_mxfp8_quantize_then_dot_is_close_to_the_float_product():
   np.testing.assert_allclose(out, odg.slow_dot_general(a, b, DN), rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize('qtype,tile,bound', [('mxfp4', 32, 0.25), ('nvfp4', 16, 0.2)])
+def test_four_bit_quantize_then_dot(qtype, tile, bound):
+  """e2m1 codes (qarray.py:566-581, numerics.py:186-187): the scales are powers of two (mxfp4)
+  or e4m3 numbers (nvfp4), the codes lie on the e2m1 grid, and the microscaled dot agrees with
+  dequantize-then-contract."""
+  import ml_dtypes
+  rng = np.random.default_rng(3)
+  x = rng.standard_normal((16, 128)).astype(np.float32)
+  w = (0.1 * rng.standard_normal((128, 24))).astype(np.float32)
+  kw = dict(dimension_numbers=DN, ndims=(2, 2), tile_size=tile, qtype=qtype)
+  a = oq.quantize(x, odg.get_how_to_quantize(for_lhs=True, **kw))
+  b = oq.quantize(w, odg.get_how_to_quantize(for_lhs=False, **kw))
+  assert a.scale.shape == (16, 128 // tile) and b.scale.shape == (128 // tile, 24)
+  if qtype == 'mxfp4':
+    assert np.all(np.frexp(a.scale)[0] == 0.5) and np.all(np.frexp(b.scale)[0] == 0.5)
+  else:
+    for s in (a.scale, b.scale):
+      assert np.array_equal(s.astype(ml_dtypes.float8_e4m3fn).astype(np.float32), s.astype(np.float32))
+  grid = {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0}
+  assert set(np.abs(a.qvalue.astype(np.float32)).ravel().tolist()) <= grid
+  # absmax of every block maps to a code of magnitude at least 4 (the scale keeps the range in use)
+  assert np.all(np.abs(a.qvalue.astype(np.float32)).reshape(16, -1, tile).max(axis=2) >= 3.0)
+  out = omx.mxfp_dot_general(a, b, DN)
+  ref = x @ w
+  assert np.abs(out - ref).mean() / np.abs(ref).mean() < bound
+  np.testing.assert_allclose(out, odg.slow_dot_general(a, b, DN), rtol=1e-5, atol=1e-5)
+
+
 def test_ragged_dot_groups_and_leftover_rows():
   rng = np.random.default_rng(2)
   x = rng.standard_normal((20, 32)).astype(np.float32)
