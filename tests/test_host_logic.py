@@ -346,3 +346,39 @@ def test_lazy_activation_protocol_is_host_only_until_consumed():
   assert not f._fusable(q.HowToQuantize(qtype='int8', channelwise_axes=[0, 1], calibration_method='minmax'))
   with pytest.raises(RuntimeError):      # CPU tensors never reach a kernel
     fused.AddRmsNorm(torch.zeros(2, 8, dtype=torch.bfloat16), None, torch.ones(8, dtype=torch.bfloat16), 1e-5)
+
+
+def test_microscaled_dispatcher_declines_what_has_no_kernel():
+  """mxfp_dot.py:51-57: the dispatcher returns None (the caller dequantizes) for operands it
+  cannot take.  Here: one side not microscaled, mixed formats, a contracted length that is not
+  whole 128-byte stages; decided on the host, before any device call."""
+  from qwix_b200.core import mxfp_dot as bmx
+  DN = (((1,), (0,)), ((), ()))
+
+  def qa(rows, K, qtype, block, k_major=False):
+    dt = torch.float8_e4m3fn if qtype == 'mxfp8' else torch.uint8
+    if k_major:
+      return bq.QArray(torch.zeros((K, rows), dtype=dt), torch.ones((K // block, rows)), None, qtype)
+    return bq.QArray(torch.zeros((rows, K), dtype=dt), torch.ones((rows, K // block)), None, qtype)
+
+  assert bmx.mxfp_dot_general(qa(8, 256, 'mxfp4', 32), torch.zeros(256, 16), DN) is None
+  assert bmx.mxfp_dot_general(qa(8, 256, 'mxfp4', 32), qa(16, 256, 'nvfp4', 16, True), DN) is None
+  assert bmx.mxfp_dot_general(qa(8, 256, 'mxfp8', 32), qa(16, 256, 'mxfp4', 32, True), DN) is None
+  assert bmx.mxfp_dot_general(qa(8, 128, 'mxfp4', 32), qa(16, 128, 'mxfp4', 32, True), DN) is None   # K % 256
+  assert bmx.mxfp_dot_general(qa(8, 128, 'nvfp4', 16), qa(16, 128, 'nvfp4', 16, True), DN) is None
+  assert bmx.mxfp_dot_general(qa(8, 64, 'mxfp8', 32), qa(16, 64, 'mxfp8', 32, True), DN) is None      # K % 128
+  # operands it is built for go on to the device library, which refuses host tensors loudly
+  with pytest.raises(RuntimeError, match='CUDA device only'):
+    bmx.mxfp_dot_general(qa(8, 256, 'mxfp4', 32), qa(16, 256, 'mxfp4', 32, True), DN)
+
+
+def test_four_bit_qtypes_are_built():
+  assert numerics.storage('mxfp4') == (torch.uint8, _lib.MXFP4)
+  assert numerics.storage('nvfp4') == (torch.uint8, _lib.NVFP4)
+  assert numerics.get_symmetric_bound('mxfp4') == numerics.get_symmetric_bound('nvfp4') == 6.0
+  with pytest.raises(NotImplementedError):
+    numerics.storage('mxfp8_16')
+  with pytest.raises(ValueError, match='requires a tile size of 16'):
+    bq.HowToQuantize(qtype='nvfp4', channelwise_axes=[0], tiled_axes={1: 32})
+  with pytest.raises(ValueError, match='requires a tile size of 32'):
+    bq.HowToQuantize(qtype='mxfp4', channelwise_axes=[0], tiled_axes={1: 16})
